@@ -1,0 +1,142 @@
+"""Python view of a compiled step program (``csrc/sched/program.h``).
+
+A program is the schedule of one collective algorithm for a fixed
+``(collective, algorithm, P, k, b, count)``: per rank and per round a list of
+pull steps ``dst = [dst op] src_0 op src_1 ...`` plus the cross-rank waits and
+signals that order them.  The same object feeds
+
+* :meth:`Program.simulate` — all ranks on host buffers in one process,
+* :class:`..parallel.gloo_exec.GlooExecutor` — one process per rank, CPU tensors,
+* the persistent GPU interpreter kernel (``csrc/kernels/interp.cu``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from functools import lru_cache
+
+import numpy as np
+
+from .. import _native as N
+
+BUF_IN, BUF_OUT, BUF_WORK = 0, 1, 2
+
+_NP_DTYPES = {
+    N.F32: np.float32, N.F64: np.float64, N.I32: np.int32, N.I64: np.int64, N.U8: np.uint8,
+}
+_DT_FROM_NP = {np.dtype(v): k for k, v in _NP_DTYPES.items()}
+_OPS = {"sum": N.SUM, "max": N.MAX, "min": N.MIN, "prod": N.PROD}
+
+COLLECTIVES = ("allreduce", "reduce_scatter", "allgather", "alltoall", "gather")
+
+
+class ProgramError(ValueError):
+    """The requested algorithm cannot be built for these parameters."""
+
+
+def list_algorithms(coll: str) -> list[str]:
+    buf = C.create_string_buffer(1024)
+    N.lib().chb_list_algorithms(coll.encode(), buf, len(buf))
+    s = buf.value.decode()
+    return s.split(",") if s else []
+
+
+@dataclass(frozen=True)
+class Step:
+    rank: int
+    round: int
+    dst_buf: int
+    dst_off: int
+    count: int
+    acc: bool
+    srcs: tuple  # of (peer, buf, off)
+
+
+class Program:
+    def __init__(self, coll: str, algo: str, P: int, count: int, k: int = 2, b: int = 1, aux: int = 0,
+                 in_symmetric: bool = False, out_symmetric: bool = False):
+        L = N.lib()
+        err = C.create_string_buffer(512)
+        h = L.chb_program_create(coll.encode(), algo.encode(), P, k, b, count, aux,
+                                 int(in_symmetric), int(out_symmetric), err, len(err))
+        if not h:
+            raise ProgramError(err.value.decode() or "program creation failed")
+        self._h = h
+        self.coll, self.algo, self.k, self.b, self.count, self.aux = coll, algo, k, b, count, aux
+        info = (C.c_int64 * 32)()
+        L.chb_program_info(h, info, 32)
+        (self.P, self.nrounds, self.in_elems, self.out_elems, self.work_elems, self.nops,
+         self.remote_msgs, self.remote_elems, self.max_rank_remote_elems, self.local_elems,
+         self.max_nsrc, rpi, rpo, self.nsrcs, self.nwaits, self.nexit_waits, self.nsignals) = [int(x) for x in info[:17]]
+        self.reads_peer_in, self.reads_peer_out = bool(rpi), bool(rpo)
+        self.in_symmetric, self.out_symmetric = in_symmetric, out_symmetric
+        self.name = L.chb_program_name(h).decode()
+        self._tables = None
+
+    def __del__(self):
+        try:
+            if getattr(self, "_h", None):
+                N.lib().chb_program_destroy(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+    @property
+    def handle(self):
+        return self._h
+
+    # ------------------------------------------------------------------ tables
+    def tables(self):
+        """(ops[NOPS,8], srcs[NSRCS,3], waits[NWAITS,4], exit_waits[*,3], signals[*,3]) as int64 arrays."""
+        if self._tables is None:
+            ops = np.zeros((self.nops, 8), np.int64)
+            srcs = np.zeros((self.nsrcs, 3), np.int64)
+            waits = np.zeros((self.nwaits, 4), np.int64)
+            ex = np.zeros((self.nexit_waits, 3), np.int64)
+            sig = np.zeros((self.nsignals, 3), np.int64)
+            p = lambda a: a.ctypes.data_as(C.c_void_p)
+            N.lib().chb_program_export(self._h, p(ops), p(srcs), p(waits), p(ex), p(sig))
+            self._tables = (ops, srcs, waits, ex, sig)
+        return self._tables
+
+    def steps(self, rank: int | None = None) -> list[Step]:
+        ops, srcs, *_ = self.tables()
+        out = []
+        for o in ops:
+            if rank is not None and o[0] != rank:
+                continue
+            s = tuple((int(p), int(b), int(f)) for p, b, f in srcs[o[6]:o[6] + o[7]])
+            out.append(Step(int(o[0]), int(o[1]), int(o[2]), int(o[3]), int(o[4]), bool(o[5]), s))
+        return out
+
+    # ------------------------------------------------------------------ checks
+    def verify(self) -> int:
+        err = C.create_string_buffer(2048)
+        bad = N.lib().chb_program_verify(self._h, err, len(err))
+        if bad:
+            raise AssertionError(f"{self.name}: {bad} unsynchronised hazards: {err.value.decode()}")
+        return 0
+
+    def simulate(self, inputs: list[np.ndarray], op: str = "sum", seed: int = 0) -> list[np.ndarray]:
+        """Run all P ranks on host arrays; returns the P output arrays."""
+        assert len(inputs) == self.P
+        dt = inputs[0].dtype
+        code = _DT_FROM_NP[np.dtype(dt)]
+        ins = [np.ascontiguousarray(x, dtype=dt) for x in inputs]
+        for x in ins:
+            assert x.size == self.in_elems, (x.size, self.in_elems)
+        # outputs start poisoned so that positions the program never writes stand out
+        outs = [np.full(self.out_elems, -17, dtype=dt) for _ in range(self.P)]
+        ip = (C.c_void_p * self.P)(*[x.ctypes.data for x in ins])
+        opp = (C.c_void_p * self.P)(*[x.ctypes.data for x in outs])
+        err = C.create_string_buffer(512)
+        rc = N.lib().chb_program_simulate(self._h, code, _OPS[op], ip, opp, seed, err, len(err))
+        if rc:
+            raise RuntimeError(f"simulate({self.name}) failed: {err.value.decode()}")
+        return outs
+
+
+@lru_cache(maxsize=512)
+def cached_program(coll: str, algo: str, P: int, count: int, k: int = 2, b: int = 1, aux: int = 0,
+                   in_symmetric: bool = False, out_symmetric: bool = False) -> Program:
+    return Program(coll, algo, P, count, k, b, aux, in_symmetric, out_symmetric)

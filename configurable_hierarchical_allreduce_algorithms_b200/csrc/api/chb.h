@@ -39,6 +39,8 @@ enum { CHB_SUM = 0, CHB_MAX = 1, CHB_MIN = 2, CHB_PROD = 3 };
 /* ------------------------------------------------------------------ programs */
 typedef struct chb_program chb_program_t;
 
+/* in_symmetric: bit 0 = peers may read the caller's input directly, bit 1 = the
+ * input aliases the output (every read of the input goes through scratch). */
 chb_program_t* chb_program_create(const char* coll, const char* algo, int P, int k, int b,
                                   int64_t count, int aux, int in_symmetric, int out_symmetric,
                                   char* err, int errlen);

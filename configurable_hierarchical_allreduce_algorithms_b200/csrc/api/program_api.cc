@@ -7,10 +7,7 @@
 #include "../sched/algos.h"
 #include "../sched/program.h"
 #include "chb.h"
-
-struct chb_program {
-  chb::Program prog;
-};
+#include "program_handle.h"
 
 namespace {
 void set_err(char* err, int errlen, const std::string& s) {
@@ -35,7 +32,8 @@ chb_program_t* chb_program_create(const char* coll, const char* algo, int P, int
     s.aux = aux;
     chb::Builder B = chb::build_algorithm(s);
     chb::LowerOpts o;
-    o.in_symmetric = in_symmetric != 0;
+    o.in_symmetric = (in_symmetric & 1) != 0;
+    o.in_place = (in_symmetric & 2) != 0;  // bit 1: input aliases output
     o.out_symmetric = out_symmetric != 0;
     auto* p = new chb_program;
     p->prog = B.lower(o);

@@ -1,0 +1,383 @@
+// Persistent step-program interpreter: one launch executes a whole collective.
+//
+// A compiled program (csrc/sched/program.h) is flattened into a device blob;
+// every rank walks its rounds: wait for the (peer, round) pairs the round
+// depends on, run the round's pull steps with all CTAs of the rank, meet at
+// the rank-local barrier, then release the peers that wait for this round.
+// A step reads up to kMaxSrc regions (local or peer, 16-byte vectors through
+// the owner's L2), combines them in fp32 (or the native integer / double
+// type) and stores the result once; this is where the reference's
+// MPI_Isend/Irecv/Waitall + MPI_Reduce_local loops end up
+// (testing/custom_implementations/work_dir/all_reduce/all_reduce_radix_batch.cpp:339-368,
+//  501-539, 552-569, 591-646).
+//
+// With World::nlocal == P (all ranks emulated on one GPU) blockIdx.y selects
+// the rank and the launch is cooperative, so that ranks which wait for each
+// other are guaranteed to be co-resident.
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "../api/chb.h"
+#include "../api/program_handle.h"
+#include "../symm/comm.h"
+#include "common.cuh"
+
+namespace chb {
+
+constexpr int kInterpThreads = 512;
+constexpr int kMaxSrc = 40;              // sources per step (incl. the accumulate operand)
+constexpr long long kSmallStepBytes = 64 << 10;  // below this one CTA runs the whole step
+
+struct DevStep { long long dst_off; long long count; int dst_buf; int nsrc; int src_begin; unsigned flags; };
+struct DevSrc { long long off; int peer; int buf; };
+struct DevWait { int peer; int need; };
+struct DevRound { int step_begin, step_end, wait_begin, wait_end, sig_begin, sig_end; };
+struct DevHeader {
+  int P, nrounds, nsteps, nsrcs, nwaits, nsigs;
+  long long off_rounds, off_steps, off_srcs, off_waits, off_sigs, off_exit;
+};
+
+struct IoTable {
+  const char* in[kMaxRanks];
+  char* out[kMaxRanks];
+};
+
+static std::vector<char> make_blob(const Program& p) {
+  DevHeader h{};
+  h.P = p.P;
+  h.nrounds = p.nrounds;
+  std::vector<DevRound> rounds((size_t)p.P * p.nrounds);
+  std::vector<DevStep> steps;
+  std::vector<DevSrc> srcs;
+  std::vector<DevWait> waits;
+  std::vector<int> sigs;
+  std::vector<int> exits((size_t)p.P * 2);
+  for (int r = 0; r < p.P; ++r)
+    for (int t = 0; t < p.nrounds; ++t) {
+      const RankRound& rr = p.rr[r][t];
+      DevRound& d = rounds[(size_t)r * p.nrounds + t];
+      d.step_begin = (int)steps.size();
+      for (int oi : rr.ops) {
+        const Op& o = p.ops[oi];
+        DevStep s{};
+        s.dst_off = o.dst_off;
+        s.count = o.count;
+        s.dst_buf = o.dst_buf;
+        s.flags = o.flags | (o.acc ? 0x100u : 0u);
+        s.src_begin = (int)srcs.size();
+        s.nsrc = (int)o.srcs.size();
+        for (const Src& x : o.srcs) srcs.push_back(DevSrc{x.off, x.peer, x.buf});
+        steps.push_back(s);
+      }
+      d.step_end = (int)steps.size();
+      d.wait_begin = (int)waits.size();
+      for (const Wait& w : rr.waits) waits.push_back(DevWait{w.peer, w.need});
+      d.wait_end = (int)waits.size();
+      d.sig_begin = (int)sigs.size();
+      for (int q : rr.signals) sigs.push_back(q);
+      d.sig_end = (int)sigs.size();
+    }
+  for (int r = 0; r < p.P; ++r) {
+    exits[2 * r] = (int)waits.size();
+    for (const Wait& w : p.exit_waits[r]) waits.push_back(DevWait{w.peer, w.need});
+    exits[2 * r + 1] = (int)waits.size();
+  }
+  h.nsteps = (int)steps.size();
+  h.nsrcs = (int)srcs.size();
+  h.nwaits = (int)waits.size();
+  h.nsigs = (int)sigs.size();
+  auto al = [](size_t x) { return (x + 15) / 16 * 16; };
+  size_t off = al(sizeof(DevHeader));
+  h.off_rounds = (long long)off; off = al(off + rounds.size() * sizeof(DevRound));
+  h.off_steps = (long long)off;  off = al(off + steps.size() * sizeof(DevStep));
+  h.off_srcs = (long long)off;   off = al(off + srcs.size() * sizeof(DevSrc));
+  h.off_waits = (long long)off;  off = al(off + waits.size() * sizeof(DevWait));
+  h.off_sigs = (long long)off;   off = al(off + sigs.size() * sizeof(int));
+  h.off_exit = (long long)off;   off = al(off + exits.size() * sizeof(int));
+  std::vector<char> blob(off, 0);
+  std::memcpy(blob.data(), &h, sizeof(h));
+  auto put = [&](long long o, const void* src, size_t n) { if (n) std::memcpy(blob.data() + o, src, n); };
+  put(h.off_rounds, rounds.data(), rounds.size() * sizeof(DevRound));
+  put(h.off_steps, steps.data(), steps.size() * sizeof(DevStep));
+  put(h.off_srcs, srcs.data(), srcs.size() * sizeof(DevSrc));
+  put(h.off_waits, waits.data(), waits.size() * sizeof(DevWait));
+  put(h.off_sigs, sigs.data(), sigs.size() * sizeof(int));
+  put(h.off_exit, exits.data(), exits.size() * sizeof(int));
+  return blob;
+}
+
+// ------------------------------------------------------------------ one step
+template <typename T>
+__device__ __forceinline__ void run_step(const DevStep& st, const DevSrc* __restrict__ srcs, const World& w,
+                                         const IoTable& io, int rank, unsigned part, unsigned nparts,
+                                         int op, float scale, const char** s_ptr, int* s_meta) {
+  using Acc = typename Elem<T>::Acc;
+  constexpr int VE = Elem<T>::kPerVec;
+  const int tid = threadIdx.x;
+  const bool acc = (st.flags & 0x100u) != 0;
+  const int nsrc = st.nsrc + (acc ? 1 : 0);
+  __syncthreads();  // previous step's readers of s_ptr are done
+  if (tid < nsrc || tid == kMaxSrc) {
+    if (tid == kMaxSrc) {
+      char* base = st.dst_buf == 0 ? const_cast<char*>(io.in[rank]) : (st.dst_buf == 1 ? io.out[rank] : w.work[rank]);
+      s_ptr[kMaxSrc] = base + st.dst_off * (long long)sizeof(T);
+    } else if (acc && tid == 0) {
+      char* base = st.dst_buf == 1 ? io.out[rank] : w.work[rank];
+      s_ptr[0] = base + st.dst_off * (long long)sizeof(T);
+    } else {
+      const DevSrc s = srcs[st.src_begin + tid - (acc ? 1 : 0)];
+      const char* base = s.buf == 0 ? io.in[s.peer] : (s.buf == 1 ? io.out[s.peer] : w.work[s.peer]);
+      s_ptr[tid] = base + s.off * (long long)sizeof(T);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    unsigned long long m = (unsigned long long)s_ptr[kMaxSrc];
+    for (int i = 0; i < nsrc; ++i) m |= (unsigned long long)s_ptr[i];
+    s_meta[0] = (m & 15ull) == 0ull;
+  }
+  __syncthreads();
+  const bool aligned = s_meta[0] != 0;
+  char* dst = const_cast<char*>(s_ptr[kMaxSrc]);
+  const bool do_scale = (st.flags & OPF_FINAL) && scale != 1.0f;
+  const long long count = st.count;
+  const long long nvec = aligned ? count / VE : 0;
+  const long long TT = (long long)nparts * blockDim.x;
+  const long long g = (long long)part * blockDim.x + tid;
+  constexpr int U = 4;
+  for (long long i0 = g; i0 < nvec; i0 += TT * U) {
+    Acc a[U][VE];
+    {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + (long long)u * TT;
+        v[u] = (i < nvec) ? ld16_cg(s_ptr[0] + i * 16) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) vec_to_acc<T>(v[u], a[u]);
+    }
+    for (int s = 1; s < nsrc; ++s) {
+      uint4 x[U];
+      const char* p0 = s_ptr[s];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + (long long)u * TT;
+        x[u] = (i < nvec) ? ld16_cg(p0 + i * 16) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) vec_combine<T>(op, x[u], a[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + (long long)u * TT;
+      if (i < nvec) {
+        if (do_scale) acc_scale<T>(a[u], scale);
+        st16(dst + i * 16, acc_to_vec<T>(a[u]));
+      }
+    }
+  }
+  // scalar tail (or the whole step when some pointer is not 16-byte aligned)
+  for (long long e = nvec * VE + g; e < count; e += TT) {
+    Acc a = Elem<T>::up(reinterpret_cast<const T*>(s_ptr[0])[e]);
+    for (int s = 1; s < nsrc; ++s)
+      a = combine<Acc>(op, a, Elem<T>::up(__ldcg(reinterpret_cast<const T*>(s_ptr[s]) + e)));
+    if (do_scale) a = (Acc)(a * scale);
+    reinterpret_cast<T*>(dst)[e] = Elem<T>::down(a);
+  }
+}
+
+// ------------------------------------------------------------------ the kernel
+template <typename T>
+__global__ void __launch_bounds__(kInterpThreads, 1)
+interp_kernel(World w, const char* __restrict__ blob, IoTable io, int op, float scale) {
+  const int rank = w.rank0 + (int)blockIdx.y;
+  const unsigned nct = gridDim.x, cta = blockIdx.x;
+  const int tid = threadIdx.x;
+  Ctrl* c = w.ctrl[rank];
+  const DevHeader* h = reinterpret_cast<const DevHeader*>(blob);
+  const DevRound* rounds = reinterpret_cast<const DevRound*>(blob + h->off_rounds) + (size_t)rank * h->nrounds;
+  const DevStep* steps = reinterpret_cast<const DevStep*>(blob + h->off_steps);
+  const DevSrc* srcs = reinterpret_cast<const DevSrc*>(blob + h->off_srcs);
+  const DevWait* waits = reinterpret_cast<const DevWait*>(blob + h->off_waits);
+  const int* sigs = reinterpret_cast<const int*>(blob + h->off_sigs);
+  const int* exits = reinterpret_cast<const int*>(blob + h->off_exit);
+  const int P = h->P, nrounds = h->nrounds;
+
+  __shared__ unsigned long long s_base;
+  __shared__ int s_ok;
+  __shared__ const char* s_ptr[kMaxSrc + 1];
+  __shared__ int s_meta[2];
+  if (tid == 0) {
+    s_base = ld_volatile_u64(&c->epoch);
+    s_ok = ld_volatile_u32(&c->abort) ? 0 : 1;
+  }
+  __syncthreads();
+  const unsigned long long base = s_base;
+  unsigned gen = 0;
+  // every peer has left the previous launch (its last round signals everybody)
+  if (tid < P && tid != rank)
+    if (!wait_flag_ge(&w.sig[rank][tid], base, c, w.timeout_ns, ST_TIMEOUT_ENTRY, rank, -1, tid)) s_ok = 0;
+  __syncthreads();
+  bool ok = s_ok != 0;
+
+  for (int t = 0; t < nrounds && ok; ++t) {
+    const DevRound R = rounds[t];
+    for (int i = R.wait_begin + tid; i < R.wait_end; i += blockDim.x) {
+      const DevWait wt = waits[i];
+      if (!wait_flag_ge(&w.sig[rank][wt.peer], base + (unsigned long long)wt.need + 1ull, c, w.timeout_ns,
+                        ST_TIMEOUT_ROUND, rank, t, wt.peer))
+        s_ok = 0;
+    }
+    __syncthreads();
+    ok = s_ok != 0;
+    if (!ok) break;
+    for (int s = R.step_begin; s < R.step_end; ++s) {
+      const DevStep st = steps[s];
+      const bool small = st.count * (long long)sizeof(T) < kSmallStepBytes;
+      if (small) {
+        if ((unsigned)(s - R.step_begin) % nct == cta)
+          run_step<T>(st, srcs, w, io, rank, 0u, 1u, op, scale, s_ptr, s_meta);
+      } else {
+        run_step<T>(st, srcs, w, io, rank, cta, nct, op, scale, s_ptr, s_meta);
+      }
+    }
+    ok = rank_barrier(c, nct, gen, w.timeout_ns, rank, t);
+    if (!ok) break;
+    if (cta == 0) {
+      const int n = R.sig_end - R.sig_begin;
+      for (int i = tid; i < n; i += blockDim.x) {
+        __threadfence_system();
+        st_release_sys(&w.sig[sigs[R.sig_begin + i]][rank], base + (unsigned long long)t + 1ull);
+      }
+    }
+  }
+  // peers that read this rank's caller buffers directly must be done with them
+  if (ok) {
+    for (int i = exits[2 * rank] + tid; i < exits[2 * rank + 1]; i += blockDim.x) {
+      const DevWait wt = waits[i];
+      wait_flag_ge(&w.sig[rank][wt.peer], base + (unsigned long long)wt.need + 1ull, c, w.timeout_ns,
+                   ST_TIMEOUT_EXIT, rank, nrounds, wt.peer);
+    }
+  }
+  rank_exit(c, nct, [&](Ctrl* cc) { cc->epoch = base + (unsigned long long)nrounds; });
+}
+
+typedef void (*InterpFn)(World, const char*, IoTable, int, float);
+
+static InterpFn pick_kernel(int dtype) {
+  switch (dtype) {
+    case DT_F32: return interp_kernel<float>;
+    case DT_BF16: return interp_kernel<__nv_bfloat16>;
+    case DT_F16: return interp_kernel<__half>;
+    case DT_I32: return interp_kernel<int32_t>;
+    case DT_F64: return interp_kernel<double>;
+    case DT_I64: return interp_kernel<int64_t>;
+    case DT_U8: return interp_kernel<uint8_t>;
+  }
+  return nullptr;
+}
+
+}  // namespace chb
+
+using namespace chb;
+
+extern "C" {
+
+// Upload (once) and return the device blob of a program for this communicator.
+static int get_blob(chb_comm* c, const chb_program* p, void** out) {
+  auto it = c->blobs.find(p);
+  if (it != c->blobs.end()) { *out = it->second; return CHB_SUCCESS; }
+  if (p->prog.stats.max_nsrc > kMaxSrc) { c->last_error = "program has a step with too many sources"; return CHB_ERR_UNSUPPORTED; }
+  std::vector<char> blob = make_blob(p->prog);
+  void* d = nullptr;
+  if (cudaMalloc(&d, blob.size()) != cudaSuccess) { c->last_error = "cudaMalloc(program blob) failed"; return CHB_ERR_NO_MEM; }
+  if (cudaMemcpy(d, blob.data(), blob.size(), cudaMemcpyHostToDevice) != cudaSuccess) {
+    cudaFree(d);
+    c->last_error = "cudaMemcpy(program blob) failed";
+    return CHB_ERR_CUDA;
+  }
+  c->blobs[p] = d;
+  *out = d;
+  return CHB_SUCCESS;
+}
+
+int chb_program_prepare(chb_comm* c, const chb_program* p) {
+  if (!c || !p) return CHB_ERR_ARG;
+  void* d;
+  return get_blob(c, p, &d);
+}
+
+void chb_program_release(chb_comm* c, const chb_program* p) {
+  if (!c) return;
+  auto it = c->blobs.find(p);
+  if (it != c->blobs.end()) { cudaFree(it->second); c->blobs.erase(it); }
+}
+
+// Launch a compiled program.  in / out hold one pointer per local rank
+// (nlocal entries).  A caller buffer that lies inside the rank's symmetric
+// heap is peer-visible at the same offset on every rank; the program must
+// have been compiled with in_symmetric / out_symmetric only if that holds.
+int chb_run_program(chb_comm* c, const chb_program* p, int dtype, int op, const void* const* in,
+                    void* const* out, float scale, int nctas, cudaStream_t stream) {
+  if (!c || !p || !in || !out) return CHB_ERR_ARG;
+  const Program& g = p->prog;
+  if (g.P != c->P) { c->last_error = "program was compiled for a different number of ranks"; return CHB_ERR_ARG; }
+  InterpFn fn = pick_kernel(dtype);
+  if (!fn) return CHB_ERR_ARG;
+  const size_t esz = (size_t)dtype_size(dtype);
+  if ((size_t)g.work_elems * esz > c->scratch_bytes) {
+    c->last_error = "program needs more symmetric scratch than the communicator has";
+    return CHB_ERR_NO_MEM;
+  }
+  if (op == OP_PROD && (dtype == DT_U8)) return CHB_ERR_OP;
+  void* blob;
+  int rc = get_blob(c, p, &blob);
+  if (rc) return rc;
+  IoTable io{};
+  for (int q = 0; q < c->P; ++q) { io.in[q] = nullptr; io.out[q] = nullptr; }
+  for (int l = 0; l < c->nlocal; ++l) {
+    io.in[c->rank + l] = (const char*)in[l];
+    io.out[c->rank + l] = (char*)out[l];
+  }
+  if (c->nlocal == 1) {
+    // peers' caller buffers: same offset inside their heaps
+    if (g.reads_peer_in && g.in_symmetric) {
+      for (int q = 0; q < c->P; ++q) {
+        char* t = c->translate(in[0], c->rank, q);
+        if (!t) { c->last_error = "input is not inside the symmetric heap"; return CHB_ERR_ARG; }
+        io.in[q] = t;
+      }
+    }
+    if (g.reads_peer_out && g.out_symmetric) {
+      for (int q = 0; q < c->P; ++q) {
+        char* t = c->translate(out[0], c->rank, q);
+        if (!t) { c->last_error = "output is not inside the symmetric heap"; return CHB_ERR_ARG; }
+        io.out[q] = t;
+      }
+    }
+  }
+  int per_rank_budget = c->max_ctas / (c->nlocal > 0 ? c->nlocal : 1);
+  if (per_rank_budget < 1) per_rank_budget = 1;
+  if (nctas <= 0) {
+    // enough CTAs to keep NVLink busy for large steps, one for latency-bound programs
+    long long bytes = (long long)std::max(g.in_elems, g.out_elems) * (long long)esz;
+    nctas = bytes <= (64 << 10) ? 1 : (bytes <= (1 << 20) ? 8 : (bytes <= (16 << 20) ? 32 : 64));
+  }
+  if (nctas > per_rank_budget) nctas = per_rank_budget;
+  dim3 grid((unsigned)nctas, (unsigned)c->nlocal, 1), block(kInterpThreads, 1, 1);
+  World w = c->world;
+  const char* blobp = (const char*)blob;
+  void* args[] = {&w, &blobp, &io, &op, &scale};
+  cudaError_t e;
+  if (c->nlocal > 1 || nctas > 1) e = cudaLaunchCooperativeKernel((const void*)fn, grid, block, args, 0, stream);
+  else e = cudaLaunchKernel((const void*)fn, grid, block, args, 0, stream);
+  if (e != cudaSuccess) {
+    c->last_error = std::string("interp launch failed: ") + cudaGetErrorString(e);
+    return CHB_ERR_CUDA;
+  }
+  return CHB_SUCCESS;
+}
+
+}  // extern "C"

@@ -1,0 +1,224 @@
+// One-shot collectives for latency-bound sizes: every rank pushes its data
+// straight into the peers' inboxes as 16-byte lines {data, flag, data, flag}
+// and every rank polls its own (local) inbox, so a whole allreduce /
+// reduce-scatter / allgather costs one launch and one NVLink traversal, with
+// no barrier at all.  The flag is the launch sequence number, never reset;
+// two inbox halves alternate by launch parity, which is enough because a rank
+// can run at most one launch ahead of the slowest peer (it needs that peer's
+// lines of the current launch to finish it).
+//
+// This is the large-radix / single-round end of the design space the
+// reference explores with k >= b (one phase, every peer at once:
+// testing/custom_implementations/work_dir/all_reduce/all_reduce_radix_batch.cpp:339-368
+// with nphases == 1), taken to its limit on a full-bandwidth switch.
+// Sums run in rank order 0..P-1 on every rank, so all ranks obtain
+// bit-identical results.
+#include <cstdio>
+
+#include "../api/chb.h"
+#include "../symm/comm.h"
+#include "common.cuh"
+
+namespace chb {
+
+constexpr int kLLThreads = 512;
+enum { LL_AR = 0, LL_RS = 1, LL_AG = 2 };
+
+struct LLIo {
+  const char* in[kMaxRanks];
+  char* out[kMaxRanks];
+};
+
+__device__ __forceinline__ void st_line(char* p, unsigned d0, unsigned d1, unsigned flag) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(d0), "r"(flag), "r"(d1), "r"(flag) : "memory");
+}
+__device__ __forceinline__ void ld_line(const char* p, unsigned& d0, unsigned& f0, unsigned& d1, unsigned& f1) {
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(d0), "=r"(f0), "=r"(d1), "=r"(f1) : "l"(p) : "memory");
+}
+
+// 8 payload bytes starting at byte offset `off` of a block of `nbytes` bytes
+// (shorter at the tail; missing bytes read as zero).
+__device__ __forceinline__ uint2 load_payload(const char* base, long long off, long long nbytes) {
+  uint2 v = make_uint2(0u, 0u);
+  if (off + 8 <= nbytes && ((reinterpret_cast<unsigned long long>(base + off) & 7ull) == 0ull)) {
+    v = *reinterpret_cast<const uint2*>(base + off);
+  } else {
+    unsigned char* b = reinterpret_cast<unsigned char*>(&v);
+    for (int i = 0; i < 8 && off + i < nbytes; ++i) b[i] = (unsigned char)base[off + i];
+  }
+  return v;
+}
+__device__ __forceinline__ void store_payload(char* base, long long off, long long nbytes, uint2 v) {
+  if (off + 8 <= nbytes && ((reinterpret_cast<unsigned long long>(base + off) & 7ull) == 0ull)) {
+    *reinterpret_cast<uint2*>(base + off) = v;
+  } else {
+    const unsigned char* b = reinterpret_cast<const unsigned char*>(&v);
+    for (int i = 0; i < 8 && off + i < nbytes; ++i) base[off + i] = (char)b[i];
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void payload_to_acc(uint2 v, typename Elem<T>::Acc* a) {
+  const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+  for (int i = 0; i < (int)(8 / sizeof(T)); ++i) a[i] = Elem<T>::up(e[i]);
+}
+template <typename T>
+__device__ __forceinline__ void payload_combine(int op, uint2 v, typename Elem<T>::Acc* a) {
+  const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+  for (int i = 0; i < (int)(8 / sizeof(T)); ++i) a[i] = combine<typename Elem<T>::Acc>(op, a[i], Elem<T>::up(e[i]));
+}
+template <typename T>
+__device__ __forceinline__ uint2 acc_to_payload(typename Elem<T>::Acc* a, float scale, bool do_scale) {
+  uint2 v;
+  T* e = reinterpret_cast<T*>(&v);
+#pragma unroll
+  for (int i = 0; i < (int)(8 / sizeof(T)); ++i) {
+    typename Elem<T>::Acc x = a[i];
+    if (do_scale) x = (typename Elem<T>::Acc)(x * scale);
+    e[i] = Elem<T>::down(x);
+  }
+  return v;
+}
+
+// nbytes: payload bytes each rank sends to one peer (AR: whole vector; RS / AG: one block)
+template <typename T, int MODE>
+__global__ void __launch_bounds__(kLLThreads, 1)
+ll_kernel(World w, LLIo io, long long nbytes, int op, float scale, long long lines_per_src) {
+  using Acc = typename Elem<T>::Acc;
+  const int rank = w.rank0 + (int)blockIdx.y;
+  const int P = w.P;
+  const unsigned nct = gridDim.x;
+  Ctrl* c = w.ctrl[rank];
+  __shared__ unsigned long long s_seq;
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) { s_seq = ld_volatile_u64(&c->ll_seq); s_abort = ld_volatile_u32(&c->abort); }
+  __syncthreads();
+  const unsigned long long seq = s_seq;
+  const bool dead = s_abort != 0;
+  const unsigned flag = (unsigned)(seq % 0xFFFFFFFFull) + 1u;
+  const long long half = (long long)(seq & 1ull) * P;
+  const long long nlines = (nbytes + 7) / 8;
+  const long long TT = (long long)nct * blockDim.x;
+  const char* in = io.in[rank];
+  char* out = io.out[rank];
+  const bool do_scale = scale != 1.0f;
+
+  const long long l0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  // ---- push all my lines to every peer first, so that they travel together
+  for (long long l = l0; l < nlines && !dead; l += TT) {
+    uint2 mine = make_uint2(0u, 0u);
+    if (MODE != LL_RS) mine = load_payload(in, l * 8, nbytes);
+    for (int i = 1; i < P; ++i) {
+      const int p = (rank + i) % P;
+      uint2 v = (MODE == LL_RS) ? load_payload(in + (long long)p * nbytes, l * 8, nbytes) : mine;
+      st_line(w.ll[p] + ((half + rank) * lines_per_src + l) * 16, v.x, v.y, flag);
+    }
+  }
+  // ---- collect the peers' lines from my inbox, combining in rank order
+  for (long long l = l0; l < nlines && !dead; l += TT) {
+    const uint2 mine = load_payload(in + (MODE == LL_RS ? (long long)rank * nbytes : 0ll), l * 8, nbytes);
+    Acc a[8 / sizeof(T)];
+    bool have = false, failed = false;
+    for (int p = 0; p < P; ++p) {
+      uint2 v;
+      if (p == rank) {
+        v = mine;
+      } else {
+        const char* line = w.ll[rank] + ((half + p) * lines_per_src + l) * 16;
+        unsigned d0, f0, d1, f1;
+        ld_line(line, d0, f0, d1, f1);
+        if (f0 != flag || f1 != flag) {
+          const unsigned long long t0 = globaltimer_ns();
+          unsigned spins = 0;
+          for (;;) {
+            ld_line(line, d0, f0, d1, f1);
+            if (f0 == flag && f1 == flag) break;
+            if ((++spins & 31u) == 0u) {
+              if (ld_volatile_u32(&c->abort)) { failed = true; break; }
+              if (globaltimer_ns() - t0 > w.timeout_ns) {
+                record_timeout(c, ST_TIMEOUT_LL, rank, (int)l, p, flag, f0);
+                failed = true;
+                break;
+              }
+            }
+          }
+        }
+        if (failed) break;
+        v = make_uint2(d0, d1);
+      }
+      if (MODE == LL_AG) {
+        store_payload(out + (long long)p * nbytes, l * 8, nbytes, v);
+      } else {
+        if (!have) { payload_to_acc<T>(v, a); have = true; }
+        else payload_combine<T>(op, v, a);
+      }
+    }
+    if (failed) break;
+    if (MODE != LL_AG) store_payload(out, l * 8, nbytes, acc_to_payload<T>(a, scale, do_scale));
+  }
+  rank_exit(c, nct, [&](Ctrl* cc) { cc->ll_seq = seq + 1ull; });
+}
+
+typedef void (*LLFn)(World, LLIo, long long, int, float, long long);
+
+template <int MODE>
+static LLFn pick_ll(int dtype) {
+  switch (dtype) {
+    case DT_F32: return ll_kernel<float, MODE>;
+    case DT_BF16: return ll_kernel<__nv_bfloat16, MODE>;
+    case DT_F16: return ll_kernel<__half, MODE>;
+    case DT_I32: return ll_kernel<int32_t, MODE>;
+    case DT_F64: return ll_kernel<double, MODE>;
+    case DT_I64: return ll_kernel<int64_t, MODE>;
+    case DT_U8: return ll_kernel<uint8_t, MODE>;
+  }
+  return nullptr;
+}
+
+}  // namespace chb
+
+using namespace chb;
+
+extern "C" {
+
+// Largest payload (bytes per rank pair) the inbox can take.
+long long chb_ll_max_bytes(const chb_comm* c) { return c ? (long long)c->ll_lines_per_src * 8 : 0; }
+
+// mode: 0 allreduce (count = vector length), 1 reduce-scatter (count = elements
+// per rank; in holds P*count), 2 allgather (count = elements per rank; out holds P*count).
+// in / out: one pointer per local rank, 8-byte aligned.
+int chb_ll_collective(chb_comm* c, int mode, int dtype, int op, const void* const* in, void* const* out,
+                      long long count, float scale, int nctas, cudaStream_t stream) {
+  if (!c || !in || !out || count < 0) return CHB_ERR_ARG;
+  const long long nbytes = count * (long long)dtype_size(dtype);
+  if (nbytes > chb_ll_max_bytes(c)) { c->last_error = "message exceeds the flagged-line inbox"; return CHB_ERR_COUNT; }
+  LLFn fn = mode == LL_AR ? pick_ll<LL_AR>(dtype) : mode == LL_RS ? pick_ll<LL_RS>(dtype) : mode == LL_AG ? pick_ll<LL_AG>(dtype) : nullptr;
+  if (!fn) return CHB_ERR_ARG;
+  LLIo io{};
+  for (int l = 0; l < c->nlocal; ++l) {
+    if ((((uintptr_t)in[l]) | ((uintptr_t)out[l])) & 7u) { c->last_error = "flagged-line path needs 8-byte aligned buffers"; return CHB_ERR_ARG; }
+    io.in[c->rank + l] = (const char*)in[l];
+    io.out[c->rank + l] = (char*)out[l];
+  }
+  if (nbytes == 0) return CHB_SUCCESS;
+  const long long nlines = (nbytes + 7) / 8;
+  int budget = c->max_ctas / (c->nlocal > 0 ? c->nlocal : 1);
+  if (budget < 1) budget = 1;
+  if (nctas <= 0) nctas = (int)((nlines + kLLThreads - 1) / kLLThreads);
+  if (nctas > 16) nctas = 16;
+  if (nctas > budget) nctas = budget;
+  if (nctas < 1) nctas = 1;
+  dim3 grid((unsigned)nctas, (unsigned)c->nlocal, 1), block(kLLThreads, 1, 1);
+  World w = c->world;
+  long long lps = (long long)c->ll_lines_per_src;
+  void* args[] = {&w, &io, (void*)&nbytes, &op, &scale, &lps};
+  cudaError_t e;
+  if (c->nlocal > 1) e = cudaLaunchCooperativeKernel((const void*)fn, grid, block, args, 0, stream);
+  else e = cudaLaunchKernel((const void*)fn, grid, block, args, 0, stream);
+  if (e != cudaSuccess) { c->last_error = std::string("ll launch failed: ") + cudaGetErrorString(e); return CHB_ERR_CUDA; }
+  return CHB_SUCCESS;
+}
+
+}  // extern "C"

@@ -111,7 +111,7 @@ Program Builder::lower(const LowerOpts& o) const {
       }
   p.reads_peer_in = rin;
   p.reads_peer_out = rout;
-  const bool stage_in = (rin && !o.in_symmetric);
+  const bool stage_in = (rin && !o.in_symmetric) || o.in_place;
   const bool stage_out = rout && !o.out_symmetric;
 
   // ---- 2. scratch layout -------------------------------------------------------
@@ -132,6 +132,7 @@ Program Builder::lower(const LowerOpts& o) const {
   ops.reserve(ops_.size() + 2 * P_);
   if (stage_in)
     for (int r = 0; r < P_; ++r) {
+      if (o.in_place) { in_lo[r] = 0; in_hi[r] = in_elems_; }
       if (in_hi[r] < 0) continue;
       Op s;
       s.rank = r;
@@ -156,7 +157,7 @@ Program Builder::lower(const LowerOpts& o) const {
     }
     for (Src& s : q.srcs) {
       if (s.buf == L_IN) {
-        if (stage_in && s.peer != l.rank) { s.buf = P_WORK; s.off += ins_off; }
+        if (stage_in && (s.peer != l.rank || o.in_place)) { s.buf = P_WORK; s.off += ins_off; }
         else s.buf = P_IN;
       } else if (s.buf == L_OUT) {
         if (stage_out) { s.buf = P_WORK; s.off += outs_off; }

@@ -27,6 +27,8 @@
 #include <string>
 #include <vector>
 
+#include "types.h"
+
 namespace chb {
 
 enum LogicalBuf : int32_t { L_IN = 0, L_OUT = 1, L_TMP0 = 2 };
@@ -92,6 +94,7 @@ struct LowerOpts {
   bool in_symmetric = false;    // peers may read the caller's input buffer
   bool out_symmetric = false;   // peers may read the caller's output buffer
   bool global_rounds = false;   // every wait becomes "all ranks" (debug aid)
+  bool in_place = false;        // input and output alias: every read of IN goes through a scratch copy
 };
 
 class Builder {
@@ -121,9 +124,6 @@ class Builder {
 };
 
 // ---- reduction / element types shared by simulator, C API and kernels ----
-enum DType : int32_t { DT_F32 = 0, DT_BF16 = 1, DT_F16 = 2, DT_I32 = 3, DT_F64 = 4, DT_I64 = 5, DT_U8 = 6 };
-enum RedOp : int32_t { OP_SUM = 0, OP_MAX = 1, OP_MIN = 2, OP_PROD = 3 };
-int dtype_size(int dt);
 
 // Run a lowered program on host memory for all P ranks in one process.
 // in[r] / out[r] point at rank r's buffers.  Ranks advance one round at a

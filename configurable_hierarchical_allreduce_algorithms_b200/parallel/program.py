@@ -54,11 +54,11 @@ class Step:
 
 class Program:
     def __init__(self, coll: str, algo: str, P: int, count: int, k: int = 2, b: int = 1, aux: int = 0,
-                 in_symmetric: bool = False, out_symmetric: bool = False):
+                 in_symmetric: bool = False, out_symmetric: bool = False, in_place: bool = False):
         L = N.lib()
         err = C.create_string_buffer(512)
         h = L.chb_program_create(coll.encode(), algo.encode(), P, k, b, count, aux,
-                                 int(in_symmetric), int(out_symmetric), err, len(err))
+                                 int(in_symmetric) | (2 if in_place else 0), int(out_symmetric), err, len(err))
         if not h:
             raise ProgramError(err.value.decode() or "program creation failed")
         self._h = h
@@ -69,7 +69,7 @@ class Program:
          self.remote_msgs, self.remote_elems, self.max_rank_remote_elems, self.local_elems,
          self.max_nsrc, rpi, rpo, self.nsrcs, self.nwaits, self.nexit_waits, self.nsignals) = [int(x) for x in info[:17]]
         self.reads_peer_in, self.reads_peer_out = bool(rpi), bool(rpo)
-        self.in_symmetric, self.out_symmetric = in_symmetric, out_symmetric
+        self.in_symmetric, self.out_symmetric, self.in_place = in_symmetric, out_symmetric, in_place
         self.name = L.chb_program_name(h).decode()
         self._tables = None
 
@@ -138,5 +138,5 @@ class Program:
 
 @lru_cache(maxsize=512)
 def cached_program(coll: str, algo: str, P: int, count: int, k: int = 2, b: int = 1, aux: int = 0,
-                   in_symmetric: bool = False, out_symmetric: bool = False) -> Program:
-    return Program(coll, algo, P, count, k, b, aux, in_symmetric, out_symmetric)
+                   in_symmetric: bool = False, out_symmetric: bool = False, in_place: bool = False) -> Program:
+    return Program(coll, algo, P, count, k, b, aux, in_symmetric, out_symmetric, in_place)

@@ -1,0 +1,253 @@
+"""Kernels on a real GPU with all ranks emulated on that one device.
+
+Each kernel is compared against a plain PyTorch fp32 / fp64 reference of the
+same collective.  The emulated world runs the same kernels as a multi-GPU
+world: the peers' heaps are slices of one allocation and one cooperative
+launch executes all ranks.
+"""
+import pytest
+import torch
+
+import configurable_hierarchical_allreduce_algorithms_b200 as chb
+from configurable_hierarchical_allreduce_algorithms_b200.parallel.comm import Communicator
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def comms(cuda):
+    made = {}
+
+    def get(P):
+        if P not in made:
+            made[P] = Communicator.emulated(P, scratch_bytes=96 << 20, user_bytes=32 << 20)
+        return made[P]
+
+    yield get
+    for c in made.values():
+        c.close()
+
+
+def make_inputs(P, n, dtype, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    if dtype in (torch.int32, torch.int64):
+        return [torch.randint(-50, 50, (n,), generator=g, device="cuda", dtype=dtype) for _ in range(P)]
+    if dtype == torch.uint8:
+        return [torch.randint(0, 8, (n,), generator=g, device="cuda", dtype=torch.int32).to(dtype) for _ in range(P)]
+    return [(torch.rand(n, generator=g, device="cuda", dtype=torch.float32) * 2 - 1).to(dtype) for _ in range(P)]
+
+
+def ref_reduce(ins, op):
+    hi = torch.float64 if ins[0].dtype.is_floating_point else torch.int64
+    st = torch.stack([x.to(hi) for x in ins])
+    return {"sum": st.sum(0), "max": st.max(0).values, "min": st.min(0).values}[op]
+
+
+def check(out, exp, dtype, P):
+    if dtype.is_floating_point:
+        tol = {torch.float32: 1e-5, torch.float64: 1e-12, torch.bfloat16: 2e-2, torch.float16: 2e-3}[dtype]
+        torch.testing.assert_close(out.to(torch.float64), exp.to(torch.float64), rtol=tol, atol=tol * P)
+    else:
+        assert torch.equal(out.to(torch.int64), exp.to(torch.int64))
+
+
+AR_CASES = [("radix_batch", 2, 1), ("radix_batch", 2, 2), ("radix_batch", 4, 4), ("radix_batch", 2, 8),
+            ("radix_batch", 8, 8), ("radix_batch", 3, 4), ("ring", 2, 1), ("recursive_doubling", 2, 1),
+            ("reduce_scatter_allgather", 2, 1), ("k_reduce_scatter_allgather", 4, 1),
+            ("recursive_multiplying", 3, 1), ("recursive_exchange", 4, 1), ("inter_reduce_exchange_bcast", 2, 2),
+            ("semi_radix_batch", 2, 2), ("custom", 2, 2)]
+
+
+@pytest.mark.parametrize("algo,k,b", AR_CASES)
+def test_allreduce_programs(comms, algo, k, b):
+    P = 8
+    comm = comms(P)
+    if P % b:
+        pytest.skip("b must divide P")
+    for dtype, n in ((torch.float32, 8 * 1024), (torch.bfloat16, 8 * 33), (torch.int32, 8 * 3), (torch.float32, 8)):
+        ins = make_inputs(P, n, dtype)
+        outs = chb.all_reduce(comm, ins, algo=algo, k=k, b=b)
+        exp = ref_reduce(ins, "sum")
+        for r in range(P):
+            check(outs[r], exp, dtype, P)
+    comm.check()
+
+
+@pytest.mark.parametrize("P", [2, 3, 4, 6, 8])
+def test_three_collectives_radix_batch(comms, P):
+    comm = comms(P)
+    for b in [d for d in (1, 2, 3, 4, 8) if P % d == 0]:
+        for k in (2, 4):
+            for n in (1, 3, 31, 127, 2048):
+                ins = make_inputs(P, n * P, torch.float32, seed=n)
+                exp = ref_reduce(ins, "sum")
+                outs = chb.all_reduce(comm, ins, algo="radix_batch", k=k, b=b)
+                for r in range(P):
+                    check(outs[r], exp, torch.float32, P)
+                outs = chb.reduce_scatter(comm, ins, algo="radix_batch", k=k, b=b)
+                for r in range(P):
+                    check(outs[r], exp[r * n:(r + 1) * n], torch.float32, P)
+                blocks = [x[:n].contiguous() for x in ins]
+                outs = chb.all_gather(comm, blocks, algo="radix_batch", k=k, b=b)
+                cat = torch.cat(blocks)
+                for r in range(P):
+                    assert torch.equal(outs[r], cat)
+    comm.check()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.int32, torch.float64, torch.int64])
+@pytest.mark.parametrize("op", ["sum", "max", "min"])
+def test_dtypes_ops(comms, dtype, op):
+    P = 4
+    comm = comms(P)
+    for n in (4, 1000):
+        ins = make_inputs(P, n * P, dtype)
+        exp = ref_reduce(ins, op)
+        for algo, k, b in (("radix_batch", 2, 2), ("ll", 2, 1)):
+            outs = chb.all_reduce(comm, ins, op=op, algo=algo, k=k, b=b)
+            for r in range(P):
+                check(outs[r], exp, dtype, P)
+    comm.check()
+
+
+@pytest.mark.parametrize("algo", ["pairwise", "ring", "recursive_halving", "recursive_doubling", "radix", "radix_block"])
+def test_reduce_scatter_baselines(comms, algo):
+    for P in (4, 6, 8):
+        comm = comms(P)
+        n = 257
+        ins = make_inputs(P, n * P, torch.float32)
+        exp = ref_reduce(ins, "sum")
+        outs = chb.reduce_scatter(comm, ins, algo=algo, k=3, b=2)
+        for r in range(P):
+            check(outs[r], exp[r * n:(r + 1) * n], torch.float32, P)
+        comm.check()
+
+
+@pytest.mark.parametrize("algo", ["k_brucks", "ring", "recursive_doubling", "linear"])
+def test_allgather_baselines(comms, algo):
+    for P in (4, 8):
+        comm = comms(P)
+        blocks = make_inputs(P, 1001, torch.bfloat16)
+        outs = chb.all_gather(comm, blocks, algo=algo, k=3)
+        cat = torch.cat(blocks)
+        for r in range(P):
+            assert torch.equal(outs[r], cat)
+        comm.check()
+
+
+def test_all_to_all_and_gather(comms):
+    P = 8
+    comm = comms(P)
+    n = 100
+    ins = make_inputs(P, n * P, torch.float32)
+    for algo, k, b in (("tuna", 2, 1), ("tuna", 3, 2), ("linear", 2, 1)):
+        outs = chb.all_to_all(comm, ins, algo=algo, k=k, b=b)
+        for r in range(P):
+            exp = torch.cat([ins[s][r * n:(r + 1) * n] for s in range(P)])
+            assert torch.equal(outs[r], exp)
+    blocks = [x[:n].contiguous() for x in ins]
+    outs = chb.gather(comm, blocks, root=5, k=3)
+    assert torch.equal(outs[5], torch.cat(blocks))
+    comm.check()
+
+
+@pytest.mark.parametrize("P", [2, 4, 8])
+def test_flagged_line_kernels(comms, P):
+    comm = comms(P)
+    for dtype in (torch.float32, torch.bfloat16):
+        for n in (1, 2, 3, 7, 64, 1000, 8192):
+            ins = make_inputs(P, n * P, dtype, seed=n)
+            exp = ref_reduce(ins, "sum")
+            outs = chb.all_reduce(comm, ins, algo="ll")
+            for r in range(P):
+                check(outs[r], exp, dtype, P)
+            # bit-identical on every rank: all ranks add in rank order
+            for r in range(1, P):
+                assert torch.equal(outs[r], outs[0])
+            outs = chb.reduce_scatter(comm, ins, algo="ll")
+            for r in range(P):
+                check(outs[r], exp[r * n:(r + 1) * n], dtype, P)
+            blocks = [x[:n].contiguous() for x in ins]
+            outs = chb.all_gather(comm, blocks, algo="ll")
+            for r in range(P):
+                assert torch.equal(outs[r], torch.cat(blocks))
+    # back-to-back launches reuse the two inbox halves
+    ins = make_inputs(P, 512, torch.float32)
+    exp = ref_reduce(ins, "sum")
+    for _ in range(7):
+        outs = chb.all_reduce(comm, ins, algo="ll")
+    for r in range(P):
+        check(outs[r], exp, torch.float32, P)
+    comm.check()
+
+
+def test_large_multi_cta_and_scale(comms):
+    P = 4
+    comm = comms(P)
+    n = (4 << 20) // 4 + 13  # 4 MiB per rank plus an odd tail
+    ins = make_inputs(P, n * P, torch.float32)
+    exp = ref_reduce(ins, "sum")
+    for nctas in (1, 4, 16):
+        outs = chb.all_reduce(comm, ins, algo="radix_batch", k=2, b=1, nctas=nctas, scale=0.25)
+        for r in range(P):
+            check(outs[r], exp * 0.25, torch.float32, P)
+        outs = chb.all_reduce(comm, ins, algo="radix_batch", k=2, b=2, nctas=nctas)
+        for r in range(P):
+            check(outs[r], exp, torch.float32, P)
+    comm.check()
+
+
+def test_symmetric_buffers_zero_copy(comms):
+    P = 4
+    comm = comms(P)
+    n = 4096
+    xs = comm.empty(n * P, torch.float32)
+    ys = comm.empty(n * P, torch.float32)
+    src = make_inputs(P, n * P, torch.float32)
+    for x, s in zip(xs, src):
+        x.copy_(s)
+    exp = ref_reduce(src, "sum")
+    prog = comm.program("allreduce", "radix_batch", n * P, 2, 1, 0, True, True)
+    assert prog.work_elems == 0
+    chb.all_reduce(comm, xs, out=ys, algo="radix_batch", k=2, b=1)
+    for r in range(P):
+        check(ys[r], exp, torch.float32, P)
+    # in place on symmetric buffers goes through the staged lowering
+    chb.all_reduce(comm, xs, out=xs, algo="radix_batch", k=2, b=2)
+    for r in range(P):
+        check(xs[r], exp, torch.float32, P)
+    comm.check()
+
+
+def test_auto_choice_and_reference_signatures(comms):
+    P = 8
+    comm = comms(P)
+    for n in (8, 4096, 1 << 18):
+        ins = make_inputs(P, n, torch.float32)
+        exp = ref_reduce(ins, "sum")
+        outs = chb.all_reduce(comm, ins)
+        for r in range(P):
+            check(outs[r], exp, torch.float32, P)
+    n = 64
+    send = make_inputs(P, n * P, torch.int32)
+    recv = [torch.zeros(n * P, dtype=torch.int32, device="cuda") for _ in range(P)]
+    assert chb.all_reduce_radix_batch(send, recv, n * P, "sum", comm, 2, 4) == 0
+    assert torch.equal(recv[3], ref_reduce(send, "sum").to(torch.int32))
+    out = [torch.zeros(n, dtype=torch.int32, device="cuda") for _ in range(P)]
+    assert chb.reduce_scatter_radix_batch(send, out, n, "sum", comm, 2, 2) == 0
+    assert torch.equal(out[2], ref_reduce(send, "sum").to(torch.int32)[2 * n:3 * n])
+    small = [s[:n].contiguous() for s in send]
+    assert chb.allgather_radix_batch(small, n, recv, comm, 4, 8) == 0
+    assert torch.equal(recv[7], torch.cat(small))
+    # wrong group size and wrong count come back as error codes, like MPI_ERR_*
+    assert chb.all_reduce_radix_batch(send, recv, n * P, "sum", comm, 2, 3) != 0
+    assert chb.all_reduce_radix_batch(send, recv, n * P - 1, "sum", comm, 2, 2) != 0
+    comm.check()
+
+
+def test_barrier(comms):
+    comm = comms(8)
+    for _ in range(3):
+        comm.barrier()
+    comm.check()
+    assert comm.status(0)["code"] == 0

@@ -1,0 +1,204 @@
+// One-call collectives on a communicator (program cache + dispatch to the
+// interpreter, flagged-line or multimem kernels) and the reference-compatible
+// entry points declared in chb_compat.h.
+#include <cstring>
+#include <map>
+#include <string>
+#include <tuple>
+
+#include "../sched/algos.h"
+#include "../symm/comm.h"
+#include "chb.h"
+#include "chb_compat.h"
+#include "program_handle.h"
+
+extern "C" {
+int chb_run_program(chb_comm* c, const chb_program* p, int dtype, int op, const void* const* in,
+                    void* const* out, float scale, int nctas, cudaStream_t stream);
+int chb_ll_collective(chb_comm* c, int mode, int dtype, int op, const void* const* in, void* const* out,
+                      long long count, float scale, int nctas, cudaStream_t stream);
+long long chb_ll_max_bytes(const chb_comm* c);
+int chb_nvls_collective(chb_comm* c, int mode, int dtype, const void* in, void* out, long long count,
+                        float scale, int nctas, cudaStream_t stream);
+}
+
+namespace {
+
+using Key = std::tuple<int, std::string, int, int, int, int64_t, int>;
+struct Cache {
+  std::map<Key, chb_program*> progs;
+  ~Cache() { for (auto& kv : progs) delete kv.second; }
+};
+// one cache per communicator, owned here so that comm.h stays free of it
+std::map<chb_comm*, Cache>& caches() {
+  static std::map<chb_comm*, Cache> m;
+  return m;
+}
+
+const char* coll_name(int coll) {
+  switch (coll) {
+    case CHB_ALLREDUCE: return "allreduce";
+    case CHB_REDUCE_SCATTER: return "reduce_scatter";
+    case CHB_ALLGATHER: return "allgather";
+    case CHB_ALLTOALL: return "alltoall";
+    case CHB_GATHER: return "gather";
+  }
+  return "";
+}
+
+bool all_symmetric(const chb_comm* c, const void* const* ptrs) {
+  for (int l = 0; l < c->nlocal; ++l) {
+    const char* p = (const char*)ptrs[l];
+    const char* u = c->user_ptr(c->rank + l);
+    if (p < u || p >= u + c->user_bytes) return false;
+  }
+  return true;
+}
+
+int get_program(chb_comm* c, int coll, const char* algo, int k, int b, int aux, int64_t count, int flags,
+                chb_program** out) {
+  Key key(coll, algo, k, b, aux, count, flags);
+  Cache& ca = caches()[c];
+  auto it = ca.progs.find(key);
+  if (it != ca.progs.end()) { *out = it->second; return CHB_SUCCESS; }
+  try {
+    chb::AlgoSpec s;
+    s.coll = coll_name(coll);
+    s.algo = algo;
+    s.P = c->P;
+    s.k = k;
+    s.b = b;
+    s.count = count;
+    s.aux = aux;
+    chb::Builder B = chb::build_algorithm(s);
+    chb::LowerOpts o;
+    o.in_symmetric = (flags & 1) != 0;
+    o.out_symmetric = (flags & 2) != 0;
+    o.in_place = (flags & 4) != 0;
+    auto* p = new chb_program;
+    p->prog = B.lower(o);
+    ca.progs[key] = p;
+    *out = p;
+    return CHB_SUCCESS;
+  } catch (const std::exception& e) {
+    c->last_error = e.what();
+    return c->last_error.find("count") != std::string::npos ? CHB_ERR_COUNT : CHB_ERR_ARG;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+void chb_collective_cache_clear(chb_comm* c) { caches().erase(c); }
+
+// Generic entry: in / out hold one pointer per local rank.  algo is a step
+// program name (chb_list_algorithms), "ll" or "nvls".  count as in chb.h.
+int chb_collective(chb_comm* c, int coll, const char* algo, int k, int b, int aux, int dtype, int op,
+                   const void* const* in, void* const* out, int64_t count, float scale, int nctas,
+                   cudaStream_t stream) {
+  if (!c || !algo || !in || !out) return CHB_ERR_ARG;
+  if (!std::strcmp(algo, "ll")) {
+    int mode = coll == CHB_ALLREDUCE ? 0 : coll == CHB_REDUCE_SCATTER ? 1 : coll == CHB_ALLGATHER ? 2 : -1;
+    if (mode < 0) return CHB_ERR_UNSUPPORTED;
+    return chb_ll_collective(c, mode, dtype, op, in, out, count, scale, nctas, stream);
+  }
+  if (!std::strncmp(algo, "nvls", 4)) {
+    if (op != CHB_SUM) return CHB_ERR_OP;
+    int mode = coll == CHB_ALLREDUCE ? (!std::strcmp(algo, "nvls1") ? 3 : 0) : coll == CHB_REDUCE_SCATTER ? 1
+             : coll == CHB_ALLGATHER ? 2 : -1;
+    if (mode < 0) return CHB_ERR_UNSUPPORTED;
+    return chb_nvls_collective(c, mode, dtype, in[0], out[0], count, scale, nctas, stream);
+  }
+  bool in_place = false;
+  for (int l = 0; l < c->nlocal; ++l) in_place |= (in[l] == out[l]);
+  int flags = 0;
+  if (in_place) flags = 4;
+  else flags = (all_symmetric(c, in) ? 1 : 0) | (all_symmetric(c, (const void* const*)out) ? 2 : 0);
+  chb_program* p = nullptr;
+  int rc = get_program(c, coll, algo, k, b, aux, count, flags, &p);
+  if (rc) return rc;
+  return chb_run_program(c, p, dtype, op, in, out, scale, nctas, stream);
+}
+
+// ---------------------------------------------------------------- reference-compatible calls
+static cudaStream_t g_compat_stream = nullptr;
+void chb_set_stream(cudaStream_t s) { g_compat_stream = s; }
+
+static int one(CHB_Comm comm, int coll, const char* algo, const void* sendbuf, void* recvbuf, int64_t count,
+               CHB_Datatype dt, CHB_Op op, int k, int b, int aux) {
+  if (!comm) return CHB_ERR_ARG;
+  if (comm->nlocal != 1) { comm->last_error = "reference-compatible calls need one rank per process"; return CHB_ERR_ARG; }
+  const void* in = (sendbuf == CHB_IN_PLACE) ? recvbuf : sendbuf;
+  return chb_collective(comm, coll, algo, k, b, aux, dt, op, &in, &recvbuf, count, 1.0f, 0, g_compat_stream);
+}
+
+int allgather_radix_batch(char* sendbuf, int sendcount, CHB_Datatype datatype, char* recvbuf, CHB_Comm comm, int k, int b) {
+  return one(comm, CHB_ALLGATHER, "radix_batch", sendbuf, recvbuf, sendcount, datatype, CHB_SUM, k, b, 0);
+}
+int reduce_scatter_radix_batch(const void* sendbuf, void* recvbuf, int64_t recvcount, CHB_Datatype datatype, CHB_Op op,
+                               CHB_Comm comm, int k, int b) {
+  if (sendbuf == CHB_IN_PLACE) {
+    // in place: recvbuf holds the P*recvcount inputs and receives the result at its start
+    return one(comm, CHB_REDUCE_SCATTER, "radix_batch", CHB_IN_PLACE, recvbuf, recvcount, datatype, op, k, b, 0);
+  }
+  return one(comm, CHB_REDUCE_SCATTER, "radix_batch", sendbuf, recvbuf, recvcount, datatype, op, k, b, 0);
+}
+int all_reduce_radix_batch(char* sendbuf, char* recvbuf, int count, CHB_Datatype datatype, CHB_Op op, CHB_Comm comm, int k, int b) {
+  return one(comm, CHB_ALLREDUCE, "radix_batch", sendbuf, recvbuf, count, datatype, op, k, b, 0);
+}
+int all_reduce_semi_radix_batch(char* sendbuf, char* recvbuf, int count, CHB_Datatype datatype, CHB_Op op, CHB_Comm comm, int k, int b) {
+  return one(comm, CHB_ALLREDUCE, "semi_radix_batch", sendbuf, recvbuf, count, datatype, op, k, b, 0);
+}
+int reduce_scatter_radix_block(char* sendbuf, char* recvbuf, int count, CHB_Datatype datatype, CHB_Op op, CHB_Comm comm, int r, int b) {
+  return one(comm, CHB_REDUCE_SCATTER, "radix_block", sendbuf, recvbuf, count, datatype, op, r, b, 0);
+}
+int allgather_k_brucks(char* sendbuf, int sendcount, CHB_Datatype datatype, char* recvbuf, CHB_Comm comm, int k) {
+  return one(comm, CHB_ALLGATHER, "k_brucks", sendbuf, recvbuf, sendcount, datatype, CHB_SUM, k, 1, 0);
+}
+int gather_k_nomial(char* sendbuf, int sendcount, CHB_Datatype datatype, char* recvbuf, CHB_Comm comm, int k, int root) {
+  return one(comm, CHB_GATHER, "k_nomial", sendbuf, recvbuf, sendcount, datatype, CHB_SUM, k, 1, root);
+}
+
+#define CHB_AR0(NAME, ALGO)                                                                                   \
+  int NAME(const char* sendbuf, char* recvbuf, int count, CHB_Datatype datatype, CHB_Op op, CHB_Comm comm) {  \
+    return one(comm, CHB_ALLREDUCE, ALGO, sendbuf, recvbuf, count, datatype, op, 2, 1, 0);                    \
+  }
+CHB_AR0(MPICH_Allreduce_recursive_doubling, "recursive_doubling")
+CHB_AR0(MPICH_Allreduce_ring, "ring")
+CHB_AR0(MPICH_Allreduce_reduce_scatter_allgather, "reduce_scatter_allgather")
+#undef CHB_AR0
+int MPICH_Allreduce_recursive_multiplying(const char* sendbuf, char* recvbuf, int count, CHB_Datatype datatype, CHB_Op op,
+                                          CHB_Comm comm, int k) {
+  return one(comm, CHB_ALLREDUCE, "recursive_multiplying", sendbuf, recvbuf, count, datatype, op, k, 1, 0);
+}
+int MPICH_Allreduce_k_reduce_scatter_allgather(const char* sendbuf, char* recvbuf, int count, CHB_Datatype datatype, CHB_Op op,
+                                               CHB_Comm comm, int k, int single_phase_recv) {
+  // single_phase_recv selects how many receive phases are pre-posted in the
+  // two-sided original; a pull schedule has no receives to post, so it is accepted and ignored
+  (void)single_phase_recv;
+  return one(comm, CHB_ALLREDUCE, "k_reduce_scatter_allgather", sendbuf, recvbuf, count, datatype, op, k, 1, 0);
+}
+int MPICH_Allreduce_recursive_exchange(const char* sendbuf, char* recvbuf, int count, CHB_Datatype datatype, CHB_Op op,
+                                       CHB_Comm comm, int k, int single_phase_recv) {
+  (void)single_phase_recv;
+  return one(comm, CHB_ALLREDUCE, "recursive_exchange", sendbuf, recvbuf, count, datatype, op, k, 1, 0);
+}
+int MPICH_Allreduce_inter_reduce_exchange_bcast(const char* sendbuf, char* recvbuf, int count, CHB_Datatype datatype, CHB_Op op,
+                                                CHB_Comm comm, int ranks_per_node) {
+  return one(comm, CHB_ALLREDUCE, "inter_reduce_exchange_bcast", sendbuf, recvbuf, count, datatype, op, 2, 1, ranks_per_node);
+}
+#define CHB_RS0(NAME, ALGO)                                                                                        \
+  int NAME(const void* sendbuf, void* recvbuf, int64_t recvcount, CHB_Datatype datatype, CHB_Op op, CHB_Comm comm) { \
+    return one(comm, CHB_REDUCE_SCATTER, ALGO, sendbuf, recvbuf, recvcount, datatype, op, 2, 1, 0);                  \
+  }
+CHB_RS0(MPICH_reduce_scatter_rec_halving, "recursive_halving")
+CHB_RS0(MPICH_reduce_scatter_rec_doubling, "recursive_doubling")
+CHB_RS0(MPICH_reduce_scatter_pairwise, "pairwise")
+#undef CHB_RS0
+int MPICH_reduce_scatter_radix(const void* sendbuf, void* recvbuf, int64_t recvcount, CHB_Datatype datatype, CHB_Op op,
+                               CHB_Comm comm, int k) {
+  return one(comm, CHB_REDUCE_SCATTER, "radix", sendbuf, recvbuf, recvcount, datatype, op, k, 1, 0);
+}
+
+}  // extern "C"

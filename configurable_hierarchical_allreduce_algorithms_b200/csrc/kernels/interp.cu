@@ -364,6 +364,8 @@ int chb_run_program(chb_comm* c, const chb_program* p, int dtype, int op, const 
     // enough CTAs to keep NVLink busy for large steps, one for latency-bound programs
     long long bytes = (long long)std::max(g.in_elems, g.out_elems) * (long long)esz;
     nctas = bytes <= (64 << 10) ? 1 : (bytes <= (1 << 20) ? 8 : (bytes <= (16 << 20) ? 32 : 64));
+    // a single-rank world only copies locally: HBM-bound, wants every SM
+    if (c->P == 1 && bytes > (16 << 20)) nctas = per_rank_budget;
   }
   if (nctas > per_rank_budget) nctas = per_rank_budget;
   dim3 grid((unsigned)nctas, (unsigned)c->nlocal, 1), block(kInterpThreads, 1, 1);

@@ -116,8 +116,11 @@ chb_comm* chb_comm_create(int rank, int P, int nlocal, void* const* heap_ptrs, v
   return c;
 }
 
+void chb_collective_cache_clear(chb_comm* c);
+
 void chb_comm_destroy(chb_comm* c) {
   if (!c) return;
+  chb_collective_cache_clear(c);
   for (auto& kv : c->blobs) cudaFree(kv.second);
   if (c->ctrl) cudaFree(c->ctrl);
   delete c;

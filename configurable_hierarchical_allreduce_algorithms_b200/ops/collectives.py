@@ -23,7 +23,9 @@ from __future__ import annotations
 
 import torch
 
-from ..parallel.comm import Communicator, CollectiveError, DTYPES
+import ctypes as C
+
+from ..parallel.comm import Communicator, CollectiveError, DTYPES, OPS, _stream_ptr
 from ..parallel.program import ProgramError
 from ..utils import autotune
 from .. import _native as N
@@ -49,38 +51,41 @@ def _ll_ok(comm, ins, outs, payload_bytes):
     return all((t.data_ptr() % 8) == 0 for t in ins + outs)
 
 
+_COLL = {"allreduce": 0, "reduce_scatter": 1, "allgather": 2, "alltoall": 3, "gather": 4}
+_ALGO_BYTES: dict = {}
+
+
 def _run(comm: Communicator, coll: str, ins, outs, count: int, op, algo, k, b, aux, scale, nctas, stream,
          payload_bytes: int, ll_mode: int):
-    esz = ins[0].element_size()
-    in_place = any(i.data_ptr() == o.data_ptr() for i, o in zip(ins, outs))
-    sym_in = all(comm.is_symmetric(t) for t in ins)
-    sym_out = all(comm.is_symmetric(t) for t in outs)
+    """Pick the kernel and enqueue it with a single native call."""
     if algo == "auto":
-        choice = autotune.choose(comm, coll, payload_bytes, ins[0].dtype, sym_in and sym_out)
+        sym = comm.is_symmetric(ins[0]) and comm.is_symmetric(outs[0])
+        key = (coll, payload_bytes, ins[0].dtype, sym)
+        choice = comm._choices.get(key)
+        if choice is None:
+            choice = autotune.choose(comm, coll, payload_bytes, ins[0].dtype, sym)
+            comm._choices[key] = choice
         algo, k, b = choice.algo, choice.k, choice.b
         if nctas == 0:
             nctas = choice.nctas
         if algo == "ll" and not _ll_ok(comm, ins, outs, payload_bytes):
             algo, k, b = "radix_batch", 2, 1
-        if algo == "nvls" and not (comm.has_multicast and sym_in and sym_out and comm.nlocal == 1):
+        elif algo.startswith("nvls") and not (comm.has_multicast and sym and comm.nlocal == 1
+                                              and payload_bytes % 16 == 0):
             algo, k, b = "radix_batch", 2, 1
-    if algo == "ll":
-        if not _ll_ok(comm, ins, outs, payload_bytes):
-            raise CollectiveError(N.ERR_COUNT, "message too large or misaligned for the flagged-line kernel")
-        comm.run_ll(ll_mode, ins, outs, count, op, scale, nctas, stream)
-        return
-    if algo == "nvls":
-        from . import nvls
-        nvls.run(comm, coll, ins[0], outs[0], count, op, scale, nctas, stream)
-        return
     if coll == "alltoall" and algo == "radix_batch":
         algo = "tuna"
-    prog = comm.program(coll, algo, count, k, b, aux, in_symmetric=sym_in and not in_place,
-                        out_symmetric=sym_out and not in_place, in_place=in_place)
-    if prog.work_elems * esz > comm.scratch_bytes:
-        raise CollectiveError(N.ERR_NO_MEM, f"{prog.name} needs {prog.work_elems * esz} bytes of symmetric scratch, "
-                                            f"the communicator has {comm.scratch_bytes}")
-    comm.run_program(prog, ins, outs, op, scale, nctas, stream)
+    ab = _ALGO_BYTES.get(algo)
+    if ab is None:
+        ab = _ALGO_BYTES[algo] = algo.encode()
+    n = len(ins)
+    rc = N.lib().chb_collective(comm._h, _COLL[coll], ab, k, b, aux, DTYPES[ins[0].dtype], OPS[op],
+                                (C.c_void_p * n)(*[t.data_ptr() for t in ins]),
+                                (C.c_void_p * n)(*[t.data_ptr() for t in outs]),
+                                count, scale, nctas, _stream_ptr(stream))
+    if rc:
+        comm._err(rc)
+    comm.launches += 1
 
 
 def all_reduce(comm: Communicator, x, out=None, op: str = "sum", algo: str = "auto", k: int = 2, b: int = 1,

@@ -48,6 +48,7 @@ N.optional("chb_program_release", None, [vp, vp])
 N.optional("chb_run_program", i32, [vp, vp, i32, i32, C.POINTER(vp), C.POINTER(vp), f32, i32, vp])
 N.optional("chb_ll_max_bytes", C.c_longlong, [vp])
 N.optional("chb_ll_collective", i32, [vp, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), C.c_longlong, f32, i32, vp])
+N.optional("chb_collective", i32, [vp, i32, C.c_char_p, i32, i32, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), i64, f32, i32, vp])
 N.optional("chb_nvls_collective", i32, [vp, i32, i32, vp, vp, C.c_longlong, f32, i32, vp])
 
 DTYPES = {
@@ -97,6 +98,8 @@ class Communicator:
         self._own_heap_ptr = None
         self._user_off = 0
         self._programs = {}
+        self._choices = {}       # (collective, bytes, dtype, symmetric) -> autotune.Choice
+        self._user_ranges = []
         self.group = None
         return self
 
@@ -269,9 +272,14 @@ class Communicator:
         return outs if self.nlocal > 1 else outs[0]
 
     def is_symmetric(self, t: torch.Tensor) -> bool:
-        for l in range(self.nlocal):
-            base = N.lib().chb_comm_user_ptr(self._h, l)
-            if base <= t.data_ptr() < base + self.user_bytes:
+        """True if the tensor lives in the peer-visible user region of a local rank."""
+        if not self._user_ranges:
+            for l in range(self.nlocal):
+                base = N.lib().chb_comm_user_ptr(self._h, l)
+                self._user_ranges.append((base, base + self.user_bytes))
+        p = t.data_ptr()
+        for lo, hi in self._user_ranges:
+            if lo <= p < hi:
                 return True
         return False
 

@@ -167,10 +167,15 @@ class Communicator:
     def _heap_symm_mem(self, group, heap_bytes, dev):
         import torch.distributed._symmetric_memory as symm_mem
 
+        name = group.group_name if hasattr(group, "group_name") else group
+        try:
+            symm_mem.enable_symm_mem_for_group(name)
+        except Exception:  # noqa: BLE001 - newer torch enables every group implicitly
+            pass
         t = symm_mem.empty(heap_bytes, dtype=torch.uint8, device=f"cuda:{dev}")
         t.zero_()
         torch.cuda.synchronize()
-        hdl = symm_mem.rendezvous(t, group.group_name if hasattr(group, "group_name") else group)
+        hdl = symm_mem.rendezvous(t, name)
         self._keep += [t, hdl]
         ptrs = [int(p) for p in hdl.buffer_ptrs]
         mc = 0

@@ -1,0 +1,145 @@
+"""One rank per GPU over NVLink: heaps exchanged as cudaIpc handles or through
+torch's symmetric memory (which adds the NVLS multicast alias), every kernel
+family against a locally computed reference.  Needs >= 2 GPUs."""
+import os
+import socket
+import traceback
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.multigpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _inp(r, n, dtype):
+    g = torch.Generator(device="cuda").manual_seed(1000 + r)
+    return (torch.rand(n, generator=g, device="cuda") * 2 - 1).to(dtype)
+
+
+def _worker(rank, P, port, backend, q):
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=P, device_id=torch.device("cuda", rank))
+        import configurable_hierarchical_allreduce_algorithms_b200 as chb
+
+        try:
+            comm = chb.Communicator.from_process_group(backend=backend, scratch_bytes=96 << 20, user_bytes=96 << 20)
+        except Exception:  # noqa: BLE001
+            if backend == "symm_mem":   # the VMM / multicast rendezvous is not available on every box
+                q.put((rank, "skip", traceback.format_exc()))
+                dist.destroy_process_group()
+                return
+            raise
+        assert comm.backend == backend, (comm.backend, getattr(comm, "_symm_mem_error", None))
+        notes = [f"backend={comm.backend} nvls={comm.has_multicast}"]
+        tol = {torch.float32: 1e-5, torch.bfloat16: 2e-2}
+
+        def close(a, b, dtype):
+            torch.testing.assert_close(a.double(), b.double(), rtol=tol[dtype], atol=tol[dtype] * P)
+
+        divs = [b for b in (1, 2, 4, 8) if P % b == 0]
+        for dtype in (torch.float32, torch.bfloat16):
+            for n in (1, 3, 1000, 1 << 16, (1 << 20) + 3):
+                N = n * P
+                ins = [_inp(r, N, dtype) for r in range(P)]
+                exp = torch.stack([x.double() for x in ins]).sum(0)
+                x = ins[rank]
+                algos = [("ll", 2, 1)] if N * x.element_size() <= comm.ll_max_bytes else []
+                algos += [("radix_batch", 2, b) for b in divs] + [("radix_batch", 4, divs[-1]), ("ring", 2, 1),
+                                                                  ("recursive_doubling", 2, 1), ("auto", 2, 1)]
+                for algo, k, b in algos:
+                    y = chb.all_reduce(comm, x, algo=algo, k=k, b=b)
+                    close(y, exp, dtype)
+                    y = chb.reduce_scatter(comm, x, algo=algo if algo not in ("recursive_doubling",) else "radix", k=k, b=b)
+                    close(y, exp[rank * n:(rank + 1) * n], dtype)
+                    y = chb.all_gather(comm, x[:n].contiguous(), algo=algo if algo != "recursive_doubling" else "k_brucks", k=k, b=b)
+                    assert torch.equal(y, torch.cat([i[:n] for i in ins]))
+                comm.check()
+        # symmetric buffers: zero-copy programs, NVLS kernels
+        n = 1 << 18
+        N = n * P
+        xs = comm.empty(N, torch.float32)
+        ys = comm.empty(N, torch.float32)
+        ins = [_inp(r, N, torch.float32) for r in range(P)]
+        exp = torch.stack([x.double() for x in ins]).sum(0)
+        xs.copy_(ins[rank])
+        torch.cuda.synchronize()
+        dist.barrier()
+        chb.all_reduce(comm, xs, out=ys, algo="radix_batch", k=2, b=1)
+        close(ys, exp, torch.float32)
+        if comm.has_multicast:
+            for algo in ("nvls", "nvls1"):
+                ys.zero_()
+                chb.all_reduce(comm, xs, out=ys, algo=algo, scale=0.5)
+                close(ys, exp * 0.5, torch.float32)
+            y2 = chb.reduce_scatter(comm, xs, algo="nvls")
+            close(y2, exp[rank * n:(rank + 1) * n], torch.float32)
+            ys.zero_()
+            chb.all_gather(comm, xs[:n], out=ys, algo="nvls")
+            torch.cuda.synchronize()
+            assert torch.equal(ys, torch.cat([i[:n] for i in ins]))
+            xb, yb = xs.view(torch.bfloat16), ys.view(torch.bfloat16)
+            insb = [_inp(r, 2 * N, torch.bfloat16) for r in range(P)]
+            xb.copy_(insb[rank])
+            torch.cuda.synchronize()
+            dist.barrier()
+            chb.all_reduce(comm, xb, out=yb, algo="nvls")
+            close(yb, torch.stack([x.double() for x in insb]).sum(0), torch.bfloat16)
+            notes.append("nvls kernels ok")
+        for _ in range(20):   # back-to-back mixed launches
+            chb.all_reduce(comm, xs, out=ys)
+            chb.all_reduce(comm, xs[:256], out=ys[:256])
+        comm.barrier()
+        comm.check()
+        dist.barrier()
+        comm.close()
+        dist.destroy_process_group()
+        q.put((rank, "ok", "; ".join(notes)))
+    except Exception:  # noqa: BLE001
+        q.put((rank, "fail", traceback.format_exc()))
+
+
+def _launch(P, backend):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, P, port, backend, q)) for r in range(P)]
+    for p in procs:
+        p.start()
+    res = []
+    for _ in range(P):
+        res.append(q.get(timeout=600))
+    for p in procs:
+        p.join(60)
+    if all(r[1] == "skip" for r in res):
+        pytest.skip("symmetric-memory rendezvous unavailable: " + res[0][2][-400:])
+    bad = [r for r in res if r[1] != "ok"]
+    assert not bad, "\n".join(f"rank {r[0]}:\n{r[2]}" for r in bad)
+    return res
+
+
+def _ngpus():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("backend", ["ipc", "symm_mem"])
+def test_all_gpus(backend):
+    P = _ngpus()
+    if P < 2:
+        pytest.skip("needs at least two GPUs")
+    os.environ.setdefault("NCCL_DEBUG", "WARN")
+    res = _launch(P, backend)
+    print(res[0][2])

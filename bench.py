@@ -101,9 +101,11 @@ def per_call_ms(fn, iters, flush, barrier):
 
     out = []
     for _ in range(iters):
-        flush()
         barrier()
         torch.cuda.synchronize()
+        # the flush runs on the stream while the host enqueues the collective behind
+        # it, so the interval between the two events is device time, not launch latency
+        flush()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         fn()

@@ -104,29 +104,34 @@ nvls_kernel(World w, const char* mc_in, char* mc_out, const char* loc_in, char* 
   // every peer has entered: its inputs are final, its outputs may be overwritten
   ok = ok && cta_barrier(w, c, rank, seq + 1ull);
   if (ok) {
-    if (MODE == NV_AR2) {
-      const long long lo = nvec * rank / P, hi = nvec * (rank + 1) / P;
-      for (long long i = lo + g; i < hi; i += TT) {
-        uint4 v = MM<T>::ld_reduce(mc_in + i * 16);
-        if (do_scale) v = scale_vec<T>(v, scale);
-        MM<T>::st(mc_out + i * 16, v);
+    // U independent 16-byte operations per thread keep enough bytes in flight
+    // to cover the switch round trip
+    constexpr int U = 8;
+    long long lo = 0, hi = nvec;        // range of vectors this rank works on
+    long long src_base = 0;             // added to the index on the source side
+    if (MODE == NV_AR2) { lo = nvec * rank / P; hi = nvec * (rank + 1) / P; }
+    if (MODE == NV_RS || MODE == NV_AG) src_base = nvec * rank;
+    for (long long i0 = lo + g; i0 < hi; i0 += TT * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + (long long)u * TT;
+        if (i < hi) {
+          if (MODE == NV_AG) v[u] = ld16_cg(loc_in + i * 16);
+          else if (MODE == NV_RS) v[u] = MM<T>::ld_reduce(mc_in + (src_base + i) * 16);
+          else v[u] = MM<T>::ld_reduce(mc_in + i * 16);
+        }
       }
-    } else if (MODE == NV_AR1) {
-      for (long long i = g; i < nvec; i += TT) {
-        uint4 v = MM<T>::ld_reduce(mc_in + i * 16);
-        if (do_scale) v = scale_vec<T>(v, scale);
-        st16(loc_out + i * 16, v);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + (long long)u * TT;
+        if (i < hi) {
+          if (MODE != NV_AG && do_scale) v[u] = scale_vec<T>(v[u], scale);
+          if (MODE == NV_AR2) MM<T>::st(mc_out + i * 16, v[u]);
+          else if (MODE == NV_AG) MM<T>::st(mc_out + (src_base + i) * 16, v[u]);
+          else st16(loc_out + i * 16, v[u]);
+        }
       }
-    } else if (MODE == NV_RS) {
-      const long long base = nvec * rank;
-      for (long long i = g; i < nvec; i += TT) {
-        uint4 v = MM<T>::ld_reduce(mc_in + (base + i) * 16);
-        if (do_scale) v = scale_vec<T>(v, scale);
-        st16(loc_out + i * 16, v);
-      }
-    } else {  // NV_AG
-      const long long base = nvec * rank;
-      for (long long i = g; i < nvec; i += TT) MM<T>::st(mc_out + (base + i) * 16, ld16_cg(loc_in + i * 16));
     }
   }
   // all my reads of the peers' inputs and my multicast stores are done
@@ -183,7 +188,7 @@ int chb_nvls_collective(chb_comm* c, int mode, int dtype, const void* in, void* 
   if (nctas <= 0) {
     long long work = (mode == NV_AR2) ? nvec / c->P : nvec;
     nctas = (int)((work + kNvlsThreads * 4 - 1) / (kNvlsThreads * 4));
-    if (nctas > 32) nctas = 32;
+    if (nctas > 64) nctas = 64;
   }
   if (nctas > kNvlsMaxCtas) nctas = kNvlsMaxCtas;
   if (nctas > c->max_ctas) nctas = c->max_ctas;

@@ -35,18 +35,25 @@ def candidates(coll: str, P: int, nbytes: int, comm) -> list[tuple]:
     out = []
     if nbytes <= comm.ll_max_bytes:
         out.append(("ll", 2, 1, 0))
+    if coll == "allreduce" and P > 1 and 64 <= nbytes <= comm.ll2_max_bytes:
+        out.append(("ll2", 2, 1, 0))
+        if nbytes >= (1 << 20):
+            out.append(("ll2", 2, 1, 64))
     divs = [b for b in (1, 2, 4, 8) if P % b == 0 and b <= P]
     for b in divs:
         ks = sorted({2, 4, max(2, b)}) if b > 2 else [2]
         for k in ks:
-            if nbytes <= (1 << 20):
+            if nbytes <= (256 << 10):
                 out.append(("radix_batch", k, b, 1))
                 out.append(("radix_batch", k, b, 4))
+            elif nbytes <= (4 << 20):
+                for n in (4, 16, 32):
+                    out.append(("radix_batch", k, b, n))
             else:
-                for n in (16, 32, 64):
+                for n in (32, 64, 128):
                     out.append(("radix_batch", k, b, n))
     if comm.has_multicast and nbytes % 16 == 0 and nbytes >= 16 * P:
-        for n in ((1, 4) if nbytes <= (1 << 20) else (16, 32, 64)):
+        for n in ((1, 4, 16) if nbytes <= (1 << 20) else (16, 32, 64)):
             out.append(("nvls", 2, 1, n))
             if coll == "allreduce" and nbytes <= (4 << 20):
                 out.append(("nvls1", 2, 1, n))

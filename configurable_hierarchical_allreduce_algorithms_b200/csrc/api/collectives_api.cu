@@ -98,6 +98,10 @@ int chb_collective(chb_comm* c, int coll, const char* algo, int k, int b, int au
                    const void* const* in, void* const* out, int64_t count, float scale, int nctas,
                    cudaStream_t stream) {
   if (!c || !algo || !in || !out) return CHB_ERR_ARG;
+  if (!std::strcmp(algo, "ll2")) {
+    if (coll != CHB_ALLREDUCE) return CHB_ERR_UNSUPPORTED;
+    return chb_ll_collective(c, 3, dtype, op, in, out, count, scale, nctas, stream);
+  }
   if (!std::strcmp(algo, "ll")) {
     int mode = coll == CHB_ALLREDUCE ? 0 : coll == CHB_REDUCE_SCATTER ? 1 : coll == CHB_ALLGATHER ? 2 : -1;
     if (mode < 0) return CHB_ERR_UNSUPPORTED;

@@ -70,6 +70,8 @@ def _run(comm: Communicator, coll: str, ins, outs, count: int, op, algo, k, b, a
             nctas = choice.nctas
         if algo == "ll" and not _ll_ok(comm, ins, outs, payload_bytes):
             algo, k, b = "radix_batch", 2, 1
+        elif algo == "ll2" and not (payload_bytes <= comm.ll2_max_bytes and _ll_ok(comm, ins, outs, 0)):
+            algo, k, b = "radix_batch", 2, 1
         elif algo.startswith("nvls") and not (comm.has_multicast and sym and comm.nlocal == 1
                                               and payload_bytes % 16 == 0):
             algo, k, b = "radix_batch", 2, 1

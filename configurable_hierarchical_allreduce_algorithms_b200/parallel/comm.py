@@ -122,7 +122,7 @@ class Communicator:
         return self
 
     @classmethod
-    def from_process_group(cls, group=None, backend: str | None = None, ll_bytes: int = 256 << 10,
+    def from_process_group(cls, group=None, backend: str | None = None, ll_bytes: int = 1 << 20,
                            scratch_bytes: int = 256 << 20, user_bytes: int = 64 << 20,
                            timeout_us: int = 10_000_000):
         """One rank per process.  ``backend``: "symm_mem" (VMM + NVLS multicast via
@@ -224,6 +224,7 @@ class Communicator:
         L.chb_comm_info(h, info, 11)
         self.scratch_bytes, self.user_bytes, self.heap_bytes = int(info[5]), int(info[6]), int(info[7])
         self.ll_max_bytes, self.sm_count, self.has_multicast = int(info[8]), int(info[9]), bool(info[10])
+        self.ll2_max_bytes = (self.ll_max_bytes // 16) * 8 * P   # two-shot flagged lines: half a slot per slice
         self.set_timeout_us(int(os.environ.get("CHB_TIMEOUT_US", timeout_us)))
         self.launches = 0   # kernels launched by this communicator (all local ranks count as one)
 

@@ -9,7 +9,7 @@ result is kept in a JSON table keyed by ``(gpu, P, collective, dtype)`` that
 
 Table format::
 
-    {"NVIDIA B200|8|allreduce|float32": [[max_bytes, algo, k, b, nctas], ...]}   # ascending max_bytes
+    {"NVIDIA B200|8|allreduce|fp32": [[max_bytes, algo, k, b, nctas], ...]}   # ascending max_bytes
 """
 from __future__ import annotations
 
@@ -53,7 +53,8 @@ def reload(path: str | None = None) -> None:
 
 def _key(comm, coll: str, dtype) -> str:
     name = torch.cuda.get_device_name(comm.device) if torch.cuda.is_available() else "cpu"
-    return f"{name}|{comm.P}|{coll}|{str(dtype).replace('torch.', '')}"
+    short = {"torch.float32": "fp32", "torch.bfloat16": "bf16", "torch.float16": "fp16"}
+    return f"{name}|{comm.P}|{coll}|{short.get(str(dtype), str(dtype).replace('torch.', ''))}"
 
 
 def heuristic(comm, coll: str, payload_bytes: int, symmetric: bool) -> Choice:
@@ -65,6 +66,8 @@ def heuristic(comm, coll: str, payload_bytes: int, symmetric: bool) -> Choice:
     ll_cut = min(comm.ll_max_bytes, 64 << 10 if coll == "allreduce" else 128 << 10)
     if comm.P > 1 and payload_bytes <= ll_cut:
         return Choice("ll")
+    if comm.P > 2 and coll == "allreduce" and payload_bytes <= min(comm.ll2_max_bytes, 2 << 20):
+        return Choice("ll2")
     if comm.has_multicast and symmetric and comm.nlocal == 1 and coll in ("allreduce", "reduce_scatter", "allgather"):
         return Choice("nvls")
     return Choice("radix_batch", 2, 1, 0)

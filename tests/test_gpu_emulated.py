@@ -164,6 +164,10 @@ def test_flagged_line_kernels(comms, P):
             # bit-identical on every rank: all ranks add in rank order
             for r in range(1, P):
                 assert torch.equal(outs[r], outs[0])
+            outs = chb.all_reduce(comm, ins, algo="ll2")      # two-shot flagged lines
+            for r in range(P):
+                check(outs[r], exp, dtype, P)
+                assert torch.equal(outs[r], outs[0])
             outs = chb.reduce_scatter(comm, ins, algo="ll")
             for r in range(P):
                 check(outs[r], exp[r * n:(r + 1) * n], dtype, P)

@@ -35,7 +35,7 @@ def _worker(rank, P, port, backend, q):
         import configurable_hierarchical_allreduce_algorithms_b200 as chb
 
         try:
-            comm = chb.Communicator.from_process_group(backend=backend, scratch_bytes=96 << 20, user_bytes=96 << 20)
+            comm = chb.Communicator.from_process_group(backend=backend, scratch_bytes=(48 << 20) * P, user_bytes=96 << 20)
         except Exception:  # noqa: BLE001
             if backend == "symm_mem":   # the VMM / multicast rendezvous is not available on every box
                 q.put((rank, "skip", traceback.format_exc()))

@@ -1,0 +1,43 @@
+"""Build the reference's own allreduce / reduce-scatter / allgather sources,
+unmodified, against the thread-per-rank MPI shim in ``baseline/shim``.
+
+The reference is plain MPI C++ without a Python package, so the prescribed
+``pip install --target baseline/_ref`` has nothing to install; this script is
+the replacement: it copies the three source files into ``baseline/_ref/src``
+(git-ignored) and links them with the shim into ``baseline/_ref/ref_driver``.
+Run it once where the reference tree is mounted; the binary travels with the
+snapshot.
+"""
+from __future__ import annotations
+
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+W = REF / "testing" / "custom_implementations" / "work_dir"
+SOURCES = [W / "all_gather" / "all_gather_radix_batch_1_0.cpp",
+           W / "reduce_scatter" / "reduce_scatter_radix_batch.cpp",
+           W / "all_reduce" / "all_reduce_radix_batch.cpp"]
+
+
+def build() -> Path:
+    out = HERE / "_ref"
+    src = out / "src"
+    src.mkdir(parents=True, exist_ok=True)
+    copied = []
+    for s in SOURCES:
+        d = src / s.name
+        shutil.copyfile(s, d)
+        copied.append(str(d))
+    exe = out / "ref_driver"
+    cmd = ["g++", "-O3", "-std=c++17", "-w", "-pthread", "-I", str(HERE / "shim"),
+           str(HERE / "shim" / "ref_driver.cpp"), str(HERE / "shim" / "shim.cpp"), *copied, "-o", str(exe)]
+    subprocess.run(cmd, check=True)
+    return exe
+
+
+if __name__ == "__main__":
+    print(build())

@@ -1,0 +1,52 @@
+// Minimal single-process stand-in for <mpi.h>: every MPI rank is a thread of
+// one process.  Only what the reference's three collectives call is provided
+// (rank / size / type size, Isend / Irecv / Wait / Waitall, Reduce_local,
+// Barrier, Wtime).  Sends are eager (the payload is copied into the
+// destination's mailbox), receives match on (source, tag) in arrival order.
+// This exists so that the reference's own sources can be compiled unmodified
+// and timed on a machine without an MPI installation.
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+typedef int MPI_Comm;
+typedef int MPI_Datatype;   // value = element size in bytes, except the tags below
+typedef int MPI_Op;
+typedef long MPI_Aint;
+struct MPI_Status { int MPI_SOURCE, MPI_TAG, MPI_ERROR; };
+struct ShimRequest;
+typedef ShimRequest* MPI_Request;
+
+#define MPI_COMM_WORLD 0
+#define MPI_SUCCESS 0
+#define MPI_ERR_NO_MEM 1
+#define MPI_ERR_OTHER 2
+#define MPI_ERR_COUNT 3
+#define MPI_ERR_OP 4
+#define MPI_ERR_ARG 5
+#define MPI_CHAR 1
+#define MPI_INT 4
+#define MPI_DOUBLE 8
+#define MPI_FLOAT 104      /* 4-byte float, told apart from MPI_INT */
+#define MPI_SUM 0
+#define MPI_MAX 1
+#define MPI_MIN 2
+#define MPI_IN_PLACE ((void*)-1)
+#define MPI_STATUS_IGNORE ((MPI_Status*)0)
+#define MPI_STATUSES_IGNORE ((MPI_Status*)0)
+
+int MPI_Comm_rank(MPI_Comm, int*);
+int MPI_Comm_size(MPI_Comm, int*);
+int MPI_Type_size(MPI_Datatype, int*);
+int MPI_Isend(const void*, int, MPI_Datatype, int, int, MPI_Comm, MPI_Request*);
+int MPI_Irecv(void*, int, MPI_Datatype, int, int, MPI_Comm, MPI_Request*);
+int MPI_Wait(MPI_Request*, MPI_Status*);
+int MPI_Waitall(int, MPI_Request*, MPI_Status*);
+int MPI_Reduce_local(const void*, void*, int, MPI_Datatype, MPI_Op);
+int MPI_Barrier(MPI_Comm);
+double MPI_Wtime();
+
+// shim control (not MPI): world size, per-thread rank, failure flag
+void shim_init(int nprocs);
+void shim_set_rank(int rank);
+int shim_failed();

@@ -118,7 +118,9 @@ def per_call_ms(fn, iters, flush, barrier):
 def reference_arm(args):
     from baseline import reference_bench
 
-    print(json.dumps(reference_bench.run(args)), flush=True)
+    out = reference_bench.run(args)
+    if out is not None:
+        print(json.dumps(out), flush=True)
 
 
 def main():

@@ -1,0 +1,48 @@
+"""Same inputs through the reference's own sources (built unmodified against
+the thread-per-rank MPI shim, baseline/build_reference.py) and through this
+library's schedules: results must be identical for integers."""
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from configurable_hierarchical_allreduce_algorithms_b200.parallel.program import Program
+
+ROOT = Path(__file__).resolve().parent.parent
+EXE = ROOT / "baseline" / "_ref" / "ref_driver"
+
+
+@pytest.fixture(scope="module")
+def ref_driver():
+    if not EXE.exists():
+        if not Path("/root/reference/testing").exists():
+            pytest.skip("reference sources are not available on this machine")
+        import sys
+        sys.path.insert(0, str(ROOT))
+        from baseline import build_reference
+        build_reference.build()
+    return EXE
+
+
+def reference_result(exe, coll, P, k, b, n, seed):
+    r = subprocess.run([str(exe), "check", coll, str(P), str(k), str(b), str(n), str(seed)],
+                       capture_output=True, text=True, timeout=120)
+    vals = [int(v) for v in r.stdout.split()]
+    assert vals[0] == 0, "the reference itself failed (timeout / bad destination / truncation)"
+    per = {"ag": n * P, "rs": n, "ar": n * P}[coll]
+    return [np.array(vals[1 + i * per:1 + (i + 1) * per], dtype=np.int32) for i in range(P)]
+
+
+@pytest.mark.parametrize("P,b", [(4, 1), (4, 2), (8, 2), (8, 4), (8, 8), (12, 3), (16, 4), (18, 3)])
+def test_same_results_as_reference(ref_driver, P, b):
+    seed, n = 5, 3
+    for k in (2, 3, 4, 7):
+        for short, coll in (("ag", "allgather"), ("rs", "reduce_scatter"), ("ar", "allreduce")):
+            ref = reference_result(ref_driver, short, P, k, b, n, seed)
+            count = n * P if coll == "allreduce" else n
+            prog = Program(coll, "radix_batch", P, count, k, b)
+            ins = [((seed * 31 + r * 1009 + np.arange(prog.in_elems)) % 97).astype(np.int32) for r in range(P)]
+            ours = prog.simulate(ins)
+            for r in range(P):
+                np.testing.assert_array_equal(ours[r], ref[r], err_msg=f"{coll} P={P} k={k} b={b} rank {r}")

@@ -177,6 +177,25 @@ __device__ __forceinline__ void rank_exit(Ctrl* c, unsigned nctas, F publish) {
   }
 }
 
+// Cross-rank barrier at CTA granularity: CTA c of this rank meets CTA c of every
+// peer (all ranks launch the same grid).  `seq` is a per-communicator barrier
+// sequence number (Ctrl::bar_seq based); slots are never reset.
+// Returns false on expiry.
+__device__ __forceinline__ bool cta_barrier(const World& w, Ctrl* c, int rank, unsigned long long seq) {
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) s_ok = 1;
+  __syncthreads();
+  const int q = threadIdx.x;
+  if (q < w.P && q != rank) {
+    __threadfence_system();
+    const int slot = kSigNvlsBase + (int)blockIdx.x * kMaxRanks;
+    st_release_sys(&w.sig[q][slot + rank], seq);
+    if (!wait_flag_ge(&w.sig[rank][slot + q], seq, c, w.timeout_ns, ST_TIMEOUT_BARRIER, rank, -2, q)) s_ok = 0;
+  }
+  __syncthreads();
+  return s_ok != 0;
+}
+
 // ------------------------------------------------------------------ element types
 
 template <typename T> struct Elem;  // acc type, elements per 16 bytes, conversions

@@ -61,22 +61,6 @@ template <> struct MM<__half> {
   }
 };
 
-// CTA c of this rank meets CTA c of every peer.  Returns false on expiry.
-__device__ __forceinline__ bool cta_barrier(const World& w, Ctrl* c, int rank, unsigned long long seq) {
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) s_ok = 1;
-  __syncthreads();
-  const int q = threadIdx.x;
-  if (q < w.P && q != rank) {
-    __threadfence_system();
-    const int slot = kSigNvlsBase + (int)blockIdx.x * kMaxRanks;
-    st_release_sys(&w.sig[q][slot + rank], seq);
-    if (!wait_flag_ge(&w.sig[rank][slot + q], seq, c, w.timeout_ns, ST_TIMEOUT_BARRIER, rank, -2, q)) s_ok = 0;
-  }
-  __syncthreads();
-  return s_ok != 0;
-}
-
 template <typename T>
 __device__ __forceinline__ uint4 scale_vec(uint4 v, float s) {
   typename Elem<T>::Acc a[Elem<T>::kPerVec];

@@ -1,0 +1,57 @@
+"""Fused collective + compute kernels: reduce-scatter with an fp8 block-scaled
+wire format, and reduce-scatter fused with the sharded AdamW update
+(``csrc/kernels/fp8_wire.cu``, ``csrc/kernels/fused_adam.cu``)."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import _native as N
+from ..parallel.comm import DTYPES, Communicator, _stream_ptr
+
+vp, i32, f32 = C.c_void_p, C.c_int, C.c_float
+N.optional("chb_rs_fp8_wire", i32, [vp, i32, C.POINTER(vp), C.POINTER(vp), C.c_longlong, f32, i32, vp])
+N.optional("chb_rs_adam", i32, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
+                                C.c_longlong, C.POINTER(f32), i32, i32, vp])
+
+
+def _lst(x):
+    return [x] if isinstance(x, torch.Tensor) else list(x)
+
+
+def _arr(ts):
+    return (vp * len(ts))(*[t.data_ptr() for t in ts])
+
+
+def reduce_scatter_fp8(comm: Communicator, x, out=None, scale: float = 1.0, nctas: int = 0, stream=None):
+    """Sum reduce-scatter whose wire format is fp8 e4m3 in 128-element blocks
+    with fp32 scales.  ``x``: P blocks of n elements (n % 128 == 0), f32 or bf16."""
+    ins = _lst(x)
+    n = ins[0].numel() // comm.P
+    outs = _lst(out) if out is not None else [torch.empty(n, dtype=t.dtype, device=t.device) for t in ins]
+    rc = N.lib().chb_rs_fp8_wire(comm.handle, DTYPES[ins[0].dtype], _arr(ins), _arr(outs), n, scale, nctas,
+                                 _stream_ptr(stream))
+    comm._err(rc)
+    comm.launches += 1
+    return outs if comm.nlocal > 1 else outs[0]
+
+
+def reduce_scatter_adam(comm: Communicator, grads, master, exp_avg, exp_avg_sq, param_shard, *, lr: float,
+                        betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.0, step: int = 1,
+                        grad_scale: float = 1.0, use_multimem: bool | None = None, nctas: int = 0, stream=None):
+    """Rank r sums shard r of every rank's flat fp32 gradient buffer (symmetric
+    memory), applies AdamW to its fp32 master shard and writes the bf16 shard
+    into ``param_shard``.  All tensor arguments: one tensor, or a list of P
+    tensors in an emulated world."""
+    g, w, m, v, p = _lst(grads), _lst(master), _lst(exp_avg), _lst(exp_avg_sq), _lst(param_shard)
+    n = w[0].numel()
+    assert g[0].numel() == n * comm.P and g[0].dtype == torch.float32 and p[0].dtype == torch.bfloat16
+    if use_multimem is None:
+        use_multimem = comm.has_multicast and comm.nlocal == 1 and comm.P > 2
+    hyper = (f32 * 8)(lr, betas[0], betas[1], eps, weight_decay, 1.0 - betas[0] ** step, 1.0 - betas[1] ** step,
+                      grad_scale)
+    rc = N.lib().chb_rs_adam(comm.handle, _arr(g), _arr(w), _arr(m), _arr(v), _arr(p), n, hyper,
+                             int(bool(use_multimem)), nctas, _stream_ptr(stream))
+    comm._err(rc)
+    comm.launches += 1

@@ -114,11 +114,23 @@ int chb_collective(chb_comm* c, int coll, const char* algo, int k, int b, int au
     if (mode < 0) return CHB_ERR_UNSUPPORTED;
     return chb_nvls_collective(c, mode, dtype, in[0], out[0], count, scale, nctas, stream);
   }
-  bool in_place = false;
-  for (int l = 0; l < c->nlocal; ++l) in_place |= (in[l] == out[l]);
+  // In place means in == out, except for the allgather, whose in-place form is
+  // "my block already sits at its slot of the output" (in == out + rank * block):
+  // that needs no staging, the self copy is a no-op.
+  bool in_place = false, ag_alias = false;
+  for (int l = 0; l < c->nlocal; ++l) {
+    if (coll == CHB_ALLGATHER) {
+      const char* slot = (const char*)out[l] + (int64_t)(c->rank + l) * count * chb_dtype_size(dtype);
+      if ((const char*)in[l] == slot) { ag_alias = true; continue; }
+    }
+    in_place |= (in[l] == out[l]);
+  }
   int flags = 0;
   if (in_place) flags = 4;
   else flags = (all_symmetric(c, in) ? 1 : 0) | (all_symmetric(c, (const void* const*)out) ? 2 : 0);
+  // aliased allgather inputs sit at a different heap offset on every rank, so
+  // peers cannot address them as "my input pointer, your heap": stage them
+  if (ag_alias) flags &= ~1;
   chb_program* p = nullptr;
   int rc = get_program(c, coll, algo, k, b, aux, count, flags, &p);
   if (rc) return rc;

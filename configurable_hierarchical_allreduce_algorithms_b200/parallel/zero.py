@@ -1,0 +1,98 @@
+"""ZeRO-style sharded optimizer step.
+
+All parameters live in one flat bf16 buffer and all gradients in one flat fp32
+buffer, both in symmetric memory.  ``step()`` is two launches:
+
+1. ``reduce_scatter_adam`` — rank r pulls shard r of every rank's gradient
+   buffer (or has the switch sum it), applies AdamW to its fp32 master shard
+   and writes the updated bf16 shard into the parameter buffer
+   (``csrc/kernels/fused_adam.cu``);
+2. an allgather of the parameter buffer with the configurable radix-batch
+   schedule (or NVLS / the tuned choice).
+
+The reference provides the two primitives only
+(reduce_scatter_radix_batch.cpp:200, all_gather_radix_batch_1_0.cpp:37).
+With ``comm=None`` the same step runs over ``torch.distributed`` (gloo) with
+plain tensor math: the host-level fallback used by the CPU tests.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..ops import collectives, fused
+
+
+class ShardedAdamW:
+    def __init__(self, module: torch.nn.Module, comm=None, lr=3e-4, betas=(0.9, 0.95), eps=1e-8,
+                 weight_decay=0.1, ag_algo: str = "auto", ag_k: int = 2, ag_b: int = 1, group=None):
+        self.module, self.comm, self.group = module, comm, group
+        self.lr, self.betas, self.eps, self.wd = lr, betas, eps, weight_decay
+        self.ag_algo, self.ag_k, self.ag_b = ag_algo, ag_k, ag_b
+        self.P = comm.P if comm is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
+        self.rank = comm.rank if comm is not None else (dist.get_rank(group) if dist.is_initialized() else 0)
+        self.params = [p for p in module.parameters() if p.requires_grad]
+        dev = self.params[0].device
+        offs, total = [], 0
+        for p in self.params:
+            offs.append(total)
+            total += (p.numel() + 7) // 8 * 8          # 16-byte aligned bf16 slots
+        unit = 64 * self.P
+        total = (total + unit - 1) // unit * unit
+        self.n = total // self.P
+        self.total = total
+        if comm is not None:
+            self.grad_flat = comm.empty(total, torch.float32)
+            self.param_flat = comm.empty(total, torch.bfloat16)
+        else:
+            self.grad_flat = torch.zeros(total, device=dev)
+            self.param_flat = torch.zeros(total, dtype=self.params[0].dtype, device=dev)
+        self.grad_flat.zero_()
+        self.param_flat.zero_()
+        for p, off in zip(self.params, offs):
+            self.param_flat[off:off + p.numel()].copy_(p.detach().reshape(-1))
+            p.data = self.param_flat[off:off + p.numel()].view_as(p)     # the model now lives in the flat buffer
+            p.main_grad = self.grad_flat[off:off + p.numel()].view_as(p)
+            p.register_post_accumulate_grad_hook(self._hook)
+        lo = self.rank * self.n
+        self.master = self.param_flat[lo:lo + self.n].float().clone()
+        self.exp_avg = torch.zeros(self.n, device=dev)
+        self.exp_avg_sq = torch.zeros(self.n, device=dev)
+        self.t = 0
+
+    @staticmethod
+    def _hook(p):
+        p.main_grad.add_(p.grad)
+        p.grad = None
+
+    def zero_grad(self):
+        self.grad_flat.zero_()
+
+    @torch.no_grad()
+    def step(self, stream=None):
+        self.t += 1
+        lo = self.rank * self.n
+        shard = self.param_flat[lo:lo + self.n]
+        if self.comm is not None:
+            fused.reduce_scatter_adam(self.comm, self.grad_flat, self.master, self.exp_avg, self.exp_avg_sq, shard,
+                                      lr=self.lr, betas=self.betas, eps=self.eps, weight_decay=self.wd, step=self.t,
+                                      grad_scale=1.0 / self.P, stream=stream)
+            collectives.all_gather(self.comm, shard, out=self.param_flat, algo=self.ag_algo, k=self.ag_k,
+                                   b=self.ag_b, stream=stream)
+            return
+        # host-level fallback: same arithmetic with library collectives
+        g = self.grad_flat.clone()
+        if self.P > 1:
+            dist.all_reduce(g, group=self.group)
+        g = g[lo:lo + self.n] / self.P
+        b1, b2 = self.betas
+        self.exp_avg.mul_(b1).add_(g, alpha=1 - b1)
+        self.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
+        mhat = self.exp_avg / (1 - b1 ** self.t)
+        vhat = self.exp_avg_sq / (1 - b2 ** self.t)
+        self.master.sub_(self.lr * (mhat / (vhat.sqrt() + self.eps) + self.wd * self.master))
+        shard.copy_(self.master)
+        if self.P > 1:
+            parts = [torch.empty_like(shard) for _ in range(self.P)]
+            dist.all_gather(parts, shard.clone(), group=self.group)
+            self.param_flat.copy_(torch.cat(parts))

@@ -30,7 +30,7 @@ from ..parallel.zero import ShardedAdamW
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--mode", default="dp", choices=["dp", "zero"])
-    ap.add_argument("--impl", default="ours", choices=["ours", "nccl"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "nccl", "torchddp"])
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--micro-batch", type=int, default=0)
@@ -62,7 +62,15 @@ def main(argv=None):
         need = nparam * (8 if args.mode == "dp" else 6) + (256 << 20)
         comm = (Communicator.from_process_group(user_bytes=need, scratch_bytes=256 << 20) if world > 1
                 else Communicator.emulated(1, user_bytes=need, scratch_bytes=1 << 20))
-    if args.mode == "dp":
+    torch_ddp = None
+    if args.impl == "torchddp":
+        # the stock data-parallel path: bf16 gradients, 25 MB buckets, NCCL allreduce overlapped by torch
+        assert args.mode == "dp"
+        torch_ddp = (torch.nn.parallel.DistributedDataParallel(model, device_ids=[lr_], bucket_cap_mb=25)
+                     if world > 1 else model)
+        topt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+        ddp, opt = None, None
+    elif args.mode == "dp":
         ddp = DataParallel(model, comm=comm if ours else None, algo=args.algo, k=args.k, b=args.b)
         if not ours:
             ddp.cuda = False     # library collectives on CUDA tensors through torch.distributed
@@ -77,6 +85,13 @@ def main(argv=None):
 
     def step(i):
         dev_tokens.copy_(host_tokens[i], non_blocking=True)          # this step's inputs from pinned host memory
+        if torch_ddp is not None:
+            topt.zero_grad(set_to_none=True)
+            loss = torch_ddp(dev_tokens, dev_tokens)
+            loss.backward()
+            topt.step()
+            loss_host.copy_(loss.detach().float().reshape(1), non_blocking=True)
+            return loss
         (ddp or opt).zero_grad()
         loss = (ddp or model)(dev_tokens, dev_tokens)
         loss.backward()

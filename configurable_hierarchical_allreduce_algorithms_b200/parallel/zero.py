@@ -81,10 +81,15 @@ class ShardedAdamW:
                                    b=self.ag_b, stream=stream)
             return
         # host-level fallback: same arithmetic with library collectives
-        g = self.grad_flat.clone()
-        if self.P > 1:
-            dist.all_reduce(g, group=self.group)
-        g = g[lo:lo + self.n] / self.P
+        if self.P > 1 and self.grad_flat.is_cuda:
+            g = torch.empty(self.n, device=self.grad_flat.device)
+            dist.reduce_scatter_tensor(g, self.grad_flat, group=self.group)
+            g = g / self.P
+        else:
+            g = self.grad_flat.clone()
+            if self.P > 1:
+                dist.all_reduce(g, group=self.group)      # gloo has no reduce-scatter
+            g = g[lo:lo + self.n] / self.P
         b1, b2 = self.betas
         self.exp_avg.mul_(b1).add_(g, alpha=1 - b1)
         self.exp_avg_sq.mul_(b2).addcmul_(g, g, value=1 - b2)
@@ -92,7 +97,9 @@ class ShardedAdamW:
         vhat = self.exp_avg_sq / (1 - b2 ** self.t)
         self.master.sub_(self.lr * (mhat / (vhat.sqrt() + self.eps) + self.wd * self.master))
         shard.copy_(self.master)
-        if self.P > 1:
+        if self.P > 1 and shard.is_cuda:
+            dist.all_gather_into_tensor(self.param_flat, shard.clone(), group=self.group)
+        elif self.P > 1:
             parts = [torch.empty_like(shard) for _ in range(self.P)]
             dist.all_gather(parts, shard.clone(), group=self.group)
             self.param_flat.copy_(torch.cat(parts))

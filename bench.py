@@ -269,16 +269,17 @@ def main():
                 esz = 4 if dtype == torch.float32 else 2
                 ne = max(1, sz // esz)
                 ne_rs = max(1, ne // max(N, 1))
-                xv, yv = x.view(dtype)[:ne], y.view(dtype)[:ne]
+                xf, yf = x.view(dtype), y.view(dtype)     # slices below may be longer than ne for tiny sizes
+                xv, yv = xf[:ne], yf[:ne]
                 row = {"bytes": ne * esz, "dtype": dname}
                 cases = {
                     "allreduce": (lambda: chb.all_reduce(comm, wrap(xv), out=wrap(yv)),
                                   (lambda: dist.all_reduce(yv)) if world > 1 else None, 2 * (N - 1) / N, ne * esz),
-                    "reduce_scatter": (lambda: chb.reduce_scatter(comm, wrap(xv[:ne_rs * N]), out=wrap(yv[:ne_rs])),
-                                       (lambda: dist.reduce_scatter_tensor(yv[:ne_rs], xv[:ne_rs * N])) if world > 1 else None,
+                    "reduce_scatter": (lambda: chb.reduce_scatter(comm, wrap(xf[:ne_rs * N]), out=wrap(yf[:ne_rs])),
+                                       (lambda: dist.reduce_scatter_tensor(yf[:ne_rs], xf[:ne_rs * N])) if world > 1 else None,
                                        (N - 1) / N, ne_rs * N * esz),
-                    "allgather": (lambda: chb.all_gather(comm, wrap(xv[:ne_rs]), out=wrap(yv[:ne_rs * N])),
-                                  (lambda: dist.all_gather_into_tensor(yv[:ne_rs * N], xv[:ne_rs])) if world > 1 else None,
+                    "allgather": (lambda: chb.all_gather(comm, wrap(xf[:ne_rs]), out=wrap(yf[:ne_rs * N])),
+                                  (lambda: dist.all_gather_into_tensor(yf[:ne_rs * N], xf[:ne_rs])) if world > 1 else None,
                                   (N - 1) / N, ne_rs * N * esz),
                 }
                 for name, (ours, theirs, factor, total_bytes) in cases.items():

@@ -26,6 +26,7 @@ class _Bucket:
         self.params = []
         self.pending = 0
         self.ready_event = None
+        self.fresh = False                   # True: the next gradient of each parameter overwrites
 
 
 class DataParallel:
@@ -75,7 +76,10 @@ class DataParallel:
     # ------------------------------------------------------------------ hooks
     def _hook(self, p):
         bk, _ = self._where[p]
-        p.main_grad.add_(p.grad)            # bf16 (or fp32) gradient accumulated in fp32
+        if bk.fresh:
+            p.main_grad.copy_(p.grad)       # first micro-batch: cast only, the bucket needs no zero fill
+        else:
+            p.main_grad.add_(p.grad)        # bf16 (or fp32) gradient accumulated in fp32
         p.grad = None
         bk.pending -= 1
         if bk.pending == 0 and self.require_sync:
@@ -121,6 +125,7 @@ class DataParallel:
                 torch.cuda.current_stream().wait_stream(self.side)
         for bk in self.buckets:
             bk.pending = len(bk.params)
+            bk.fresh = False
 
     def exposed_comm_ms(self) -> float:
         """Communication time not hidden behind backward in the last step (after a synchronize)."""
@@ -129,8 +134,9 @@ class DataParallel:
         return max(0.0, self._ev_bwd_end.elapsed_time(self._ev_comm_end))
 
     def zero_grad(self):
+        """Start a new accumulation: the first gradient written to a slot replaces its content."""
         for bk in self.buckets:
-            bk.acc.zero_()
+            bk.fresh = True
 
     def no_sync(self):
         """Context manager for gradient accumulation: bucket reductions are skipped."""
@@ -144,6 +150,7 @@ class DataParallel:
                 ddp.require_sync = True
                 for bk in ddp.buckets:
                     bk.pending = len(bk.params)
+                    bk.fresh = False
 
         return _Ctx()
 

@@ -1,0 +1,190 @@
+"""Benchmark driver with the reference's command line and CSV schema.
+
+    torchrun --nproc-per-node N -m configurable_hierarchical_allreduce_algorithms_b200.bench.driver \
+        <n_iter> [--overwrite] [b=<group>] [base=<elements>] [num_nodes=<n>] [radix_increment=<step>]
+        [coll=allreduce|reduce_scatter|allgather] [dtype=int32|fp32|bf16|fp64] [op=sum|max|min]
+        [algos=radix_batch,ring,...] [reps=50] [backend=gpu|gloo] [out=<file.csv>]
+
+Like the reference's drivers (testing/custom_implementations/work_dir/all_reduce/main.cpp:111-199,
+.../all_gather/main.cpp:109-201, .../reduce_scatter/main.cpp:169-264, testing/main.cpp:146-220):
+message sizes double ``n_iter`` times starting from ``base`` elements per rank, the radix sweeps
+``k = 2 .. b-1`` in steps of ``radix_increment`` for the hierarchical algorithm, every repetition is
+checked against the library collective (``MPI_Allreduce`` there, NCCL / gloo here) and written as one
+CSV row ``algorithm_name,k,b,nprocs,send_count,time,is_correct`` (the same columns, followed by
+``dtype,op,bytes,algbw_GBs,busbw_GBs,ngpus``).  An existing file is appended to unless ``--overwrite``
+is given, and rows are flushed one by one, so an interrupted sweep resumes where it stopped.
+Correctness is AND-reduced and time MAX-reduced over ranks, as in the reference's reduce-scatter
+driver (main.cpp:79-83).  Time is device time (CUDA events) on GPUs and wall time under gloo.
+"""
+from __future__ import annotations
+
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+DT = {"int32": torch.int32, "fp32": torch.float32, "bf16": torch.bfloat16, "fp64": torch.float64, "fp16": torch.float16}
+HEADER = "algorithm_name,k,b,nprocs,send_count,time,is_correct,dtype,op,bytes,algbw_GBs,busbw_GBs,ngpus"
+BASELINES = {
+    "allreduce": ["recursive_doubling", "ring", "reduce_scatter_allgather", "k_reduce_scatter_allgather",
+                  "recursive_multiplying", "recursive_exchange"],
+    "reduce_scatter": ["recursive_halving", "recursive_doubling", "pairwise", "radix"],
+    "allgather": ["k_brucks", "ring"],
+}
+VENDOR = {"allreduce": "MPICH_allreduce", "reduce_scatter": "reduce_scatter_standard", "allgather": "allgather_standard"}
+K_ALGOS = {"radix_batch", "k_reduce_scatter_allgather", "recursive_multiplying", "recursive_exchange", "radix",
+           "k_brucks", "semi_radix_batch", "custom", "radix_block"}
+
+
+def parse(argv):
+    if not argv or not argv[0].lstrip("-").isdigit():
+        raise SystemExit(__doc__)
+    o = {"n_iter": int(argv[0]), "overwrite": False, "b": 0, "base": 1, "num_nodes": 1, "radix_increment": 1,
+         "coll": "allreduce", "dtype": "int32", "op": "sum", "algos": "", "reps": 50, "backend": "", "out": ""}
+    for a in argv[1:]:
+        if a == "--overwrite":
+            o["overwrite"] = True
+        elif "=" in a and a.split("=", 1)[0] in o:
+            k, v = a.split("=", 1)
+            o[k] = type(o[k])(v) if not isinstance(o[k], bool) else v.lower() in ("1", "true")
+        else:
+            raise SystemExit(f"Unknown parameter: {a}")
+    return o
+
+
+def make_input(rank, n_in, dtype, device):
+    # the reference's deterministic ramps (rank*count + i), folded to stay exact in every dtype
+    i = torch.arange(n_in, device=device, dtype=torch.int64)
+    return ((rank * 1009 + i * 31 + 7) % 97).to(dtype)
+
+
+def main(argv=None):
+    o = parse(list(sys.argv[1:] if argv is None else argv))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    lr = int(os.environ.get("LOCAL_RANK", "0"))
+    backend = o["backend"] or ("gpu" if torch.cuda.is_available() else "gloo")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29540")
+    if backend == "gpu":
+        torch.cuda.set_device(lr)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", lr))
+        device = torch.device("cuda", lr)
+    else:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        device = torch.device("cpu")
+    P = world
+    coll, dtype, op = o["coll"], DT[o["dtype"]], o["op"]
+    b = o["b"] or P
+    if P % b:
+        raise SystemExit(f"b={b} must divide the number of ranks ({P})")
+    esz = torch.empty((), dtype=dtype).element_size()
+    max_n = o["base"] << max(0, o["n_iter"] - 1)
+    comm = None
+    if backend == "gpu":
+        from ..parallel.comm import Communicator
+        total = max_n * P * esz
+        comm = Communicator.from_process_group(scratch_bytes=4 * total + (32 << 20), user_bytes=64 << 20)
+    from .. import all_gather, all_reduce, reduce_scatter
+    from ..parallel import gloo_exec
+
+    path = o["out"] or f"results{P}_{o['num_nodes']}_{b}.csv"
+    csv = None
+    if rank == 0:
+        fresh = o["overwrite"] or not os.path.exists(path)
+        csv = open(path, "w" if fresh else "a")
+        if fresh:
+            csv.write(HEADER + "\n")
+    redop = {"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN}[op]
+    algos = [a for a in o["algos"].split(",") if a] or (["radix_batch"] + BASELINES[coll])
+
+    def run_one(name, algo, k, bb, n, x, ref):
+        """`reps` timed, checked repetitions of one configuration."""
+        send_count = n
+        kk, gb = (k or 2), (bb or 1)       # the CSV keeps 0 for "not applicable", the generators need valid values
+        for _ in range(o["reps"]):
+            if backend == "gpu":
+                dist.barrier()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                if algo == "vendor":
+                    y = vendor(x)
+                elif coll == "allreduce":
+                    y = all_reduce(comm, x, op=op, algo=algo, k=kk, b=gb)
+                elif coll == "reduce_scatter":
+                    y = reduce_scatter(comm, x, op=op, algo=algo, k=kk, b=gb)
+                else:
+                    y = all_gather(comm, x, algo=algo, k=kk, b=gb)
+                e1.record()
+                torch.cuda.synchronize()
+                t = e0.elapsed_time(e1) * 1e-3
+            else:
+                dist.barrier()
+                t0 = time.perf_counter()
+                if algo == "vendor":
+                    y = vendor(x)
+                else:
+                    count = n * P if coll == "allreduce" else n
+                    y = gloo_exec.run_collective(coll, algo, x, count, kk, gb, op=op)
+                dist.barrier()
+                t = time.perf_counter() - t0
+            ok = torch.equal(y, ref) if not dtype.is_floating_point else bool(
+                torch.allclose(y.double(), ref.double(), rtol=1e-5 if dtype != torch.bfloat16 else 2e-2, atol=1e-5 * P))
+            flag = torch.tensor([1 if ok else 0, 0], device=device, dtype=torch.float64)
+            tt = torch.tensor([t], device=device, dtype=torch.float64)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            if rank == 0:
+                t = float(tt.item())
+                total = n * P * esz
+                factor = 2 * (P - 1) / P if coll == "allreduce" else (P - 1) / P
+                csv.write(f"{name},{k},{bb},{P},{send_count},{t:.9f},{int(flag[0].item())},{o['dtype']},{op},{total},"
+                          f"{total / t / 1e9:.4f},{total / t / 1e9 * factor:.4f},{P if backend == 'gpu' else 0}\n")
+                csv.flush()
+
+    def vendor(x):
+        if coll == "allreduce":
+            y = x.clone()
+            dist.all_reduce(y, op=redop)
+            return y
+        if coll == "reduce_scatter":
+            if backend == "gpu":
+                y = torch.empty(x.numel() // P, dtype=x.dtype, device=device)
+                dist.reduce_scatter_tensor(y, x, op=redop)
+                return y
+            y = x.clone()
+            dist.all_reduce(y, op=redop)
+            n = x.numel() // P
+            return y[rank * n:(rank + 1) * n].clone()
+        parts = [torch.empty_like(x) for _ in range(P)]
+        dist.all_gather(parts, x)
+        return torch.cat(parts)
+
+    for i in range(o["n_iter"]):
+        n = o["base"] << i                                   # elements per rank
+        n_in = n if coll == "allgather" else n * P
+        x = make_input(rank, n_in, dtype, device)
+        ref = vendor(x)
+        for algo in algos:
+            name = f"{coll}_{algo}" if algo != "radix_batch" else {"allreduce": "all_reduce_radix_batch", "reduce_scatter": "reduce_scatter_radix_batch", "allgather": "allgather_radix_batch"}[coll]
+            if algo in K_ALGOS:
+                hi = max(3, b) if algo == "radix_batch" else max(3, P)
+                for k in range(2, hi, max(1, o["radix_increment"])):
+                    run_one(name, algo, k, b if algo in ("radix_batch", "semi_radix_batch", "custom", "radix_block") else 0, n, x, ref)
+            else:
+                run_one(name, algo, 0, 0, n, x, ref)
+        run_one(VENDOR[coll], "vendor", 0, 0, n, x, ref)
+    if csv:
+        csv.close()
+    if comm:
+        comm.check()
+        comm.close()
+    dist.destroy_process_group()
+    return path
+
+
+if __name__ == "__main__":
+    main()

@@ -69,10 +69,11 @@ class ClockSampler:
                     rs = pynvml.nvmlDeviceGetCurrentClocksEventReasons(h)
                 except Exception:  # noqa: BLE001
                     rs = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-                row = [str(self.idx), str(sm), str(mx), "", ""]
+                row = [str(self.idx), str(sm), str(mx), "", "", time.perf_counter()]
+                ts = row.pop()
                 row += ["Active" if rs & bits[n] else "Not Active"
                         for n in ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")]
-                self.rows.append(row)
+                self.rows.append(row + [ts])
                 self._stop.wait(0.01)
             return
         except Exception:  # noqa: BLE001
@@ -82,7 +83,7 @@ class ClockSampler:
                 out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
                                       "-i", str(self.idx)], capture_output=True, text=True, timeout=5).stdout
                 for line in out.strip().splitlines():
-                    self.rows.append([c.strip() for c in line.split(",")])
+                    self.rows.append([c.strip() for c in line.split(",")][:9] + [time.perf_counter()])
             except Exception:  # noqa: BLE001
                 pass
             self._stop.wait(0.2)
@@ -96,20 +97,34 @@ class ClockSampler:
         self._stop.set()
         self._t.join(timeout=6)
 
+    def mark(self, t0: float, t1: float):
+        """Timed region [t0, t1] (perf_counter): summary() prefers the samples inside it."""
+        self.window = (t0, t1)
+
     def summary(self) -> dict:
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        rows = self.rows
+        w = getattr(self, "window", None)
+        where = "timed region"
+        if w:
+            inside = [r for r in rows if w[0] <= r[-1] <= w[1]]
+            if inside:
+                rows = inside
+            else:   # region shorter than the sampling period: the samples taken under the preceding warm-up load
+                rows = [r for r in rows if r[-1] <= w[1]][-20:] or rows
+                where = "warm-up immediately before the timed region (region shorter than one sampling period)"
+        for r in rows:
             try:
                 sm.append(float(r[1]))
                 mx.append(float(r[2]))
             except (ValueError, IndexError):
                 continue
             for name, v in zip(names, r[5:9]):
-                if v.lower().startswith("active"):
+                if str(v).lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "sampled_during": where}
 
 
 # ----------------------------------------------------------------------------- helpers
@@ -236,11 +251,18 @@ def main():
         tol = 0.0
     correct = err <= tol
 
-    for _ in range(W):
-        step()
-    l0 = comm.launches
     with ClockSampler(local_rank) as cs:
+        t_end = time.perf_counter() + 1.0
+        i = 0
+        while i < W or (time.perf_counter() < t_end and not cs.rows):   # warm-up, at least until the sampler is live
+            step()
+            i += 1
+            if i % 16 == 0:
+                torch.cuda.synchronize()
+        l0 = comm.launches
+        tw0 = time.perf_counter()
         ms = device_time_ms(step, K, None, barrier)
+        cs.mark(tw0, time.perf_counter())
     launches = comm.launches - l0
     ms = max_over_ranks(ms)
     comm.check()

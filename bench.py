@@ -252,13 +252,14 @@ def main():
     correct = err <= tol
 
     with ClockSampler(local_rank) as cs:
-        t_end = time.perf_counter() + 1.0
-        i = 0
-        while i < W or (time.perf_counter() < t_end and not cs.rows):   # warm-up, at least until the sampler is live
+        for _ in range(W):
             step()
-            i += 1
-            if i % 16 == 0:
-                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        t_end = time.perf_counter() + 2.0
+        while not cs.rows and time.perf_counter() < t_end:     # sampler start-up (no collectives here:
+            time.sleep(0.01)                                   # every rank must issue the same number of calls)
+        for _ in range(max(W, 50)):                            # load right before the timed region
+            step()
         l0 = comm.launches
         tw0 = time.perf_counter()
         ms = device_time_ms(step, K, None, barrier)

@@ -57,6 +57,9 @@ struct World {
   char* work[kMaxRanks];                // symmetric scratch of every rank (peer-mapped)
   char* ll[kMaxRanks];                  // flagged-line inbox of every rank (peer-mapped)
   Ctrl* ctrl[kMaxRanks];                // control blocks (valid for local ranks only)
+  unsigned long long* trace[kMaxRanks]; // optional per-round %globaltimer stamps of local ranks (null = off)
+  int trace_rounds;                     // capacity of a trace buffer in rounds
+  int reserved2;
 };
 
 // ------------------------------------------------------------------ PTX helpers

@@ -233,6 +233,8 @@ interp_kernel(World w, const char* __restrict__ blob, IoTable io, int op, float 
     __syncthreads();
     ok = s_ok != 0;
     if (!ok) break;
+    unsigned long long* tr = w.trace[rank];
+    if (tr && cta == 0 && tid == 0 && t < w.trace_rounds) tr[2 * t] = globaltimer_ns();   // waits of round t satisfied
     for (int s = R.step_begin; s < R.step_end; ++s) {
       const DevStep st = steps[s];
       const bool small = st.count * (long long)sizeof(T) < kSmallStepBytes;
@@ -245,6 +247,7 @@ interp_kernel(World w, const char* __restrict__ blob, IoTable io, int op, float 
     }
     ok = rank_barrier(c, nct, gen, w.timeout_ns, rank, t);
     if (!ok) break;
+    if (tr && cta == 0 && tid == 0 && t < w.trace_rounds) tr[2 * t + 1] = globaltimer_ns();  // round t complete on this rank
     if (cta == 0) {
       const int n = R.sig_end - R.sig_begin;
       for (int i = tid; i < n; i += blockDim.x) {

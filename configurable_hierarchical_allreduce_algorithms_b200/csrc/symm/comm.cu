@@ -123,6 +123,7 @@ void chb_comm_destroy(chb_comm* c) {
   chb_collective_cache_clear(c);
   for (auto& kv : c->blobs) cudaFree(kv.second);
   if (c->ctrl) cudaFree(c->ctrl);
+  if (c->trace) cudaFree(c->trace);
   delete c;
 }
 
@@ -192,6 +193,35 @@ int chb_comm_clear_error(chb_comm* c, cudaStream_t stream) {
   if (!c) return CHB_ERR_ARG;
   reset_ctrl_kernel<<<1, 32, 0, stream>>>(c->ctrl, c->nlocal);
   return cudaGetLastError() == cudaSuccess ? CHB_SUCCESS : CHB_ERR_CUDA;
+}
+
+// Per-round tracing of program launches: for every local rank the interpreter
+// stamps %globaltimer when round t may start (its waits are satisfied) and when
+// the round is complete on that rank.  The counterpart of the reference's
+// optional per-phase MPI_Wtime prints under DEBUG_MODE
+// (testing/custom_implementations/work_dir/all_reduce/all_reduce_radix_batch.cpp:228-232,480-489).
+// rounds == 0 switches tracing off.
+int chb_comm_trace_enable(chb_comm* c, int rounds) {
+  if (!c || rounds < 0) return CHB_ERR_ARG;
+  cudaDeviceSynchronize();
+  if (c->trace) { cudaFree(c->trace); c->trace = nullptr; }
+  c->trace_rounds = rounds;
+  for (int p = 0; p < kMaxRanks; ++p) c->world.trace[p] = nullptr;
+  c->world.trace_rounds = rounds;
+  if (rounds == 0) return CHB_SUCCESS;
+  const size_t per = (size_t)rounds * 2;
+  if (cudaMalloc(&c->trace, per * 8 * (size_t)c->nlocal) != cudaSuccess) return CHB_ERR_NO_MEM;
+  cudaMemset(c->trace, 0, per * 8 * (size_t)c->nlocal);
+  for (int l = 0; l < c->nlocal; ++l) c->world.trace[c->rank + l] = c->trace + per * l;
+  return cudaDeviceSynchronize() == cudaSuccess ? CHB_SUCCESS : CHB_ERR_CUDA;
+}
+// Copies 2 * rounds stamps (start, end per round, ns) of a local rank after synchronising the stream.
+int chb_comm_trace_read(chb_comm* c, int local_index, unsigned long long* out, int rounds, cudaStream_t stream) {
+  if (!c || !out || !c->trace || local_index < 0 || local_index >= c->nlocal || rounds > c->trace_rounds) return CHB_ERR_ARG;
+  if (cudaStreamSynchronize(stream) != cudaSuccess) return CHB_ERR_CUDA;
+  const size_t per = (size_t)c->trace_rounds * 2;
+  return cudaMemcpy(out, c->trace + per * local_index, (size_t)rounds * 16, cudaMemcpyDeviceToHost) == cudaSuccess
+             ? CHB_SUCCESS : CHB_ERR_CUDA;
 }
 
 // ---- cudaIpc helpers: one allocation per rank, exported as a 64-byte handle

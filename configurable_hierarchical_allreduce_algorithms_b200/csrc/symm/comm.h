@@ -30,6 +30,8 @@ struct chb_comm {
   std::vector<char*> heap;      // [P] peer-mapped base pointers
   char* mc_heap = nullptr;      // multicast alias of the heap (NVLS), or null
   chb::Ctrl* ctrl = nullptr;    // [nlocal] control blocks, device memory owned by the comm
+  unsigned long long* trace = nullptr;  // [nlocal][2 * trace_rounds] round stamps, or null
+  int trace_rounds = 0;
   chb::World world{};           // device view handed to kernels
   unsigned long long timeout_ns = 10ull * 1000 * 1000 * 1000;
   int max_ctas = 0;             // co-resident CTA budget per rank

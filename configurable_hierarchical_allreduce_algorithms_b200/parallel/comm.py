@@ -38,6 +38,8 @@ N.optional("chb_comm_scratch_ptr", vp, [vp, i32])
 N.optional("chb_barrier", i32, [vp, u64, vp])
 N.optional("chb_comm_status", i32, [vp, i32, C.POINTER(u64), vp])
 N.optional("chb_comm_clear_error", i32, [vp, vp])
+N.optional("chb_comm_trace_enable", i32, [vp, i32])
+N.optional("chb_comm_trace_read", i32, [vp, i32, C.POINTER(u64), i32, vp])
 N.optional("chb_ipc_alloc", i32, [C.c_size_t, C.POINTER(vp), vp])
 N.optional("chb_ipc_open", i32, [vp, C.POINTER(vp)])
 N.optional("chb_ipc_close", i32, [vp])
@@ -323,6 +325,19 @@ class Communicator:
                                                       f"expected {d['expected']}, seen {d['seen']})")
             if d["rc"]:
                 self._err(d["rc"])
+
+    def enable_trace(self, rounds: int = 64):
+        """Record per-round device timestamps of program launches (0 switches it off)."""
+        self._err(N.lib().chb_comm_trace_enable(self._h, rounds))
+        self._trace_rounds = rounds
+
+    def read_trace(self, nrounds: int, local_index: int = 0, stream=None) -> list[tuple[float, float]]:
+        """(start_us, end_us) of every round of the last program launch, relative to the first round's start."""
+        n = min(nrounds, getattr(self, "_trace_rounds", 0))
+        buf = (u64 * (2 * n))()
+        self._err(N.lib().chb_comm_trace_read(self._h, local_index, buf, n, _stream_ptr(stream)))
+        t0 = buf[0] if n else 0
+        return [((buf[2 * i] - t0) / 1e3, (buf[2 * i + 1] - t0) / 1e3) for i in range(n)]
 
     def clear_error(self, stream=None):
         self._err(N.lib().chb_comm_clear_error(self._h, _stream_ptr(stream)))

@@ -192,3 +192,19 @@ class MasterAdamW:
                     self._src.append(flat[off:off + p.numel()].view_as(p))
                     off += (p.numel() + 3) // 4 * 4
         torch._foreach_copy_(self._dst, self._src)
+
+    # ------------------------------------------------------------------ checkpoint / resume
+    def state_dict(self) -> dict:
+        return {"opt": self.opt.state_dict(), "masters": [m.detach().cpu().clone() for m in self.masters]}
+
+    @torch.no_grad()
+    def load_state_dict(self, sd: dict) -> None:
+        for m, saved in zip(self.masters, sd["masters"]):
+            m.copy_(saved)
+        self.opt.load_state_dict(sd["opt"])
+        for bk, flat in zip(self.ddp.buckets, self.masters):
+            flat.grad = bk.red
+            off = 0
+            for p in bk.params:
+                p.copy_(flat[off:off + p.numel()].view_as(p))
+                off += (p.numel() + 3) // 4 * 4

@@ -103,3 +103,37 @@ class ShardedAdamW:
             parts = [torch.empty_like(shard) for _ in range(self.P)]
             dist.all_gather(parts, shard.clone(), group=self.group)
             self.param_flat.copy_(torch.cat(parts))
+
+    # ------------------------------------------------------------------ checkpoint / resume
+    def state_dict(self) -> dict:
+        """This rank's shard of the optimizer state (save one file per rank with ``torch.save``)."""
+        return {"rank": self.rank, "world": self.P, "n": self.n, "step": self.t,
+                "master": self.master.detach().cpu().clone(), "exp_avg": self.exp_avg.detach().cpu().clone(),
+                "exp_avg_sq": self.exp_avg_sq.detach().cpu().clone(),
+                "hyper": {"lr": self.lr, "betas": self.betas, "eps": self.eps, "weight_decay": self.wd}}
+
+    @torch.no_grad()
+    def load_state_dict(self, sd: dict) -> None:
+        """Restore a shard saved by :meth:`state_dict` with the same world size; the bf16 parameter
+        shard is rebuilt from the fp32 master (call ``step``-free ``sync_params`` afterwards)."""
+        if sd["world"] != self.P or sd["rank"] != self.rank or sd["n"] != self.n:
+            raise ValueError("optimizer shard was saved for a different rank / world size / model")
+        self.t = int(sd["step"])
+        self.master.copy_(sd["master"])
+        self.exp_avg.copy_(sd["exp_avg"])
+        self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+        lo = self.rank * self.n
+        self.param_flat[lo:lo + self.n].copy_(self.master)
+
+    @torch.no_grad()
+    def sync_params(self, stream=None) -> None:
+        """Allgather the parameter shards (after ``load_state_dict``)."""
+        lo = self.rank * self.n
+        shard = self.param_flat[lo:lo + self.n]
+        if self.comm is not None:
+            collectives.all_gather(self.comm, shard, out=self.param_flat, algo=self.ag_algo, k=self.ag_k,
+                                   b=self.ag_b, stream=stream)
+        elif self.P > 1:
+            parts = [torch.empty_like(shard) for _ in range(self.P)]
+            dist.all_gather(parts, shard.clone(), group=self.group)
+            self.param_flat.copy_(torch.cat(parts))

@@ -255,3 +255,20 @@ def test_barrier(comms):
         comm.barrier()
     comm.check()
     assert comm.status(0)["code"] == 0
+
+
+def test_round_trace(comms):
+    P = 8
+    comm = comms(P)
+    comm.enable_trace(32)
+    ins = make_inputs(P, P * 4096, torch.float32)
+    prog = comm.program("allreduce", "radix_batch", P * 4096, 2, 4)
+    chb.all_reduce(comm, ins, algo="radix_batch", k=2, b=4)
+    for r in (0, 5):
+        tr = comm.read_trace(prog.nrounds, r)
+        assert len(tr) == prog.nrounds
+        assert all(e >= s for s, e in tr), tr
+        assert all(tr[i + 1][0] >= tr[i][1] - 1e-3 for i in range(len(tr) - 1)), tr   # rounds are ordered
+    comm.enable_trace(0)
+    chb.all_reduce(comm, ins, algo="radix_batch", k=2, b=4)
+    comm.check()

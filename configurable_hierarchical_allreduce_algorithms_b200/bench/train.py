@@ -23,7 +23,7 @@ import torch.distributed as dist
 
 from ..models.gpt import GPT, GPTConfig
 from ..parallel.comm import Communicator
-from ..parallel.ddp import DataParallel, MasterAdamW
+from ..parallel.ddp import DataParallel, FusedMasterAdamW, MasterAdamW
 from ..parallel.zero import ShardedAdamW
 
 
@@ -74,7 +74,7 @@ def main(argv=None):
         ddp = DataParallel(model, comm=comm if ours else None, algo=args.algo, k=args.k, b=args.b)
         if not ours:
             ddp.cuda = False     # library collectives on CUDA tensors through torch.distributed
-        opt = MasterAdamW(ddp)
+        opt = FusedMasterAdamW(ddp) if ours else MasterAdamW(ddp)
     else:
         opt = ShardedAdamW(model, comm=comm if ours else None, ag_algo=args.algo, ag_k=args.k, ag_b=args.b)
         ddp = None

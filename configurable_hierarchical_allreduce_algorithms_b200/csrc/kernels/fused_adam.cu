@@ -105,6 +105,30 @@ rs_adam_kernel(World w, AdamIo io, long long n, AdamHyper h, const char* mc_grad
   rank_exit(c, gridDim.x, [&](Ctrl* cc) { cc->bar_seq = seq + 2ull; });
 }
 
+// Plain (unsharded) variant for the data-parallel path: the gradient has
+// already been allreduced; AdamW on the fp32 master, bf16 copy of the result.
+__global__ void __launch_bounds__(kAdamThreads)
+adam_flat_kernel(const float* __restrict__ grad, float* master, float* m, float* v, __nv_bfloat16* param,
+                 long long n, AdamHyper h) {
+  const long long nvec = n / 4;
+  const long long TT = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += TT) {
+    const float4 g = reinterpret_cast<const float4*>(grad)[i];
+    float4 ww = reinterpret_cast<float4*>(master)[i], m1 = reinterpret_cast<float4*>(m)[i],
+           v1 = reinterpret_cast<float4*>(v)[i];
+    const float s = h.grad_scale;
+    __nv_bfloat16 o[4];
+    o[0] = __float2bfloat16_rn(adam_one(g.x * s, ww.x, m1.x, v1.x, h));
+    o[1] = __float2bfloat16_rn(adam_one(g.y * s, ww.y, m1.y, v1.y, h));
+    o[2] = __float2bfloat16_rn(adam_one(g.z * s, ww.z, m1.z, v1.z, h));
+    o[3] = __float2bfloat16_rn(adam_one(g.w * s, ww.w, m1.w, v1.w, h));
+    reinterpret_cast<float4*>(master)[i] = ww;
+    reinterpret_cast<float4*>(m)[i] = m1;
+    reinterpret_cast<float4*>(v)[i] = v1;
+    reinterpret_cast<uint2*>(param)[i] = *reinterpret_cast<uint2*>(o);
+  }
+}
+
 }  // namespace chb
 
 using namespace chb;
@@ -164,6 +188,20 @@ int chb_rs_adam(chb_comm* c, const void* const* grad, void* const* master, void*
                                 : cudaLaunchKernel((const void*)rs_adam_kernel, grid, block, args, 0, stream);
   if (e != cudaSuccess) { c->last_error = std::string("rs_adam launch failed: ") + cudaGetErrorString(e); return CHB_ERR_CUDA; }
   return CHB_SUCCESS;
+}
+
+// AdamW on a flat fp32 master with a bf16 copy of the result; n % 4 == 0, 16-byte aligned buffers.
+int chb_adam_flat(const void* grad, void* master, void* m, void* v, void* param_bf16, long long n,
+                  const float* hyper, cudaStream_t stream) {
+  if (!grad || !master || !m || !v || !param_bf16 || !hyper || n < 0 || (n % 4)) return CHB_ERR_ARG;
+  if (((uintptr_t)grad | (uintptr_t)master | (uintptr_t)m | (uintptr_t)v) & 15u || ((uintptr_t)param_bf16 & 7u)) return CHB_ERR_ARG;
+  if (n == 0) return CHB_SUCCESS;
+  AdamHyper h{hyper[0], hyper[1], hyper[2], hyper[3], hyper[4], hyper[5], hyper[6], hyper[7]};
+  long long blocks = (n / 4 + kAdamThreads - 1) / kAdamThreads;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  adam_flat_kernel<<<(unsigned)blocks, kAdamThreads, 0, stream>>>((const float*)grad, (float*)master, (float*)m, (float*)v,
+                                                                   (__nv_bfloat16*)param_bf16, n, h);
+  return cudaGetLastError() == cudaSuccess ? CHB_SUCCESS : CHB_ERR_CUDA;
 }
 
 }  // extern "C"

@@ -16,6 +16,20 @@ N.optional("chb_rs_adam", i32, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
                                 C.c_longlong, C.POINTER(f32), i32, i32, vp])
 
 
+N.optional("chb_adam_flat", i32, [vp, vp, vp, vp, vp, C.c_longlong, C.POINTER(f32), vp])
+
+
+def adam_flat(grad, master, exp_avg, exp_avg_sq, param_bf16, *, lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
+              step=1, grad_scale=1.0, stream=None):
+    """AdamW on a flat fp32 master tensor fed by a flat fp32 gradient; writes the bf16 parameters."""
+    n = master.numel()
+    hyper = (f32 * 8)(lr, betas[0], betas[1], eps, weight_decay, 1.0 - betas[0] ** step, 1.0 - betas[1] ** step, grad_scale)
+    rc = N.lib().chb_adam_flat(grad.data_ptr(), master.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(),
+                               param_bf16.data_ptr(), n, hyper, _stream_ptr(stream))
+    if rc:
+        raise RuntimeError(f"chb_adam_flat failed with code {rc}")
+
+
 def _lst(x):
     return [x] if isinstance(x, torch.Tensor) else list(x)
 

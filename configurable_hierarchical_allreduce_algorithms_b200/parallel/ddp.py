@@ -158,6 +158,49 @@ class DataParallel:
         return [(p, p.reduced_grad) for bk in self.buckets for p in bk.params]
 
 
+class FusedMasterAdamW:
+    """Same update as :class:`MasterAdamW` in one kernel per bucket: reduced fp32
+    gradient -> AdamW on the fp32 master -> bf16 parameters, which are re-homed in
+    one flat bf16 buffer per bucket (``csrc/kernels/fused_adam.cu``).  CUDA, bf16 parameters."""
+
+    def __init__(self, ddp: DataParallel, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1):
+        from ..ops import fused
+        self._fused = fused
+        self.ddp, self.lr, self.betas, self.eps, self.wd, self.t = ddp, lr, betas, eps, weight_decay, 0
+        self.state = []
+        for bk in ddp.buckets:
+            flat_p = torch.zeros(bk.numel, dtype=torch.bfloat16, device=bk.red.device)
+            master = torch.zeros_like(bk.red)
+            off = 0
+            for p in bk.params:
+                assert p.dtype == torch.bfloat16, "the fused optimizer keeps bf16 parameters"
+                flat_p[off:off + p.numel()].copy_(p.detach().reshape(-1))
+                master[off:off + p.numel()].copy_(p.detach().reshape(-1).float())
+                p.data = flat_p[off:off + p.numel()].view_as(p)
+                off += (p.numel() + 3) // 4 * 4
+            self.state.append((bk, flat_p, master, torch.zeros_like(master), torch.zeros_like(master)))
+
+    @torch.no_grad()
+    def step(self):
+        self.t += 1
+        for bk, flat_p, master, m, v in self.state:
+            self._fused.adam_flat(bk.red, master, m, v, flat_p, lr=self.lr, betas=self.betas, eps=self.eps,
+                                  weight_decay=self.wd, step=self.t)
+
+    def state_dict(self) -> dict:
+        return {"step": self.t, "buckets": [(ms.cpu().clone(), m.cpu().clone(), v.cpu().clone())
+                                            for _, _, ms, m, v in self.state]}
+
+    @torch.no_grad()
+    def load_state_dict(self, sd: dict) -> None:
+        self.t = int(sd["step"])
+        for (_, flat_p, master, m, v), (sm, s1, s2) in zip(self.state, sd["buckets"]):
+            master.copy_(sm)
+            m.copy_(s1)
+            v.copy_(s2)
+            flat_p.copy_(master)
+
+
 class MasterAdamW:
     """AdamW on fp32 master copies fed by the reduced fp32 gradients of a
     :class:`DataParallel`; the (bf16) model parameters are refreshed from the

@@ -63,3 +63,20 @@ def test_reduce_scatter_adam_matches_torch(cuda, P):
         torch.testing.assert_close(torch.cat(params).float(), ref_w.detach().bfloat16().float(), rtol=1e-2, atol=1e-2)
     comm.check()
     comm.close()
+
+
+def test_adam_flat_matches_torch(cuda):
+    n = 4 * 5003
+    g = torch.Generator(device="cuda").manual_seed(5)
+    w0 = torch.randn(n, generator=g, device="cuda")
+    master, m, v = w0.clone(), torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    pb = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    ref = torch.nn.Parameter(w0.clone())
+    opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1)
+    for step in (1, 2, 3):
+        grad = torch.randn(n, generator=g, device="cuda")
+        fused.adam_flat(grad, master, m, v, pb, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1, step=step)
+        ref.grad = grad.clone()
+        opt.step()
+        torch.testing.assert_close(master, ref.detach(), rtol=2e-5, atol=2e-6)
+        torch.testing.assert_close(pb.float(), ref.detach().bfloat16().float(), rtol=1e-2, atol=1e-2)

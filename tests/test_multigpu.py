@@ -98,6 +98,43 @@ def _worker(rank, P, port, backend, q):
             chb.all_reduce(comm, xb, out=yb, algo="nvls")
             close(yb, torch.stack([x.double() for x in insb]).sum(0), torch.bfloat16)
             notes.append("nvls kernels ok")
+        # ---- the reference-compatible C entry points, called through their exported symbols
+        import ctypes as C
+        from configurable_hierarchical_allreduce_algorithms_b200 import _native as NN
+        L = C.CDLL(str(NN._LIB_PATH))
+        vp, i32, i64 = C.c_void_p, C.c_int, C.c_int64
+        L.chb_set_stream.argtypes = [vp]
+        L.chb_set_stream(torch.cuda.current_stream().cuda_stream)
+        cnt = 4096 * P
+        a = _inp(rank, cnt, torch.float32)
+        full = torch.stack([_inp(r, cnt, torch.float32).double() for r in range(P)]).sum(0)
+        o = torch.zeros(cnt, device="cuda")
+        L.all_reduce_radix_batch.argtypes = [vp, vp, i32, i32, i32, vp, i32, i32]
+        assert L.all_reduce_radix_batch(a.data_ptr(), o.data_ptr(), cnt, NN.F32, NN.SUM, comm.handle, 2, divs[-1]) == 0
+        close(o, full, torch.float32)
+        L.MPICH_Allreduce_ring.argtypes = [vp, vp, i32, i32, i32, vp]
+        o.zero_()
+        assert L.MPICH_Allreduce_ring(a.data_ptr(), o.data_ptr(), cnt, NN.F32, NN.SUM, comm.handle) == 0
+        close(o, full, torch.float32)
+        L.reduce_scatter_radix_batch.argtypes = [vp, vp, i64, i32, i32, vp, i32, i32]
+        inplace = a.clone()
+        assert L.reduce_scatter_radix_batch(C.c_void_p(-1), inplace.data_ptr(), 4096, NN.F32, NN.SUM, comm.handle, 2, 1) == 0   # CHB_IN_PLACE
+        close(inplace[:4096], full[rank * 4096:(rank + 1) * 4096], torch.float32)
+        L.allgather_radix_batch.argtypes = [vp, i32, i32, vp, vp, i32, i32]
+        og = torch.zeros(cnt, device="cuda")
+        assert L.allgather_radix_batch(a.data_ptr(), 4096, NN.F32, og.data_ptr(), comm.handle, 2, divs[-1]) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(og, torch.cat([_inp(r, cnt, torch.float32)[:4096] for r in range(P)]))
+        assert L.all_reduce_radix_batch(a.data_ptr(), o.data_ptr(), cnt - 1, NN.F32, NN.SUM, comm.handle, 2, 1) == NN.ERR_COUNT
+        # ---- fp8 block-scaled wire reduce-scatter against the exact result
+        from configurable_hierarchical_allreduce_algorithms_b200.ops import fused
+        nb = 128 * 512
+        ab = _inp(rank, nb * P, torch.bfloat16)
+        exact = torch.stack([_inp(r, nb * P, torch.bfloat16).double() for r in range(P)]).sum(0)[rank * nb:(rank + 1) * nb]
+        got = fused.reduce_scatter_fp8(comm, ab)
+        rel = (got.double() - exact).norm() / exact.norm()
+        assert rel < 0.05, rel
+        notes.append(f"fp8 wire rel err {float(rel):.4f}")
         for _ in range(20):   # back-to-back mixed launches
             chb.all_reduce(comm, xs, out=ys)
             chb.all_reduce(comm, xs[:256], out=ys[:256])

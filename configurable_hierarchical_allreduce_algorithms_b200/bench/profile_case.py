@@ -5,6 +5,10 @@ on it): a few launches of one kernel, inputs larger than L2, about a GB held.
       interp_ar  8 emulated ranks, allreduce radix_batch k=2 b=1 on symmetric buffers (program interpreter)
       interp_kb  same with k=2 b=4 (hierarchical schedule)
       ll_ar      8 emulated ranks, one-shot flagged-line allreduce of 64 KiB
+      ll2_ar     8 emulated ranks, two-shot flagged-line allreduce of 1 MiB
+      fp8_rs     4 emulated ranks, fp8 block-scaled wire reduce-scatter, --mib MiB of bf16 per rank
+      adam_flat  AdamW on a flat fp32 master of --mib MiB with bf16 parameter copy (data-parallel optimizer)
+      noalloc    allocation-free one-shot allreduce, 8 ranks x 8 KiB
       copy1      single rank, allreduce of --mib MiB (degenerates to the local copy, HBM bound)
       rs_adam    4 emulated ranks, reduce-scatter + AdamW on a shard of --mib MiB of gradients per rank
 Prints the CUDA-event time per launch so the same command line can be checked without a profiler first.
@@ -28,16 +32,18 @@ def main():
     a = ap.parse_args()
     torch.cuda.set_device(0)
     n = (a.mib << 20) // 4
-    if a.case in ("interp_ar", "interp_kb", "ll_ar"):
+    if a.case in ("interp_ar", "interp_kb", "ll_ar", "ll2_ar"):
         P = 8
         if a.case == "ll_ar":
             n = (64 << 10) // 4
+        if a.case == "ll2_ar":
+            n = (1 << 20) // 4
         comm = Communicator.emulated(P, scratch_bytes=8 << 20, user_bytes=2 * n * 4 + (1 << 20))
         xs, ys = comm.empty(n, torch.float32), comm.empty(n, torch.float32)
         for i, x in enumerate(xs):
             x.copy_(torch.rand(n, device="cuda") + i)
         kw = {"interp_ar": dict(algo="radix_batch", k=2, b=1), "interp_kb": dict(algo="radix_batch", k=2, b=4),
-              "ll_ar": dict(algo="ll")}[a.case]
+              "ll_ar": dict(algo="ll"), "ll2_ar": dict(algo="ll2")}[a.case]
         fn = lambda: all_reduce(comm, xs, out=ys, **kw)
         nbytes = n * 4
     elif a.case == "copy1":
@@ -59,6 +65,37 @@ def main():
         p = [torch.zeros(shard, dtype=torch.bfloat16, device="cuda") for _ in range(P)]
         fn = lambda: fused.reduce_scatter_adam(comm, grads, w, m, v, p, lr=1e-3, step=1, grad_scale=0.25, use_multimem=False)
         nbytes = shard * P * 4
+    elif a.case == "fp8_rs":
+        P = 4
+        nb = (a.mib << 20) // 2 // P // 128 * 128
+        comm = Communicator.emulated(P, scratch_bytes=(a.mib << 20) + (1 << 20), user_bytes=1 << 20)
+        xs = [torch.randn(nb * P, device="cuda").bfloat16() for _ in range(P)]
+        ys = [torch.empty(nb, dtype=torch.bfloat16, device="cuda") for _ in range(P)]
+        fn = lambda: fused.reduce_scatter_fp8(comm, xs, out=ys, scale=0.25)
+        nbytes = nb * P * 2
+    elif a.case == "adam_flat":
+        comm = Communicator.emulated(1, scratch_bytes=1 << 20, user_bytes=1 << 20)
+        g, w = torch.randn(n, device="cuda"), torch.randn(n, device="cuda")
+        m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+        pb = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+        fn = lambda: fused.adam_flat(g, w, m, v, pb, lr=1e-3, step=1)
+        nbytes = n * 4
+    elif a.case == "noalloc":
+        import ctypes as C
+        from .. import _native as N
+        from ..parallel.comm import DTYPES, OPS
+        P, n = 8, 2048
+        comm = Communicator.emulated(1, scratch_bytes=1 << 20, user_bytes=1 << 20)
+        xs = [torch.randn(n, device="cuda") for _ in range(P)]
+        ys = [torch.empty(n, device="cuda") for _ in range(P)]
+        L = C.CDLL(str(N._LIB_PATH))
+        L.chb_allreduce_oneshot_noalloc.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                                    C.c_int64, C.c_float, C.c_void_p, C.c_char_p, C.c_int]
+        ip = (C.c_void_p * P)(*[t.data_ptr() for t in xs])
+        op_ = (C.c_void_p * P)(*[t.data_ptr() for t in ys])
+        fn = lambda: L.chb_allreduce_oneshot_noalloc(P, DTYPES[torch.float32], OPS["sum"], ip, op_, n, 1.0,
+                                                     torch.cuda.current_stream().cuda_stream, None, 0)
+        nbytes = n * 4
     else:
         raise SystemExit(f"unknown case {a.case}")
     for _ in range(2):

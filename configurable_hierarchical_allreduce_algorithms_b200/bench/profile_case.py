@@ -38,7 +38,7 @@ def main():
             n = (64 << 10) // 4
         if a.case == "ll2_ar":
             n = (1 << 20) // 4
-        comm = Communicator.emulated(P, scratch_bytes=8 << 20, user_bytes=2 * n * 4 + (1 << 20))
+        comm = Communicator.emulated(P, scratch_bytes=n * 4 + (8 << 20), user_bytes=2 * n * 4 + (1 << 20))
         xs, ys = comm.empty(n, torch.float32), comm.empty(n, torch.float32)
         for i, x in enumerate(xs):
             x.copy_(torch.rand(n, device="cuda") + i)

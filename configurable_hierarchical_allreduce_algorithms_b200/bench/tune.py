@@ -152,6 +152,21 @@ def main(argv=None):
                                  total / (t * 1e-3) / 1e9, total / (t * 1e-3) / 1e9 * factor, t * 1e3, P, c])
                     if best is None or t < best[0]:
                         best = (t, a, k, b, c)
+                if coll == "reduce_scatter" and n % 128 == 0 and dname in ("fp32", "bf16"):
+                    # lossy wire format: reported next to the exact candidates, never chosen by the table
+                    from ..ops import fused
+                    try:
+                        for _ in range(2):
+                            fused.reduce_scatter_fp8(comm, xin, out=yout)
+                        t8 = time_call(lambda: fused.reduce_scatter_fp8(comm, xin, out=yout), args.iters, world)
+                        comm.check()
+                        rows.append([f"{coll}_fp8wire", 0, 0, P, n, t8 * 1e-3, 1, dname, "sum", total,
+                                     total / (t8 * 1e-3) / 1e9, total / (t8 * 1e-3) / 1e9 * factor, t8 * 1e3, P, 0])
+                        if rank == 0:
+                            print(f"{'  fp8 wire':14s} {dname} {total:>11d} B  {t8 * 1e3:9.1f} us", flush=True)
+                    except CollectiveError as e:
+                        if rank == 0:
+                            print(f"# skip fp8 wire: {e}", flush=True)
                 rows.append([f"{coll}_nccl", 0, 0, P, n, t_nccl * 1e-3, 1, dname, "sum", total,
                              total / (t_nccl * 1e-3) / 1e9, total / (t_nccl * 1e-3) / 1e9 * factor, t_nccl * 1e3, P, 0])
                 if rank == 0 and best:

@@ -84,23 +84,41 @@ fp8_rs_kernel(World w, Fp8Io io, long long n, float out_scale) {
     __syncthreads();
     ok = ok && s_entry_ok != 0;
   }
-  // ---- quantise the blocks owed to the peers (one warp per 128-element group)
+  // ---- quantise the blocks owed to the peers: one warp per 128-element group,
+  // U groups per iteration so that several loads are in flight per lane
+  constexpr int U = 4;
   if (ok)
-    for (long long g = warp; g < gpb * P; g += nwarps) {
-      if (g / gpb == rank) continue;
-      float x[4];
-      load4<T>(in + g * kGroup + lane * 4, x);
-      float amax = fmaxf(fmaxf(fabsf(x[0]), fabsf(x[1])), fmaxf(fabsf(x[2]), fabsf(x[3])));
+    for (long long g0 = warp * U; g0 < gpb * P; g0 += nwarps * U) {
+      float x[U][4];
+      bool live[U];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-      const float sc = amax > 0.f ? amax * (1.0f / 448.0f) : 1.0f;
-      const float inv = 1.0f / sc;
-      unsigned packed = 0;
+      for (int u = 0; u < U; ++u) {
+        const long long g = g0 + u;
+        live[u] = g < gpb * P && g / gpb != rank;
+        if (live[u]) load4<T>(in + g * kGroup + lane * 4, x[u]);
+        else x[u][0] = x[u][1] = x[u][2] = x[u][3] = 0.f;
+      }
+      float amax[U];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        packed |= (unsigned)__nv_cvt_float_to_fp8(x[i] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * i);
-      *reinterpret_cast<unsigned*>(wire + g * kGroup + lane * 4) = packed;
-      if (lane == 0) scales[g] = sc;
+      for (int u = 0; u < U; ++u)
+        amax[u] = fmaxf(fmaxf(fabsf(x[u][0]), fabsf(x[u][1])), fmaxf(fabsf(x[u][2]), fabsf(x[u][3])));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int u = 0; u < U; ++u) amax[u] = fmaxf(amax[u], __shfl_xor_sync(0xffffffffu, amax[u], o));
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (!live[u]) continue;
+        const long long g = g0 + u;
+        const float sc = amax[u] > 0.f ? amax[u] * (1.0f / 448.0f) : 1.0f;
+        const float inv = 1.0f / sc;
+        unsigned packed = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          packed |= (unsigned)__nv_cvt_float_to_fp8(x[u][i] * inv, __NV_SATFINITE, __NV_E4M3) << (8 * i);
+        *reinterpret_cast<unsigned*>(wire + g * kGroup + lane * 4) = packed;
+        if (lane == 0) scales[g] = sc;
+      }
     }
   unsigned gen = 0;
   ok = rank_barrier(c, nct, gen, w.timeout_ns, rank, 0) && ok;
@@ -108,27 +126,45 @@ fp8_rs_kernel(World w, Fp8Io io, long long n, float out_scale) {
   // ---- pull my block from every peer, dequantise, accumulate in rank order
   if (ok) {
     T* out = reinterpret_cast<T*>(io.out[rank]);
-    for (long long g = warp; g < gpb; g += nwarps) {
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (long long g0 = warp * U; g0 < gpb; g0 += nwarps * U) {
+      float acc[U][4];
+#pragma unroll
+      for (int u = 0; u < U; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
       for (int q = 0; q < P; ++q) {
-        float x[4];
         if (q == rank) {
-          load4<T>(in + ((long long)rank * gpb + g) * kGroup + lane * 4, x);
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            if (g0 + u >= gpb) continue;
+            float x[4];
+            load4<T>(in + ((long long)rank * gpb + g0 + u) * kGroup + lane * 4, x);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[u][i] += x[i];
+          }
         } else {
           const unsigned char* pw = reinterpret_cast<const unsigned char*>(w.work[q]);
           const float* ps = reinterpret_cast<const float*>(pw + (long long)P * n);
-          const long long gg = (long long)rank * gpb + g;
-          const unsigned packed = __ldcg(reinterpret_cast<const unsigned*>(pw + gg * kGroup + lane * 4));
-          const float sc = __ldcg(ps + gg);
+          unsigned packed[U];
+          float sc[U];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) x[i] = fp8_to_float((unsigned char)(packed >> (8 * i))) * sc;
+          for (int u = 0; u < U; ++u) {
+            const long long gg = (long long)rank * gpb + g0 + u;
+            const bool lv = g0 + u < gpb;
+            packed[u] = lv ? __ldcg(reinterpret_cast<const unsigned*>(pw + gg * kGroup + lane * 4)) : 0u;
+            sc[u] = lv ? __ldcg(ps + gg) : 0.f;
+          }
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[u][i] += fp8_to_float((unsigned char)(packed[u] >> (8 * i))) * sc[u];
         }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) acc[i] += x[i];
       }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) acc[i] *= out_scale;
-      store4<T>(out + g * kGroup + lane * 4, acc);
+      for (int u = 0; u < U; ++u) {
+        if (g0 + u >= gpb) continue;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[u][i] *= out_scale;
+        store4<T>(out + (g0 + u) * kGroup + lane * 4, acc[u]);
+      }
     }
   }
   // peers are done with my wire buffer

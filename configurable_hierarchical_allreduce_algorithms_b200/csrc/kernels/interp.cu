@@ -28,7 +28,6 @@ namespace chb {
 constexpr int kInterpThreads = 512;
 constexpr int kMaxSrc = 40;              // sources per step (incl. the accumulate operand)
 constexpr long long kSmallStepBytes = 64 << 10;  // below this one CTA runs the whole step
-constexpr int kMaxLarge = 16;            // large steps of one round that can run side by side
 
 struct DevStep { long long dst_off; long long count; int dst_buf; int nsrc; int src_begin; unsigned flags; };
 struct DevSrc { long long off; int peer; int buf; };
@@ -210,8 +209,6 @@ interp_kernel(World w, const char* __restrict__ blob, IoTable io, int op, float 
   __shared__ int s_ok;
   __shared__ const char* s_ptr[kMaxSrc + 1];
   __shared__ int s_meta[2];
-  __shared__ int s_lstep[kMaxLarge], s_lcnt[kMaxLarge];
-  __shared__ float s_lw[kMaxLarge];
   if (tid == 0) {
     s_base = ld_volatile_u64(&c->epoch);
     s_ok = ld_volatile_u32(&c->abort) ? 0 : 1;
@@ -238,69 +235,48 @@ interp_kernel(World w, const char* __restrict__ blob, IoTable io, int op, float 
     if (!ok) break;
     unsigned long long* tr = w.trace[rank];
     if (tr && cta == 0 && tid == 0 && t < w.trace_rounds) tr[2 * t] = globaltimer_ns();   // waits of round t satisfied
-    // Large steps of one round are independent of each other: when there are
-    // several (e.g. the local copy of the own block next to the pulls from the
-    // peers) they run side by side on disjoint CTA groups sized by cost, so that
-    // HBM-bound and NVLink-bound work overlap instead of running back to back.
+    // Large steps of one round are independent of each other.  When a round has
+    // both steps that pull from peers (NVLink bound) and steps that only touch
+    // local memory (HBM bound, e.g. the copy of the own block), the CTAs split
+    // into two groups sized by cost, one per kind, so the two overlap; inside a
+    // group the steps still run one after the other on all of the group's CTAs,
+    // which keeps the load balanced.
     if (tid == 0) {
-      int nl = 0;
-      float wsum = 0.f;
-      for (int s = R.step_begin; s < R.step_end && nl <= kMaxLarge; ++s) {
+      float wr = 0.f, wl = 0.f;
+      for (int s = R.step_begin; s < R.step_end; ++s) {
         const DevStep st = steps[s];
         if (st.count * (long long)sizeof(T) < kSmallStepBytes) continue;
-        if (nl < kMaxLarge) {
-          float wgt = 1.f;                                  // the store
-          for (int j = 0; j < st.nsrc; ++j) wgt += (srcs[st.src_begin + j].peer != rank) ? 8.f : 1.f;
-          wgt *= (float)st.count;
-          s_lstep[nl] = s;
-          s_lw[nl] = wgt;
-          wsum += wgt;
+        bool remote = false;
+        float wgt = 1.f;                                    // the store
+        for (int j = 0; j < st.nsrc; ++j) {
+          const bool rj = srcs[st.src_begin + j].peer != rank;
+          remote |= rj;
+          wgt += rj ? 8.f : 1.f;
         }
-        ++nl;
+        (remote ? wr : wl) += wgt * (float)st.count;
       }
-      if (nl >= 2 && nl <= kMaxLarge && (unsigned)nl <= nct) {
-        int used = 0;
-        for (int i = 0; i < nl; ++i) {
-          int cnt = (int)(s_lw[i] / wsum * (float)nct + 0.5f);
-          s_lcnt[i] = cnt < 1 ? 1 : cnt;
-          used += s_lcnt[i];
-        }
-        while (used != (int)nct) {                          // fix rounding on the heaviest step
-          int big = 0;
-          for (int i = 1; i < nl; ++i)
-            if (s_lw[i] > s_lw[big] && (used < (int)nct || s_lcnt[i] > 1)) big = i;
-          if (used > (int)nct) {
-            if (s_lcnt[big] <= 1) { for (int i = 0; i < nl; ++i) if (s_lcnt[i] > 1) big = i; }
-            --s_lcnt[big]; --used;
-          } else { ++s_lcnt[big]; ++used; }
-        }
-        s_meta[1] = nl;
-      } else {
-        s_meta[1] = 0;
+      int na = 0;                                           // CTAs of the remote group; 0 = no split
+      if (wr > 0.f && wl > 0.f && nct >= 2) {
+        na = (int)(wr / (wr + wl) * (float)nct + 0.5f);
+        na = na < 1 ? 1 : (na > (int)nct - 1 ? (int)nct - 1 : na);
       }
+      s_meta[1] = na;
     }
     __syncthreads();
-    const int nlarge = s_meta[1];
+    const unsigned na = (unsigned)s_meta[1];
     for (int s = R.step_begin; s < R.step_end; ++s) {
       const DevStep st = steps[s];
       const bool small = st.count * (long long)sizeof(T) < kSmallStepBytes;
       if (small) {
         if ((unsigned)(s - R.step_begin) % nct == cta)
           run_step<T>(st, srcs, w, io, rank, 0u, 1u, op, scale, s_ptr, s_meta);
-      } else if (nlarge == 0) {
+      } else if (na == 0) {
         run_step<T>(st, srcs, w, io, rank, cta, nct, op, scale, s_ptr, s_meta);
-      }
-    }
-    if (nlarge > 0) {
-      unsigned first = 0;
-      for (int i = 0; i < nlarge; ++i) {
-        const unsigned cnt = (unsigned)s_lcnt[i];
-        if (cta >= first && cta < first + cnt) {
-          const DevStep st = steps[s_lstep[i]];
-          run_step<T>(st, srcs, w, io, rank, cta - first, cnt, op, scale, s_ptr, s_meta);
-          break;
-        }
-        first += cnt;
+      } else {
+        bool remote = false;
+        for (int j = 0; j < st.nsrc; ++j) remote |= (srcs[st.src_begin + j].peer != rank);
+        if (remote && cta < na) run_step<T>(st, srcs, w, io, rank, cta, na, op, scale, s_ptr, s_meta);
+        if (!remote && cta >= na) run_step<T>(st, srcs, w, io, rank, cta - na, nct - na, op, scale, s_ptr, s_meta);
       }
     }
     ok = rank_barrier(c, nct, gen, w.timeout_ns, rank, t);

@@ -10,13 +10,16 @@ snapshot.
 """
 from __future__ import annotations
 
+import os
 import shutil
 import subprocess
 import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+# reference tree: argv[1], $CHB_REFERENCE_DIR, or a "reference" directory next to this repository
+REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(
+    os.environ.get("CHB_REFERENCE_DIR", HERE.parent.parent / "reference"))
 W = REF / "testing" / "custom_implementations" / "work_dir"
 SOURCES = [W / "all_gather" / "all_gather_radix_batch_1_0.cpp",
            W / "reduce_scatter" / "reduce_scatter_radix_batch.cpp",

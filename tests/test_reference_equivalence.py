@@ -16,11 +16,11 @@ EXE = ROOT / "baseline" / "_ref" / "ref_driver"
 @pytest.fixture(scope="module")
 def ref_driver():
     if not EXE.exists():
-        if not Path("/root/reference/testing").exists():
-            pytest.skip("reference sources are not available on this machine")
         import sys
         sys.path.insert(0, str(ROOT))
         from baseline import build_reference
+        if not (build_reference.REF / "testing").exists():
+            pytest.skip("reference sources are not available on this machine")
         build_reference.build()
     return EXE
 

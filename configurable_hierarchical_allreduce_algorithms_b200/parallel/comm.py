@@ -148,14 +148,25 @@ class Communicator:
             self._keep.append(heap)
             ptrs, backend = [heap.data_ptr()], "local"
         elif backend in ("auto", "symm_mem"):
+            err = None
             try:
                 ptrs, mc = self._heap_symm_mem(group, heap_bytes, dev)
-                backend = "symm_mem"
             except Exception as e:  # noqa: BLE001 - any failure means "not available here"
+                err, ptrs = e, None
+            # every rank must end up on the same backend: agree before going on
+            oks = [None] * P
+            dist.all_gather_object(oks, err is None, group=group)
+            if all(oks):
+                backend = "symm_mem"
+                mcs = [None] * P
+                dist.all_gather_object(mcs, bool(mc), group=group)
+                if not all(mcs):
+                    mc = 0            # multicast must be usable on all ranks or on none
+            else:
                 if backend == "symm_mem":
-                    raise
-                self._symm_mem_error = repr(e)
-                ptrs = None
+                    raise err if err is not None else RuntimeError("symmetric-memory rendezvous failed on a peer")
+                self._symm_mem_error = repr(err)
+                ptrs, mc = None, 0
         if ptrs is None:
             ptrs = self._heap_ipc(group, heap_bytes, rank, P)
             backend = "ipc"

@@ -272,3 +272,39 @@ def test_round_trace(comms):
     comm.enable_trace(0)
     chb.all_reduce(comm, ins, algo="radix_batch", k=2, b=4)
     comm.check()
+
+
+def test_cuda_graph_replay(comms):
+    """Epochs and sequence numbers live in device memory, so a captured collective can be replayed."""
+    P = 4
+    comm = comms(P)
+    n = 2048
+    xs = comm.empty(n * P, torch.float32)
+    ys = comm.empty(n * P, torch.float32)
+    zs = comm.empty(n * P, torch.float32)
+    src = make_inputs(P, n * P, torch.float32, seed=9)
+    for x, s_ in zip(xs, src):
+        x.copy_(s_)
+    # warm up outside of capture (program upload, caches)
+    chb.all_reduce(comm, xs, out=ys, algo="radix_batch", k=2, b=2)
+    chb.all_reduce(comm, xs, out=zs, algo="ll")
+    torch.cuda.synchronize()
+    st = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(st):
+        with torch.cuda.graph(g, stream=st):
+            chb.all_reduce(comm, xs, out=ys, algo="radix_batch", k=2, b=2, stream=st)
+            chb.all_reduce(comm, ys, out=zs, algo="ll", scale=0.5, stream=st)
+    for it in range(4):
+        for x, s_ in zip(xs, src):
+            x.copy_(s_ * (it + 1))
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        exp = ref_reduce(src, "sum") * (it + 1)
+        for r in range(P):
+            check(ys[r], exp, torch.float32, P)
+            check(zs[r], exp * P * 0.5, torch.float32, P * P)
+    # the communicator keeps working eagerly after replays
+    chb.all_reduce(comm, xs, out=ys, algo="radix_batch", k=2, b=2)
+    comm.check()

@@ -184,6 +184,7 @@ def main():
     ap.add_argument("--sweep-iters", type=int, default=10)
     ap.add_argument("--no-nccl", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -355,6 +356,47 @@ def main():
                 sweep.append(row)
         comm.check()
 
+    # ---- launch-free latency: 20 back-to-back allreduces captured in one CUDA graph (small sizes only)
+    graph_lat = []
+    if args.sweep and not args.no_graph:
+        try:
+            for sz in (8, 1024, 32768):
+                ne = max(1, sz // 4)
+                xv, yv = x[:ne], y[:ne]
+                row = {"bytes": ne * 4, "dtype": "fp32", "calls_per_graph": 20}
+                for name, fn in (("ours", lambda: chb.all_reduce(comm, xv, out=yv, stream=gs)),
+                                 ("nccl", (lambda: dist.all_reduce(yv)) if world > 1 and not args.no_nccl else None)):
+                    if fn is None:
+                        continue
+                    gs = torch.cuda.Stream()
+                    with torch.cuda.stream(gs):
+                        for _ in range(3):
+                            fn()
+                    torch.cuda.synchronize()
+                    barrier()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.stream(gs):
+                        with torch.cuda.graph(g, stream=gs):
+                            for _ in range(20):
+                                fn()
+                    ts = []
+                    for _ in range(7):
+                        barrier()
+                        torch.cuda.synchronize()
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record()
+                        g.replay()
+                        e1.record()
+                        torch.cuda.synchronize()
+                        ts.append(max_over_ranks(e0.elapsed_time(e1)) / 20)
+                    row[name + "_us_per_call"] = statistics.median(ts) * 1e3
+                    del g
+                graph_lat.append(row)
+            comm.check()
+        except Exception as e:  # noqa: BLE001 - an optional table must not cost the headline
+            graph_lat = [{"error": repr(e)[:200]}]
+
+
     if rank == 0:
         peaks = {}
         try:
@@ -380,6 +422,7 @@ def main():
             "roofline_note": "of measured (770 GB/s NVLink per direction; HBM copy from MEASURED_PEAKS.json at N=1)",
             "is_correct": bool(correct), "max_abs_err": err,
             "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "nccl": nccl, "sweep": sweep,
+            "graph_replay_latency": graph_lat,
         }
         print(json.dumps(out), flush=True)
     comm.close()

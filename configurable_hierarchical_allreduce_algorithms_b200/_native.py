@@ -35,6 +35,8 @@ def _declare(L: C.CDLL) -> None:
     vp, i32, i64, u64, cp = C.c_void_p, C.c_int, C.c_int64, C.c_uint64, C.c_char_p
     L.chb_program_create.restype = vp
     L.chb_program_create.argtypes = [cp, cp, i32, i32, i32, i64, i32, i32, i32, cp, i32]
+    L.chb_program_create_alltoallv.restype = vp
+    L.chb_program_create_alltoallv.argtypes = [i32, i32, i32, C.POINTER(i64), cp, i32]
     L.chb_program_destroy.restype = None
     L.chb_program_destroy.argtypes = [vp]
     L.chb_program_info.restype = i32

@@ -44,6 +44,9 @@ typedef struct chb_program chb_program_t;
 chb_program_t* chb_program_create(const char* coll, const char* algo, int P, int k, int b,
                                   int64_t count, int aux, int in_symmetric, int out_symmetric,
                                   char* err, int errlen);
+/* all-to-all-v with the radix-r / batch-b store-and-forward routing; counts[s*P + d] = elements rank s
+ * sends to rank d, blocks packed contiguously (input in destination order, output in source order) */
+chb_program_t* chb_program_create_alltoallv(int P, int r, int b, const int64_t* counts, char* err, int errlen);
 void chb_program_destroy(chb_program_t* p);
 
 enum {

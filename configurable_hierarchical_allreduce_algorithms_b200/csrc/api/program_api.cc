@@ -9,6 +9,11 @@
 #include "chb.h"
 #include "program_handle.h"
 
+#include <stdexcept>
+#include <vector>
+
+namespace chb { Builder gen_a2av_tuna(int P, const std::vector<int64_t>& counts, int r, int b); }
+
 namespace {
 void set_err(char* err, int errlen, const std::string& s) {
   if (!err || errlen <= 0) return;
@@ -37,6 +42,20 @@ chb_program_t* chb_program_create(const char* coll, const char* algo, int P, int
     o.out_symmetric = out_symmetric != 0;
     auto* p = new chb_program;
     p->prog = B.lower(o);
+    return p;
+  } catch (const std::exception& e) {
+    set_err(err, errlen, e.what());
+    return nullptr;
+  }
+}
+
+chb_program_t* chb_program_create_alltoallv(int P, int r, int b, const int64_t* counts, char* err, int errlen) {
+  try {
+    if (!counts || P < 1) throw std::runtime_error("alltoallv needs a P x P count matrix");
+    std::vector<int64_t> c(counts, counts + (size_t)P * P);
+    chb::Builder B = chb::gen_a2av_tuna(P, c, r, b);
+    auto* p = new chb_program;
+    p->prog = B.lower(chb::LowerOpts{});
     return p;
   } catch (const std::exception& e) {
     set_err(err, errlen, e.what());

@@ -29,6 +29,7 @@ Builder gen_ag_ring(int P, int64_t n);
 Builder gen_ag_recursive_doubling(int P, int64_t n);
 Builder gen_ag_linear(int P, int64_t n);
 Builder gen_gather_knomial(int P, int64_t n, int k, int root);
+Builder gen_grouped(const std::string& coll, const std::string& flat_algo, int P, int64_t count, int k, int b, bool lanes);
 // gen_tuna.cc
 Builder gen_rs_tuna(int P, int64_t n, int r, int b);
 void emit_rs_tuna(Builder& B, int P, int64_t n, int r, int b, int dbuf, int64_t doff);
@@ -79,7 +80,7 @@ std::vector<std::string> list_algorithms(const std::string& coll) {
             "recursive_exchange", "inter_reduce_exchange_bcast"};
   if (coll == "reduce_scatter")
     return {"radix_batch", "pairwise", "ring", "recursive_halving", "recursive_doubling", "radix",
-            "radix_block"};
+            "radix_block", "k_nomial"};
   if (coll == "allgather")
     return {"radix_batch", "k_brucks", "ring", "recursive_doubling", "linear"};
   if (coll == "alltoall") return {"tuna", "linear"};
@@ -111,6 +112,9 @@ Builder build_algorithm(const AlgoSpec& s) {
     if (a == "recursive_doubling") return gen_rs_recursive_doubling(s.P, s.count);
     if (a == "radix") return gen_rs_radix(s.P, s.count, s.k);
     if (a == "radix_block") return gen_rs_tuna(s.P, s.count, s.k, s.b);
+    // k-nomial recursive halving (tuna_based_outdated/reduce_scatter_k_nomial.cpp:25-217): the same radix-k
+    // neighbour sets and halving ranges as "radix"; only the way leftover ranks are folded differs
+    if (a == "k_nomial") return gen_rs_radix(s.P, s.count, s.k);
   } else if (c == "allgather") {
     if (a == "radix_batch") return gen_ag_radix_batch(s.P, s.count, s.k, s.b);
     if (a == "k_brucks") return gen_ag_kbruck(s.P, s.count, s.k);
@@ -123,6 +127,10 @@ Builder build_algorithm(const AlgoSpec& s) {
   } else if (c == "gather") {
     if (a == "k_nomial") return gen_gather_knomial(s.P, s.count, s.k, s.aux);
   }
+  // phases as stand-alone collectives on sub-communicators: "intra_<flat algorithm>" runs it inside
+  // every group of b consecutive ranks, "inter_<flat algorithm>" along every lane of stride b
+  if (a.rfind("intra_", 0) == 0) return gen_grouped(c, a.substr(6), s.P, s.count, s.k, s.b, false);
+  if (a.rfind("inter_", 0) == 0 && a != "inter_reduce_exchange_bcast") return gen_grouped(c, a.substr(6), s.P, s.count, s.k, s.b, true);
   throw std::runtime_error("unknown collective/algorithm: " + c + "/" + a);
 }
 

@@ -635,3 +635,45 @@ Builder gen_gather_knomial(int P, int64_t n, int k, int root) {
 }
 
 }  // namespace chb
+
+// ============================ building blocks on sub-groups =========================
+// The reference keeps the phases of its hierarchical collectives as stand-alone
+// functions over the whole communicator with the group structure inside
+// (intra_allgather_k_brucks, inter_allgather_linear:
+//  testing/custom_implementations/work_dir/all_gather/outdated_versions/intra_allgather_k_brucks.cpp:22-256,
+//  inter_allgather_linear.cpp:12-55; intra_reduce_scatter_radix_batch, inter_reduce_linear,
+//  intra_scatter_radix_batch: work_dir/reduce_scatter/intra_reduce_scatter_radix.cpp:208-541,
+//  inter_linear_reduce.cpp:11-73, intra_scatter_radix_batch.cpp:11-110).
+// Here a phase is a flat algorithm embedded once per group of b consecutive
+// ranks ("intra") or once per lane of equal in-group slot ("inter"):
+//   intra: collective among ranks g*b .. g*b+b-1       (sub-communicator size b)
+//   inter: collective among ranks r, r+b, r+2b, ...     (sub-communicator size P/b)
+namespace chb {
+Builder build_algorithm(const AlgoSpec& s);
+
+Builder gen_grouped(const std::string& coll, const std::string& flat_algo, int P, int64_t count, int k, int b,
+                    bool lanes) {
+  if (b < 1 || P % b) throw std::runtime_error("group size b must divide the number of ranks");
+  const int sub_p = lanes ? P / b : b;
+  AlgoSpec ss;
+  ss.coll = coll;
+  ss.algo = flat_algo;
+  ss.P = sub_p;
+  ss.k = k;
+  ss.b = 1;
+  ss.count = count;
+  Builder sub = build_algorithm(ss);
+  // same buffer lengths as the sub-program; every rank belongs to exactly one sub-communicator
+  int64_t in_e = coll == "allgather" ? count : (coll == "allreduce" ? count : count * sub_p);
+  int64_t out_e = coll == "allgather" ? count * sub_p : count;
+  Builder B(P, in_e, out_e, std::string(lanes ? "inter_" : "intra_") + coll + "_" + flat_algo);
+  int tmp_base = -1;
+  const int nsub = P / sub_p;
+  for (int g = 0; g < nsub; ++g) {
+    std::vector<int> map(sub_p);
+    for (int i = 0; i < sub_p; ++i) map[i] = lanes ? i * b + g : g * b + i;
+    tmp_base = B.embed(sub, map, tmp_base);
+  }
+  return B;
+}
+}  // namespace chb

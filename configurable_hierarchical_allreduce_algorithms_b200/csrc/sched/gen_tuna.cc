@@ -118,3 +118,78 @@ Builder gen_a2a_linear(int P, int64_t n) {
 }
 
 }  // namespace chb
+
+// ---- all-to-all-v: per-pair element counts (counts[s*P + d] = elements rank s
+// owes rank d), blocks packed in destination order in the input and in source
+// order in the output, as MPI_Alltoallv with contiguous displacements.  Same
+// radix-r / batch-b routing as above (the algorithm the reference's
+// store-and-forward reduce-scatter was derived from, debug/tuna.cpp:9-270).
+namespace chb {
+
+Builder gen_a2av_tuna(int P, const std::vector<int64_t>& counts, int r, int b) {
+  if ((int)counts.size() != P * P) throw std::runtime_error("alltoallv needs a P x P count matrix");
+  for (int64_t c : counts) if (c < 0) throw std::runtime_error("alltoallv counts must be >= 0");
+  auto cnt = [&](int s, int d) { return counts[(size_t)s * P + d]; };
+  std::vector<int64_t> sdis((size_t)P * P), rdis((size_t)P * P);
+  int64_t in_e = 0, out_e = 0, maxc = 0;
+  for (int s = 0; s < P; ++s) {
+    int64_t a = 0;
+    for (int d = 0; d < P; ++d) { sdis[(size_t)s * P + d] = a; a += cnt(s, d); maxc = std::max(maxc, cnt(s, d)); }
+    in_e = std::max(in_e, a);
+  }
+  for (int d = 0; d < P; ++d) {
+    int64_t a = 0;
+    for (int s = 0; s < P; ++s) { rdis[(size_t)d * P + s] = a; a += cnt(s, d); }
+    out_e = std::max(out_e, a);
+  }
+  Builder B(P, std::max<int64_t>(in_e, 1), std::max<int64_t>(out_e, 1), "alltoallv_tuna");
+  if (r < 2) r = 2;
+  if (P > 2 && r > P - 1) r = P - 1;
+  if (b <= 0 || b > P) b = P;
+  for (int d = 0; d < P; ++d)
+    B.copy(d, L_OUT, rdis[(size_t)d * P + d], d, L_IN, sdis[(size_t)d * P + d], cnt(d, d));
+  if (P == 1) return B;
+  int w = 0;
+  for (int m = P - 1; m > 0; m /= r) ++w;
+  const int64_t slot = std::max<int64_t>(maxc, 1);
+  int PARK = B.tmp((int64_t)w * (P - 1) * slot);
+  auto park_off = [&](int area, int i) { return ((int64_t)area * (P - 1) + (i - 1)) * slot; };
+  auto prev_digit_pos = [&](int i, int x) {
+    int pos = -1;
+    int64_t q = 1;
+    for (int y = 0; y < x; ++y, q *= r)
+      if ((i / q) % r != 0) pos = y;
+    return pos;
+  };
+  B.fence();
+  int64_t pw = 1;
+  for (int x = 0; x < w; ++x, pw *= r) {
+    std::vector<int> zs;
+    for (int z = 1; z < r; ++z)
+      if ((int64_t)z * pw <= P - 1) zs.push_back(z);
+    for (size_t k0 = 0; k0 < zs.size(); k0 += (size_t)b) {
+      size_t k1 = std::min(zs.size(), k0 + (size_t)b);
+      for (int me = 0; me < P; ++me)
+        for (size_t zi = k0; zi < k1; ++zi) {
+          int z = zs[zi];
+          int from = (int)((me + (int64_t)z * pw) % P);
+          for (int i = 1; i < P; ++i) {
+            if ((i / pw) % r != z) continue;
+            int64_t hi_next = (i / (pw * r)) * (pw * r);
+            int d = (int)(((me - hi_next) % P + P) % P);
+            int s = (d + i) % P;                       // origin of this block
+            int64_t c = cnt(s, d);
+            if (c == 0) continue;
+            Src src = (i % pw == 0) ? Src{from, L_IN, sdis[(size_t)s * P + d]}
+                                    : Src{from, PARK, park_off(prev_digit_pos(i, x), i)};
+            if (hi_next == 0) B.copy(me, L_OUT, rdis[(size_t)d * P + s], src.peer, src.buf, src.off, c);
+            else B.copy(me, PARK, park_off(x, i), src.peer, src.buf, src.off, c);
+          }
+        }
+      B.fence();
+    }
+  }
+  return B;
+}
+
+}  // namespace chb

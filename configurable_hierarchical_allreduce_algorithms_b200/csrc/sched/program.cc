@@ -70,6 +70,30 @@ void Builder::reduce(int rank, int dbuf, int64_t doff, const std::vector<Src>& s
   ops_.push_back(std::move(op));
 }
 
+int Builder::embed(const Builder& sub, const std::vector<int>& rank_map, int tmp_base) {
+  if ((int)rank_map.size() != sub.P_) throw std::runtime_error(name_ + ": rank map does not match the embedded program");
+  if (sub.in_elems_ > in_elems_ || sub.out_elems_ > out_elems_)
+    throw std::runtime_error(name_ + ": embedded program needs larger buffers");
+  if (tmp_base < 0) {
+    tmp_base = L_TMP0 + (int)tmp_elems_.size();
+    for (int64_t e : sub.tmp_elems_) tmp_elems_.push_back(e);
+  }
+  auto map_buf = [&](int b) { return b < L_TMP0 ? b : tmp_base + (b - L_TMP0); };
+  const int32_t fence0 = fence_;
+  int32_t maxf = 0;
+  for (const Op& o : sub.ops_) {
+    Op q = o;
+    q.rank = rank_map[o.rank];
+    q.dst_buf = map_buf(o.dst_buf);
+    q.fence = fence0 + o.fence;
+    maxf = std::max(maxf, o.fence);
+    for (Src& s : q.srcs) { s.peer = rank_map[s.peer]; s.buf = map_buf(s.buf); }
+    ops_.push_back(std::move(q));
+  }
+  embed_fence_span_ = std::max(embed_fence_span_, maxf);
+  return tmp_base;
+}
+
 namespace {
 
 struct Access {
@@ -181,6 +205,12 @@ Program Builder::lower(const LowerOpts& o) const {
       s.srcs = {Src{r, P_WORK, outs_off}};
       ops.push_back(std::move(s));
     }
+
+  // Fence groups must be visited in order.  Generators emit them in order; only
+  // embedded sub-programs (independent rank sets, each restarting at the current
+  // fence) interleave them, and for those a stable sort by fence keeps every
+  // sub-program's own order.
+  std::stable_sort(ops.begin(), ops.end(), [](const Op& a, const Op& b) { return a.fence < b.fence; });
 
   // ---- 4. dependency analysis and round assignment ----------------------------
   // history[(owner rank, phys buf)] -> accesses so far

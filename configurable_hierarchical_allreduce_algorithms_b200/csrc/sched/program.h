@@ -112,6 +112,12 @@ class Builder {
   // Everything emitted after fence() is scheduled in a later round than
   // everything emitted before it (models a global MPI_Waitall boundary).
   void fence() { ++fence_; }
+  // Append all steps of `sub` (a program over rank_map.size() ranks with the same
+  // input / output lengths) with sub-rank i executed by rank rank_map[i]; used to
+  // run one flat algorithm independently inside every group or along every lane.
+  // tmp_base < 0 allocates fresh temporaries and returns their first id, so that
+  // further embeddings of the same sub-program can share them.
+  int embed(const Builder& sub, const std::vector<int>& rank_map, int tmp_base = -1);
   Program lower(const LowerOpts& o) const;
 
  private:
@@ -121,6 +127,7 @@ class Builder {
   std::vector<int64_t> tmp_elems_;
   std::vector<Op> ops_;
   int32_t fence_ = 0;
+  int32_t embed_fence_span_ = 0;   // largest fence offset used by embedded programs
 };
 
 // ---- reduction / element types shared by simulator, C API and kernels ----

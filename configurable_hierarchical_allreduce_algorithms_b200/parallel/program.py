@@ -73,6 +73,31 @@ class Program:
         self.name = L.chb_program_name(h).decode()
         self._tables = None
 
+    @classmethod
+    def alltoallv(cls, counts, r: int = 2, b: int = 1) -> "Program":
+        """All-to-all-v program; ``counts[s][d]`` = elements rank s sends to rank d."""
+        counts = np.ascontiguousarray(counts, dtype=np.int64)
+        P = counts.shape[0]
+        assert counts.shape == (P, P)
+        L = N.lib()
+        err = C.create_string_buffer(512)
+        h = L.chb_program_create_alltoallv(P, r, b, counts.ctypes.data_as(C.POINTER(C.c_int64)), err, len(err))
+        if not h:
+            raise ProgramError(err.value.decode() or "program creation failed")
+        self = cls.__new__(cls)
+        self._h = h
+        self.coll, self.algo, self.k, self.b, self.count, self.aux = "alltoallv", "tuna", r, b, 0, 0
+        info = (C.c_int64 * 32)()
+        L.chb_program_info(h, info, 32)
+        (self.P, self.nrounds, self.in_elems, self.out_elems, self.work_elems, self.nops,
+         self.remote_msgs, self.remote_elems, self.max_rank_remote_elems, self.local_elems,
+         self.max_nsrc, rpi, rpo, self.nsrcs, self.nwaits, self.nexit_waits, self.nsignals) = [int(x) for x in info[:17]]
+        self.reads_peer_in, self.reads_peer_out = bool(rpi), bool(rpo)
+        self.in_symmetric = self.out_symmetric = self.in_place = False
+        self.name = L.chb_program_name(h).decode()
+        self._tables = None
+        return self
+
     def __del__(self):
         try:
             if getattr(self, "_h", None):

@@ -153,3 +153,55 @@ def test_config1_cpu_plumbing_single_process():
     run_case("allreduce", "radix_batch", 4, 1024, 2, 1)
     run_case("reduce_scatter", "radix_batch", 4, 1024, 2, 1)
     run_case("allgather", "radix_batch", 4, 1024, 2, 1)
+
+
+def test_phases_as_standalone_collectives():
+    # intra_<algo>: inside every group of b consecutive ranks; inter_<algo>: along every lane of stride b
+    P, b, n = 12, 4, 3
+    G = P // b
+    ins = [(np.arange(n) + 100 * r).astype(np.int32) for r in range(P)]
+    o = Program("allgather", "intra_k_brucks", P, n, 3, b)
+    o.verify()
+    out = o.simulate(ins)
+    for r in range(P):
+        g = r // b
+        np.testing.assert_array_equal(out[r], np.concatenate(ins[g * b:(g + 1) * b]))
+    o = Program("allgather", "inter_linear", P, n, 2, b)
+    o.verify()
+    out = o.simulate(ins)
+    for r in range(P):
+        np.testing.assert_array_equal(out[r], np.concatenate([ins[q] for q in range(r % b, P, b)]))
+    ins = [(np.arange(n * G) + 7 * r).astype(np.int32) for r in range(P)]
+    out = Program("reduce_scatter", "inter_pairwise", P, n, 2, b).simulate(ins)
+    for r in range(P):
+        tot = sum(ins[q] for q in range(r % b, P, b))
+        np.testing.assert_array_equal(out[r], tot[(r // b) * n:(r // b + 1) * n])
+    ins = [(np.arange(n * b) + 7 * r).astype(np.int32) for r in range(P)]
+    out = Program("reduce_scatter", "intra_radix", P, n, 3, b).simulate(ins)
+    for r in range(P):
+        tot = sum(ins[(r // b) * b:(r // b + 1) * b])
+        np.testing.assert_array_equal(out[r], tot[(r % b) * n:(r % b + 1) * n])
+
+
+def test_alltoallv_store_and_forward():
+    rng = np.random.default_rng(0)
+    for P in (1, 2, 5, 8):
+        counts = rng.integers(0, 6, size=(P, P))
+        for r, b in ((2, 1), (3, 2), (8, 8)):
+            p = Program.alltoallv(counts, r, b)
+            p.verify()
+            ins = []
+            for s in range(P):
+                x = np.full(p.in_elems, -1, np.int64)
+                off = 0
+                for d in range(P):
+                    x[off:off + counts[s, d]] = 1000 * s + 10 * d + np.arange(counts[s, d])
+                    off += counts[s, d]
+                ins.append(x)
+            outs = p.simulate(ins)
+            for d in range(P):
+                off = 0
+                for s in range(P):
+                    exp = 1000 * s + 10 * d + np.arange(counts[s, d])
+                    np.testing.assert_array_equal(outs[d][off:off + counts[s, d]], exp)
+                    off += counts[s, d]

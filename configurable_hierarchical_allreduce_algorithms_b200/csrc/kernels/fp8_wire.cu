@@ -23,26 +23,29 @@ struct Fp8Io {
   char* out[kMaxRanks];
 };
 
-template <typename T> __device__ __forceinline__ void load4(const T* p, float* x);
-template <> __device__ __forceinline__ void load4<float>(const float* p, float* x) {
-  const float4 v = *reinterpret_cast<const float4*>(p);
-  x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+// 8 consecutive elements per lane: a 128-element group is 16 lanes, a warp covers two groups.
+template <typename T> __device__ __forceinline__ void load8(const T* p, float* x);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float* x) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
 }
-template <> __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float* x) {
-  const uint2 v = *reinterpret_cast<const uint2*>(p);
-  const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* x) {
+  const uint4 v = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) x[i] = __bfloat162float(e[i]);
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(e[i]); x[2 * i] = f.x; x[2 * i + 1] = f.y; }
 }
-template <typename T> __device__ __forceinline__ void store4(T* p, const float* x);
-template <> __device__ __forceinline__ void store4<float>(float* p, const float* x) {
-  *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+template <typename T> __device__ __forceinline__ void store8(T* p, const float* x);
+template <> __device__ __forceinline__ void store8<float>(float* p, const float* x) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(x[0], x[1], x[2], x[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(x[4], x[5], x[6], x[7]);
 }
-template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float* x) {
-  __nv_bfloat16 e[4];
+template <> __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float* x) {
+  uint4 v;
+  __nv_bfloat162* e = reinterpret_cast<__nv_bfloat162*>(&v);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) e[i] = __float2bfloat16_rn(x[i]);
-  *reinterpret_cast<uint2*>(p) = *reinterpret_cast<uint2*>(e);
+  for (int i = 0; i < 4; ++i) e[i] = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = v;
 }
 
 __device__ __forceinline__ float2 fp8x2_to_float2(unsigned short b) {
@@ -63,10 +66,11 @@ fp8_rs_kernel(World w, Fp8Io io, long long n, float out_scale) {
   if (threadIdx.x == 0) s_seq = ld_volatile_u64(&c->bar_seq);
   __syncthreads();
   const unsigned long long seq = s_seq;
-  const int lane = threadIdx.x & 31;
+  const int sub = threadIdx.x & 15;                         // lane inside its 16-lane group
+  const int hw = (threadIdx.x >> 4) & 1;                    // which half of the warp
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)nct * blockDim.x) >> 5;
-  const long long gpb = n / kGroup;                 // groups per block
+  const long long gpb = n / kGroup;                         // groups per block
   const T* in = reinterpret_cast<const T*>(io.in[rank]);
   unsigned char* wire = reinterpret_cast<unsigned char*>(w.work[rank]);
   float* scales = reinterpret_cast<float*>(wire + (long long)P * n);
@@ -84,26 +88,32 @@ fp8_rs_kernel(World w, Fp8Io io, long long n, float out_scale) {
     __syncthreads();
     ok = ok && s_entry_ok != 0;
   }
-  // ---- quantise the blocks owed to the peers: one warp per 128-element group,
-  // U groups per iteration so that several loads are in flight per lane
-  constexpr int U = 4;
+  constexpr int U = 4;   // groups in flight per half-warp
+  // ---- quantise the blocks owed to the peers
   if (ok)
-    for (long long g0 = warp * U; g0 < gpb * P; g0 += nwarps * U) {
-      float x[U][4];
+    for (long long gw = warp * 2 * U; gw < gpb * P; gw += nwarps * 2 * U) {   // trip count uniform per warp (shuffles below)
+      const long long g0 = gw + hw * U;
+      float x[U][8];
       bool live[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const long long g = g0 + u;
         live[u] = g < gpb * P && g / gpb != rank;
-        if (live[u]) load4<T>(in + g * kGroup + lane * 4, x[u]);
-        else x[u][0] = x[u][1] = x[u][2] = x[u][3] = 0.f;
+        if (live[u]) load8<T>(in + g * kGroup + sub * 8, x[u]);
+        else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x[u][i] = 0.f;
+        }
       }
       float amax[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u)
-        amax[u] = fmaxf(fmaxf(fabsf(x[u][0]), fabsf(x[u][1])), fmaxf(fabsf(x[u][2]), fabsf(x[u][3])));
+      for (int u = 0; u < U; ++u) {
+        amax[u] = 0.f;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1)
+        for (int i = 0; i < 8; ++i) amax[u] = fmaxf(amax[u], fabsf(x[u][i]));
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1)
 #pragma unroll
         for (int u = 0; u < U; ++u) amax[u] = fmaxf(amax[u], __shfl_xor_sync(0xffffffffu, amax[u], o));
 #pragma unroll
@@ -112,12 +122,12 @@ fp8_rs_kernel(World w, Fp8Io io, long long n, float out_scale) {
         const long long g = g0 + u;
         const float sc = amax[u] > 0.f ? amax[u] * (1.0f / 448.0f) : 1.0f;
         const float inv = 1.0f / sc;
-        // two hardware conversions (cvt ... e4m3x2) per lane
-        const unsigned lo = __nv_cvt_float2_to_fp8x2(make_float2(x[u][0] * inv, x[u][1] * inv), __NV_SATFINITE, __NV_E4M3);
-        const unsigned hi = __nv_cvt_float2_to_fp8x2(make_float2(x[u][2] * inv, x[u][3] * inv), __NV_SATFINITE, __NV_E4M3);
-        const unsigned packed = lo | (hi << 16);
-        *reinterpret_cast<unsigned*>(wire + g * kGroup + lane * 4) = packed;
-        if (lane == 0) scales[g] = sc;
+        unsigned q[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)   // hardware pair conversions (cvt ... e4m3x2)
+          q[i] = __nv_cvt_float2_to_fp8x2(make_float2(x[u][2 * i] * inv, x[u][2 * i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+        *reinterpret_cast<uint2*>(wire + g * kGroup + sub * 8) = make_uint2(q[0] | (q[1] << 16), q[2] | (q[3] << 16));
+        if (sub == 0) scales[g] = sc;
       }
     }
   unsigned gen = 0;
@@ -126,38 +136,43 @@ fp8_rs_kernel(World w, Fp8Io io, long long n, float out_scale) {
   // ---- pull my block from every peer, dequantise, accumulate in rank order
   if (ok) {
     T* out = reinterpret_cast<T*>(io.out[rank]);
-    for (long long g0 = warp * U; g0 < gpb; g0 += nwarps * U) {
-      float acc[U][4];
+    for (long long gw = warp * 2 * U; gw < gpb; gw += nwarps * 2 * U) {
+      const long long g0 = gw + hw * U;
+      float acc[U][8];
 #pragma unroll
-      for (int u = 0; u < U; ++u) acc[u][0] = acc[u][1] = acc[u][2] = acc[u][3] = 0.f;
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[u][i] = 0.f;
       for (int q = 0; q < P; ++q) {
         if (q == rank) {
 #pragma unroll
           for (int u = 0; u < U; ++u) {
             if (g0 + u >= gpb) continue;
-            float x[4];
-            load4<T>(in + ((long long)rank * gpb + g0 + u) * kGroup + lane * 4, x);
+            float x[8];
+            load8<T>(in + ((long long)rank * gpb + g0 + u) * kGroup + sub * 8, x);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[u][i] += x[i];
+            for (int i = 0; i < 8; ++i) acc[u][i] += x[i];
           }
         } else {
           const unsigned char* pw = reinterpret_cast<const unsigned char*>(w.work[q]);
           const float* ps = reinterpret_cast<const float*>(pw + (long long)P * n);
-          unsigned packed[U];
+          uint2 packed[U];
           float sc[U];
 #pragma unroll
           for (int u = 0; u < U; ++u) {
             const long long gg = (long long)rank * gpb + g0 + u;
             const bool lv = g0 + u < gpb;
-            packed[u] = lv ? __ldcg(reinterpret_cast<const unsigned*>(pw + gg * kGroup + lane * 4)) : 0u;
+            packed[u] = lv ? __ldcg(reinterpret_cast<const uint2*>(pw + gg * kGroup + sub * 8)) : make_uint2(0u, 0u);
             sc[u] = lv ? __ldcg(ps + gg) : 0.f;
           }
 #pragma unroll
           for (int u = 0; u < U; ++u) {
-            const float2 a = fp8x2_to_float2((unsigned short)(packed[u] & 0xffffu));
-            const float2 b = fp8x2_to_float2((unsigned short)(packed[u] >> 16));
-            acc[u][0] += a.x * sc[u]; acc[u][1] += a.y * sc[u];
-            acc[u][2] += b.x * sc[u]; acc[u][3] += b.y * sc[u];
+            const float2 a0 = fp8x2_to_float2((unsigned short)(packed[u].x & 0xffffu));
+            const float2 a1 = fp8x2_to_float2((unsigned short)(packed[u].x >> 16));
+            const float2 a2 = fp8x2_to_float2((unsigned short)(packed[u].y & 0xffffu));
+            const float2 a3 = fp8x2_to_float2((unsigned short)(packed[u].y >> 16));
+            acc[u][0] += a0.x * sc[u]; acc[u][1] += a0.y * sc[u]; acc[u][2] += a1.x * sc[u]; acc[u][3] += a1.y * sc[u];
+            acc[u][4] += a2.x * sc[u]; acc[u][5] += a2.y * sc[u]; acc[u][6] += a3.x * sc[u]; acc[u][7] += a3.y * sc[u];
           }
         }
       }
@@ -165,8 +180,8 @@ fp8_rs_kernel(World w, Fp8Io io, long long n, float out_scale) {
       for (int u = 0; u < U; ++u) {
         if (g0 + u >= gpb) continue;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[u][i] *= out_scale;
-        store4<T>(out + (g0 + u) * kGroup + lane * 4, acc[u]);
+        for (int i = 0; i < 8; ++i) acc[u][i] *= out_scale;
+        store8<T>(out + (g0 + u) * kGroup + sub * 8, acc[u]);
       }
     }
   }
@@ -200,7 +215,7 @@ int chb_rs_fp8_wire(chb_comm* c, int dtype, const void* const* in, void* const* 
   if (n == 0) return CHB_SUCCESS;
   const int max_pair_ctas = (kSigSlots - kSigNvlsBase) / kMaxRanks;
   int budget = c->max_ctas / c->nlocal;
-  if (nctas <= 0) nctas = (int)(((long long)c->P * n / kGroup + 15) / 16 / 4);
+  if (nctas <= 0) nctas = (int)(((long long)c->P * n / kGroup + 127) / 128);
   if (nctas > 120) nctas = 120;
   if (nctas > max_pair_ctas) nctas = max_pair_ctas;
   if (nctas > budget) nctas = budget;

@@ -53,7 +53,7 @@ def candidates(coll: str, P: int, nbytes: int, comm) -> list[tuple]:
                 for n in (32, 64, 128):
                     out.append(("radix_batch", k, b, n))
     if comm.has_multicast and nbytes % 16 == 0 and nbytes >= 16 * P:
-        for n in ((1, 4, 16) if nbytes <= (1 << 20) else (16, 32, 64)):
+        for n in ((1, 4, 16) if nbytes <= (1 << 20) else (8, 16, 24, 32, 64)):
             out.append(("nvls", 2, 1, n))
             if coll == "allreduce" and nbytes <= (4 << 20):
                 out.append(("nvls1", 2, 1, n))

@@ -53,6 +53,7 @@ def _ll_ok(comm, ins, outs, payload_bytes):
 
 _COLL = {"allreduce": 0, "reduce_scatter": 1, "allgather": 2, "alltoall": 3, "gather": 4}
 _ALGO_BYTES: dict = {}
+_NVTX = __import__("os").environ.get("CHB_NVTX", "0") == "1"   # NVTX range around every launch
 
 
 def _run(comm: Communicator, coll: str, ins, outs, count: int, op, algo, k, b, aux, scale, nctas, stream,
@@ -81,10 +82,14 @@ def _run(comm: Communicator, coll: str, ins, outs, count: int, op, algo, k, b, a
     if ab is None:
         ab = _ALGO_BYTES[algo] = algo.encode()
     n = len(ins)
+    if _NVTX:
+        torch.cuda.nvtx.range_push(f"chb.{coll}.{algo}[{payload_bytes}B]")
     rc = N.lib().chb_collective(comm._h, _COLL[coll], ab, k, b, aux, DTYPES[ins[0].dtype], OPS[op],
                                 (C.c_void_p * n)(*[t.data_ptr() for t in ins]),
                                 (C.c_void_p * n)(*[t.data_ptr() for t in outs]),
                                 count, scale, nctas, _stream_ptr(stream))
+    if _NVTX:
+        torch.cuda.nvtx.range_pop()
     if rc:
         comm._err(rc)
     comm.launches += 1

@@ -308,3 +308,17 @@ def test_cuda_graph_replay(comms):
     # the communicator keeps working eagerly after replays
     chb.all_reduce(comm, xs, out=ys, algo="radix_batch", k=2, b=2)
     comm.check()
+
+
+def test_in_place_flagged_line_kernels(comms):
+    P = 8
+    comm = comms(P)
+    for algo in ("ll", "ll2"):
+        for n in (5, 4096):
+            src = make_inputs(P, n * P, torch.float32, seed=n)
+            bufs = [s_.clone() for s_ in src]
+            exp = ref_reduce(src, "sum")
+            chb.all_reduce(comm, bufs, out=bufs, algo=algo)
+            for r in range(P):
+                check(bufs[r], exp, torch.float32, P)
+    comm.check()

@@ -75,6 +75,57 @@ int chb_program_export(const chb_program_t* p, int64_t* ops, int64_t* srcs, int6
 /* names accepted as `algo` for a collective, comma separated */
 int chb_list_algorithms(const char* coll, char* out, int outlen);
 
+/* -------------------------------------------------------------- communicators
+ * A communicator is driven from one host thread and one stream at a time (like an
+ * MPI communicator inside one collective): launches of the same communicator that
+ * could overlap on the GPU are not supported.  Every rank must issue the same
+ * sequence of collectives.  The first launch of a program uploads its schedule
+ * (an allocation and a copy): do it once outside of any stream capture. */
+struct chb_comm;
+typedef struct CUstream_st* chb_stream_t;   /* cudaStream_t */
+
+size_t chb_heap_bytes(int P, size_t ll_payload_bytes, size_t scratch_bytes, size_t user_bytes);
+/* heap_ptrs: P peer-mapped bases of equally laid out, zero-filled heaps (P slices of one
+ * local allocation when nlocal == P, the emulated world); mc_ptr: NVLS multicast alias or NULL */
+struct chb_comm* chb_comm_create(int rank, int P, int nlocal, void* const* heap_ptrs, void* mc_ptr,
+                                 size_t ll_payload_bytes, size_t scratch_bytes, size_t user_bytes,
+                                 char* err, int errlen);
+void chb_comm_destroy(struct chb_comm* c);
+const char* chb_comm_last_error(const struct chb_comm* c);
+int chb_comm_set_timeout_us(struct chb_comm* c, unsigned long long us);
+int chb_comm_info(const struct chb_comm* c, int64_t* info, int n);
+void* chb_comm_user_ptr(const struct chb_comm* c, int local_index);    /* peer-visible region for caller buffers */
+void* chb_comm_scratch_ptr(const struct chb_comm* c, int local_index);
+int chb_barrier(struct chb_comm* c, unsigned long long timeout_us, chb_stream_t stream);
+/* synchronises the stream; status8 = code, rank, round, peer, expected, seen, launches, epoch */
+int chb_comm_status(struct chb_comm* c, int local_index, unsigned long long* status8, chb_stream_t stream);
+int chb_comm_clear_error(struct chb_comm* c, chb_stream_t stream);
+int chb_comm_trace_enable(struct chb_comm* c, int rounds);
+int chb_comm_trace_read(struct chb_comm* c, int local_index, unsigned long long* out, int rounds, chb_stream_t stream);
+/* cudaIpc helpers for the one-rank-per-process case */
+int chb_ipc_alloc(size_t bytes, void** ptr, void* handle64);
+int chb_ipc_open(const void* handle64, void** ptr);
+int chb_ipc_close(void* ptr);
+
+/* --------------------------------------------------------------- collectives
+ * in / out: one device pointer per local rank.  See chb_compat.h for chb_collective
+ * (any algorithm by name) and the reference-compatible entry points. */
+int chb_run_program(struct chb_comm* c, const chb_program_t* p, int dtype, int op, const void* const* in,
+                    void* const* out, float scale, int nctas, chb_stream_t stream);
+/* mode 0 allreduce, 1 reduce-scatter, 2 allgather, 3 two-shot allreduce (flagged lines, no barrier) */
+int chb_ll_collective(struct chb_comm* c, int mode, int dtype, int op, const void* const* in, void* const* out,
+                      long long count, float scale, int nctas, chb_stream_t stream);
+/* mode 0 two-shot allreduce, 1 reduce-scatter, 2 allgather, 3 one-shot allreduce (multimem, sums) */
+int chb_nvls_collective(struct chb_comm* c, int mode, int dtype, const void* in, void* out, long long count,
+                        float scale, int nctas, chb_stream_t stream);
+int chb_rs_fp8_wire(struct chb_comm* c, int dtype, const void* const* in, void* const* out, long long n,
+                    float out_scale, int nctas, chb_stream_t stream);
+int chb_rs_adam(struct chb_comm* c, const void* const* grad, void* const* master, void* const* m, void* const* v,
+                void* const* param_shard, long long n, const float* hyper, int use_multimem, int nctas,
+                chb_stream_t stream);
+int chb_adam_flat(const void* grad, void* master, void* m, void* v, void* param_bf16, long long n,
+                  const float* hyper, chb_stream_t stream);
+
 int chb_dtype_size(int dtype);
 const char* chb_version(void);
 

@@ -324,7 +324,7 @@ extern "C" {
 
 // Upload (once) and return the device blob of a program for this communicator.
 static int get_blob(chb_comm* c, const chb_program* p, void** out) {
-  auto it = c->blobs.find(p);
+  auto it = c->blobs.find(p->uid);
   if (it != c->blobs.end()) { *out = it->second; return CHB_SUCCESS; }
   if (p->prog.stats.max_nsrc > kMaxSrc) { c->last_error = "program has a step with too many sources"; return CHB_ERR_UNSUPPORTED; }
   std::vector<char> blob = make_blob(p->prog);
@@ -335,7 +335,7 @@ static int get_blob(chb_comm* c, const chb_program* p, void** out) {
     c->last_error = "cudaMemcpy(program blob) failed";
     return CHB_ERR_CUDA;
   }
-  c->blobs[p] = d;
+  c->blobs[p->uid] = d;
   *out = d;
   return CHB_SUCCESS;
 }
@@ -348,7 +348,8 @@ int chb_program_prepare(chb_comm* c, const chb_program* p) {
 
 void chb_program_release(chb_comm* c, const chb_program* p) {
   if (!c) return;
-  auto it = c->blobs.find(p);
+  if (!p) return;
+  auto it = c->blobs.find(p->uid);
   if (it != c->blobs.end()) { cudaFree(it->second); c->blobs.erase(it); }
 }
 

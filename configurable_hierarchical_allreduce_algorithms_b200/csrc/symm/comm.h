@@ -36,8 +36,8 @@ struct chb_comm {
   unsigned long long timeout_ns = 10ull * 1000 * 1000 * 1000;
   int max_ctas = 0;             // co-resident CTA budget per rank
   int sm_count = 0;
-  // device copies of compiled programs, keyed by program pointer
-  std::map<const chb_program*, void*> blobs;
+  // device copies of compiled programs, keyed by the program's unique id
+  std::map<uint64_t, void*> blobs;
   std::string last_error;
 
   char* sig_ptr(int p) const { return heap[p]; }

@@ -1,0 +1,32 @@
+"""The C ABI from a plain C program (no Python in the call path)."""
+import shutil
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+PKG = ROOT / "configurable_hierarchical_allreduce_algorithms_b200"
+
+
+def _build(tmp_path):
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    exe = tmp_path / "c_abi_example"
+    cmd = [nvcc, "-x", "c", str(ROOT / "tests" / "native" / "c_abi_example.c"), "-I", str(PKG / "csrc" / "api"),
+           "-L", str(PKG), "-lchb", "-Xlinker", f"-rpath={PKG}", "-o", str(exe)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    return exe
+
+
+def test_c_example_compiles_against_the_headers(tmp_path):
+    from configurable_hierarchical_allreduce_algorithms_b200 import _native
+    _native.lib()                      # builds libchb.so if needed
+    _build(tmp_path)
+
+
+@pytest.mark.gpu
+def test_c_example_runs(tmp_path, cuda):
+    exe = _build(tmp_path)
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "C ABI OK" in r.stdout, r.stdout + r.stderr

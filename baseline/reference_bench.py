@@ -51,6 +51,21 @@ def run(args) -> dict | None:
         return _unavailable(f"reference driver failed rc={r.returncode}: {r.stderr[-150:]}")
     d = json.loads(line[-1])
     ms = d["ms_per_step"]
+    # the same collective with this library's schedule on host threads (one thread per rank, same machine):
+    # a CPU-to-CPU comparison that does not involve the GPUs at all
+    host_ms = None
+    try:
+        import numpy as np
+        import sys
+        sys.path.insert(0, str(HERE.parent))
+        from configurable_hierarchical_allreduce_algorithms_b200.parallel.program import Program
+        n = S // 4 // N * N
+        prog = Program("allreduce", "radix_batch", N, n, 2, 1)
+        ins = [np.full(n, float(r), np.float32) for r in range(N)]
+        _, sec = prog.run_threads(ins, iters=2)
+        host_ms = sec * 1e3
+    except Exception:  # noqa: BLE001 - optional extra
+        host_ms = None
     algbw = S / (ms * 1e-3) / 1e9
     return {
         "impl": "reference", "metric": "allreduce_sum_fp32_aggregate_algbw_GBps", "value": algbw * N, "unit": "GB/s",
@@ -62,4 +77,5 @@ def run(args) -> dict | None:
                    "transport": "thread-per-rank MPI shim on the host CPUs (no MPI installation on the image)",
                    "timing": "host clock, Barrier; t0; call; Barrier; t1 as in the reference's drivers"},
         "gpu_launches": 0,
+        "this_library_same_schedule_on_host_threads_ms": host_ms,
     }

@@ -62,6 +62,9 @@ int chb_program_verify(const chb_program_t* p, char* err, int errlen);
 /* run all ranks on host buffers; in[r] / out[r] are rank r's buffers */
 int chb_program_simulate(const chb_program_t* p, int dtype, int op, void* const* in,
                          void* const* out, uint64_t seed, char* err, int errlen);
+/* run all ranks as host threads (real concurrency); mean wall seconds per repetition in *seconds */
+int chb_program_run_threads(const chb_program_t* p, int dtype, int op, void* const* in, void* const* out,
+                            int iters, double* seconds);
 /* Flat export (all int64):
  *   ops        [NOPS][8]        rank, round, dst_buf, dst_off, count, acc, src_begin, nsrc
  *   srcs       [NSRCS][3]       peer, buf, off

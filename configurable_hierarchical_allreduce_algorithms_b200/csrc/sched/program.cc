@@ -467,3 +467,104 @@ int verify(const Program& p, std::string* err) {
 }
 
 }  // namespace chb
+
+// =============================== threaded host executor =========================
+// One OS thread per rank, real concurrency: a rank publishes the index of the
+// last round it completed (release), waiters spin on it (acquire).  This is the
+// host-memory counterpart of the GPU interpreter (same waits, same signals) and
+// the closest analogue of the reference's execution model, where every rank is a
+// process and message matching orders the rounds.
+#include <atomic>
+#include <chrono>
+#include <thread>
+
+namespace chb {
+namespace {
+
+template <typename T>
+void run_rank(const Program& p, int rank, int rop, void* const* in, void* const* out, std::vector<T>* work,
+              std::atomic<int>* done, std::atomic<bool>* failed) {
+  auto ptr = [&](int r, int buf, int64_t off) -> T* {
+    switch (buf) {
+      case P_IN: return (T*)in[r] + off;
+      case P_OUT: return (T*)out[r] + off;
+      default: return work[r].data() + off;
+    }
+  };
+  for (int t = 0; t < p.nrounds; ++t) {
+    for (const Wait& w : p.rr[rank][t].waits) {
+      auto t0 = std::chrono::steady_clock::now();
+      while (done[w.peer].load(std::memory_order_acquire) < w.need) {
+        if (failed->load(std::memory_order_relaxed)) return;
+        if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(20)) { failed->store(true); return; }
+        std::this_thread::yield();
+      }
+    }
+    for (int32_t oi : p.rr[rank][t].ops) {
+      const Op& op = p.ops[oi];
+      T* dst = ptr(op.rank, op.dst_buf, op.dst_off);
+      size_t first = 0;
+      if (!op.acc) {
+        const Src& s = op.srcs[0];
+        const T* sp = ptr(s.peer, s.buf, s.off);
+        if (sp != dst) std::memmove(dst, sp, (size_t)op.count * sizeof(T));
+        first = 1;
+      }
+      for (size_t si = first; si < op.srcs.size(); ++si) {
+        const Src& s = op.srcs[si];
+        const T* sp = ptr(s.peer, s.buf, s.off);
+        switch (rop) {
+          case OP_SUM: for (int64_t i = 0; i < op.count; ++i) dst[i] = dst[i] + sp[i]; break;
+          case OP_MAX: for (int64_t i = 0; i < op.count; ++i) dst[i] = dst[i] > sp[i] ? dst[i] : sp[i]; break;
+          case OP_MIN: for (int64_t i = 0; i < op.count; ++i) dst[i] = dst[i] < sp[i] ? dst[i] : sp[i]; break;
+          default: for (int64_t i = 0; i < op.count; ++i) dst[i] = dst[i] * sp[i]; break;
+        }
+      }
+    }
+    done[rank].store(t, std::memory_order_release);
+  }
+  // peers that read this rank's caller buffers must be done before it returns
+  for (const Wait& w : p.exit_waits[rank])
+    while (done[w.peer].load(std::memory_order_acquire) < w.need) {
+      if (failed->load(std::memory_order_relaxed)) return;
+      std::this_thread::yield();
+    }
+}
+
+template <typename T>
+int run_threads_t(const Program& p, int rop, void* const* in, void* const* out, int iters, double* seconds) {
+  const int P = p.P;
+  std::vector<std::vector<T>> work(P);
+  for (auto& w : work) w.resize((size_t)std::max<int64_t>(p.work_elems, 1));
+  std::atomic<bool> failed{false};
+  double total = 0;
+  for (int it = 0; it < iters; ++it) {
+    std::vector<std::atomic<int>> done(P);
+    for (auto& d : done) d.store(-1);
+    auto t0 = std::chrono::steady_clock::now();
+    std::vector<std::thread> th;
+    for (int r = 0; r < P; ++r)
+      th.emplace_back(run_rank<T>, std::cref(p), r, rop, in, out, work.data(), done.data(), &failed);
+    for (auto& t : th) t.join();
+    total += std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+    if (failed.load()) return -1;
+  }
+  if (seconds) *seconds = total / std::max(1, iters);
+  return 0;
+}
+
+}  // namespace
+
+// Note on reduction order: a non-accumulating step combines into dst starting
+// from its first source, i.e. ((s0 op s1) op s2) ..., like the simulator.
+int run_threads(const Program& p, int dtype, int op, void* const* in, void* const* out, int iters, double* seconds) {
+  switch (dtype) {
+    case DT_F32: return run_threads_t<float>(p, op, in, out, iters, seconds);
+    case DT_F64: return run_threads_t<double>(p, op, in, out, iters, seconds);
+    case DT_I32: return run_threads_t<int32_t>(p, op, in, out, iters, seconds);
+    case DT_I64: return run_threads_t<int64_t>(p, op, in, out, iters, seconds);
+  }
+  return -2;
+}
+
+}  // namespace chb

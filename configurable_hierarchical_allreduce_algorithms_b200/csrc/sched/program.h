@@ -140,6 +140,14 @@ class Builder {
 int simulate(const Program& p, int dtype, int op, void* const* in, void* const* out,
              uint64_t seed, std::string* err);
 
+// Execute a lowered program with one host thread per rank (real concurrency,
+// release / acquire on per-rank round counters); `iters` repetitions, mean wall
+// seconds per repetition in *seconds.  Returns 0, -1 on a wait that expired, -2
+// for an unsupported dtype.  A step whose first source aliases its destination
+// is handled (in-place copies are skipped).
+int run_threads(const Program& p, int dtype, int op, void* const* in, void* const* out, int iters,
+                double* seconds);
+
 // Static check: within one round no region is written by one step and read
 // or written by another (on any rank); and every cross-round cross-rank
 // hazard is covered by a wait chain.  Returns number of violations.

@@ -161,6 +161,21 @@ class Program:
         return outs
 
 
+    def run_threads(self, inputs: list[np.ndarray], op: str = "sum", iters: int = 1):
+        """Run all P ranks as concurrent host threads; returns (outputs, mean seconds per repetition)."""
+        dt = inputs[0].dtype
+        code = _DT_FROM_NP[np.dtype(dt)]
+        ins = [np.ascontiguousarray(x, dtype=dt) for x in inputs]
+        outs = [np.full(self.out_elems, -17, dtype=dt) for _ in range(self.P)]
+        ip = (C.c_void_p * self.P)(*[x.ctypes.data for x in ins])
+        opp = (C.c_void_p * self.P)(*[x.ctypes.data for x in outs])
+        sec = C.c_double(0.0)
+        rc = N.lib().chb_program_run_threads(self._h, code, _OPS[op], ip, opp, iters, C.byref(sec))
+        if rc:
+            raise RuntimeError(f"run_threads({self.name}) failed with code {rc}")
+        return outs, sec.value
+
+
 @lru_cache(maxsize=512)
 def cached_program(coll: str, algo: str, P: int, count: int, k: int = 2, b: int = 1, aux: int = 0,
                    in_symmetric: bool = False, out_symmetric: bool = False, in_place: bool = False) -> Program:

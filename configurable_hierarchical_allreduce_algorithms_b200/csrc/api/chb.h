@@ -121,6 +121,9 @@ int chb_ll_collective(struct chb_comm* c, int mode, int dtype, int op, const voi
 /* mode 0 two-shot allreduce, 1 reduce-scatter, 2 allgather, 3 one-shot allreduce (multimem, sums) */
 int chb_nvls_collective(struct chb_comm* c, int mode, int dtype, const void* in, void* out, long long count,
                         float scale, int nctas, chb_stream_t stream);
+/* allgather through the bulk-copy (TMA) engine; symmetric input, 16-byte alignment, nbytes % 16 == 0 */
+int chb_ag_bulk(struct chb_comm* c, const void* const* in, void* const* out, long long nbytes, int nctas,
+                chb_stream_t stream);
 int chb_rs_fp8_wire(struct chb_comm* c, int dtype, const void* const* in, void* const* out, long long n,
                     float out_scale, int nctas, chb_stream_t stream);
 int chb_rs_adam(struct chb_comm* c, const void* const* grad, void* const* master, void* const* m, void* const* v,

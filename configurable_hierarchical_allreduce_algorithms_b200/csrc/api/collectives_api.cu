@@ -18,6 +18,7 @@ int chb_run_program(chb_comm* c, const chb_program* p, int dtype, int op, const 
 int chb_ll_collective(chb_comm* c, int mode, int dtype, int op, const void* const* in, void* const* out,
                       long long count, float scale, int nctas, cudaStream_t stream);
 long long chb_ll_max_bytes(const chb_comm* c);
+int chb_ag_bulk(chb_comm* c, const void* const* in, void* const* out, long long nbytes, int nctas, cudaStream_t stream);
 int chb_nvls_collective(chb_comm* c, int mode, int dtype, const void* in, void* out, long long count,
                         float scale, int nctas, cudaStream_t stream);
 }
@@ -98,6 +99,10 @@ int chb_collective(chb_comm* c, int coll, const char* algo, int k, int b, int au
                    const void* const* in, void* const* out, int64_t count, float scale, int nctas,
                    cudaStream_t stream) {
   if (!c || !algo || !in || !out) return CHB_ERR_ARG;
+  if (!std::strcmp(algo, "bulk")) {
+    if (coll != CHB_ALLGATHER) return CHB_ERR_UNSUPPORTED;
+    return chb_ag_bulk(c, in, out, count * (long long)chb_dtype_size(dtype), nctas, stream);
+  }
   if (!std::strcmp(algo, "ll2")) {
     if (coll != CHB_ALLREDUCE) return CHB_ERR_UNSUPPORTED;
     return chb_ll_collective(c, 3, dtype, op, in, out, count, scale, nctas, stream);

@@ -1,0 +1,186 @@
+// Allgather by bulk asynchronous copies (the TMA engine): one elected thread per
+// CTA streams 8 KiB chunks peer-global -> shared -> local-global through a ring
+// of shared-memory stages, completion tracked by mbarriers (loads) and bulk
+// groups (stores).  No register staging and almost no issue slots: the SMs
+// stay free for whatever runs next to the collective.  Every load is a plain
+// one-destination bulk copy into this CTA's own shared memory; a peer's memory
+// is read directly.
+// Every wait is bounded.
+//
+// Replaces the inter-group linear allgather / broadcast of the reference
+// (testing/custom_implementations/work_dir/all_gather/all_gather_radix_batch_1_0.cpp:148-163)
+// in its flat (b = 1) form: every rank fetches every block from its owner.
+#include <cstdio>
+
+#include "../api/chb.h"
+#include "../symm/comm.h"
+#include "common.cuh"
+
+namespace chb {
+
+constexpr int kBulkThreads = 128;
+constexpr int kBulkStages = 4;
+constexpr int kBulkChunk = 8192;   // bytes; multiple of 16
+
+struct BulkIo {
+  const char* in[kMaxRanks];   // every rank's block (peer-mapped)
+  char* out[kMaxRanks];        // local ranks' outputs
+};
+
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void bulk_load(unsigned dst_smem, const void* src, unsigned bytes, unsigned bar) {
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst, unsigned src_smem, unsigned bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// nbytes: bytes per block (multiple of 16); all pointers 16-byte aligned.
+__global__ void __launch_bounds__(kBulkThreads)
+ag_bulk_kernel(World w, BulkIo io, long long nbytes) {
+  __shared__ __align__(128) unsigned char stage[kBulkStages][kBulkChunk];
+  __shared__ __align__(8) unsigned long long bars[kBulkStages];
+  const int rank = w.rank0 + (int)blockIdx.y;
+  const int P = w.P;
+  Ctrl* c = w.ctrl[rank];
+  __shared__ unsigned long long s_seq;
+  if (threadIdx.x == 0) {
+    s_seq = ld_volatile_u64(&c->bar_seq);
+    for (int s = 0; s < kBulkStages; ++s) mbar_init(smem_addr(&bars[s]), 1);
+    asm volatile("fence.proxy.async;" ::: "memory");
+  }
+  __syncthreads();
+  const unsigned long long seq = s_seq;
+  bool ok = !ld_volatile_u32(&c->abort);
+  // peers' blocks are final, and nobody still reads the output I am about to overwrite
+  ok = ok && (P == 1 || cta_barrier(w, c, rank, seq + 1ull));
+  if (ok && threadIdx.x == 0) {
+    // the flags were read through the generic proxy, the copies below go through the async proxy
+    asm volatile("fence.proxy.async;" ::: "memory");
+    const long long nch = (nbytes + kBulkChunk - 1) / kBulkChunk;
+    const long long total = nch * P;
+    const long long nct = gridDim.x;
+    const long long mine = (total > (long long)blockIdx.x) ? (total - blockIdx.x + nct - 1) / nct : 0;  // items of this CTA
+    auto item = [&](long long k, const char*& src, char*& dst, unsigned& bytes) {
+      const long long j = (long long)blockIdx.x + k * nct;
+      const int owner = (int)((rank + j / nch) % P);          // start with my own block, then the next ranks
+      const long long off = (j % nch) * kBulkChunk;
+      const long long left = nbytes - off;
+      bytes = (unsigned)(left < kBulkChunk ? left : kBulkChunk);
+      src = io.in[owner] + off;
+      dst = io.out[rank] + (long long)owner * nbytes + off;
+    };
+    const long long pre = mine < kBulkStages ? mine : kBulkStages;
+    for (long long k = 0; k < pre; ++k) {
+      const char* src; char* dst; unsigned bytes;
+      item(k, src, dst, bytes);
+      const unsigned bar = smem_addr(&bars[k % kBulkStages]);
+      mbar_expect_tx(bar, bytes);
+      bulk_load(smem_addr(stage[k % kBulkStages]), src, bytes, bar);
+    }
+    bool failed = false;
+    for (long long k = 0; k < mine && !failed; ++k) {
+      const int s = (int)(k % kBulkStages);
+      const unsigned bar = smem_addr(&bars[s]);
+      const unsigned parity = (unsigned)((k / kBulkStages) & 1);
+      if (!mbar_try_wait(bar, parity)) {
+        const unsigned long long t0 = globaltimer_ns();
+        unsigned spins = 0;
+        while (!mbar_try_wait(bar, parity)) {
+          if ((++spins & 63u) == 0u && globaltimer_ns() - t0 > w.timeout_ns) {
+            record_timeout(c, ST_TIMEOUT_ROUND, rank, (int)k, -3, (unsigned long long)k, 0ull);
+            failed = true;
+            break;
+          }
+        }
+        if (failed) break;
+      }
+      const char* src; char* dst; unsigned bytes;
+      item(k, src, dst, bytes);
+      bulk_store(dst, smem_addr(stage[s]), bytes);
+      if (k + kBulkStages < mine) {
+        bulk_wait_read_all();                        // the store has read the stage: it may be refilled
+        item(k + kBulkStages, src, dst, bytes);
+        mbar_expect_tx(bar, bytes);
+        bulk_load(smem_addr(stage[s]), src, bytes, bar);
+      }
+    }
+    bulk_wait_all();                                 // all my stores have landed
+    if (failed) ok = false;
+  }
+  __syncthreads();
+  if (ld_volatile_u32(&c->abort)) ok = false;
+  // peers are done reading my block
+  if (ok && P > 1) cta_barrier(w, c, rank, seq + 2ull);
+  rank_exit(c, gridDim.x, [&](Ctrl* cc) { cc->bar_seq = seq + 2ull; });
+}
+
+}  // namespace chb
+
+using namespace chb;
+
+extern "C" {
+
+// Allgather of `nbytes` per rank.  in: this rank's block inside the symmetric
+// heap (one pointer per local rank); out: P * nbytes.  16-byte alignment and
+// nbytes % 16 == 0 are required (bulk copies start on 16-byte boundaries).
+int chb_ag_bulk(chb_comm* c, const void* const* in, void* const* out, long long nbytes, int nctas, cudaStream_t stream) {
+  if (!c || !in || !out || nbytes < 0) return CHB_ERR_ARG;
+  if (nbytes % 16) { c->last_error = "bulk allgather needs a multiple of 16 bytes per block"; return CHB_ERR_COUNT; }
+  BulkIo io{};
+  for (int l = 0; l < c->nlocal; ++l) {
+    if ((((uintptr_t)in[l]) | ((uintptr_t)out[l])) & 15u) { c->last_error = "bulk allgather needs 16-byte aligned buffers"; return CHB_ERR_ARG; }
+    io.in[c->rank + l] = (const char*)in[l];
+    io.out[c->rank + l] = (char*)out[l];
+  }
+  if (c->nlocal == 1) {
+    // every rank's block sits at its own offset of the symmetric output when the call is in place
+    // (in == out + rank * nbytes); otherwise all inputs share one heap offset
+    const char* slot = (const char*)out[0] + (long long)c->rank * nbytes;
+    const bool alias = (const char*)in[0] == slot;
+    for (int q = 0; q < c->P; ++q) {
+      const void* mine_as_q = alias ? (const void*)((const char*)out[0] + (long long)q * nbytes) : in[0];
+      char* t = c->translate(mine_as_q, c->rank, q);
+      if (!t) { c->last_error = "bulk allgather input must be inside the symmetric heap"; return CHB_ERR_ARG; }
+      io.in[q] = t;
+    }
+  }
+  if (nbytes == 0) return CHB_SUCCESS;
+  const int max_pair_ctas = (kSigSlots - kSigNvlsBase) / kMaxRanks;
+  int budget = (c->max_ctas * 2) / c->nlocal;     // 128-thread CTAs with 33 KiB of shared memory: two per SM
+  const long long items = ((nbytes + kBulkChunk - 1) / kBulkChunk) * c->P;
+  if (nctas <= 0) nctas = (int)((items + 7) / 8);
+  if (nctas > 96) nctas = 96;
+  if (nctas > max_pair_ctas) nctas = max_pair_ctas;
+  if (nctas > budget) nctas = budget;
+  if (nctas < 1) nctas = 1;
+  World w = c->world;
+  dim3 grid((unsigned)nctas, (unsigned)c->nlocal, 1), block(kBulkThreads, 1, 1);
+  void* args[] = {&w, &io, &nbytes};
+  cudaError_t e = c->nlocal > 1 ? cudaLaunchCooperativeKernel((const void*)ag_bulk_kernel, grid, block, args, 0, stream)
+                                : cudaLaunchKernel((const void*)ag_bulk_kernel, grid, block, args, 0, stream);
+  if (e != cudaSuccess) { c->last_error = std::string("bulk allgather launch failed: ") + cudaGetErrorString(e); return CHB_ERR_CUDA; }
+  return CHB_SUCCESS;
+}
+
+}  // extern "C"

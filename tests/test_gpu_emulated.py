@@ -322,3 +322,26 @@ def test_in_place_flagged_line_kernels(comms):
             for r in range(P):
                 check(bufs[r], exp, torch.float32, P)
     comm.check()
+
+
+@pytest.mark.parametrize("P", [2, 4, 8])
+def test_bulk_copy_allgather(comms, P):
+    """Allgather through the bulk-copy engine (shared-memory ring, mbarriers)."""
+    comm = comms(P)
+    for dtype, n in ((torch.float32, 4), (torch.float32, 2052), (torch.bfloat16, 8 * 3001), (torch.float32, (1 << 20) + 12)):
+        xs = comm.empty(n, dtype)
+        src = make_inputs(P, n, dtype, seed=n)
+        for x, s_ in zip(xs, src):
+            x.copy_(s_)
+        outs = chb.all_gather(comm, xs, algo="bulk")
+        cat = torch.cat(src)
+        for r in range(P):
+            assert torch.equal(outs[r], cat)
+        for nctas in (1, 7):
+            outs = chb.all_gather(comm, xs, algo="bulk", nctas=nctas)
+            assert torch.equal(outs[P - 1], cat)
+    # inputs outside the symmetric heap fall back to a step program
+    loose = make_inputs(P, 1024, torch.float32)
+    outs = chb.all_gather(comm, loose, algo="bulk")
+    assert torch.equal(outs[0], torch.cat(loose))
+    comm.check()

@@ -3,7 +3,7 @@
     torchrun --nproc-per-node N -m configurable_hierarchical_allreduce_algorithms_b200.bench.driver \
         <n_iter> [--overwrite] [b=<group>] [base=<elements>] [num_nodes=<n>] [radix_increment=<step>]
         [coll=allreduce|reduce_scatter|allgather] [dtype=int32|fp32|bf16|fp64] [op=sum|max|min]
-        [algos=radix_batch,ring,...] [reps=50] [backend=gpu|gloo] [out=<file.csv>]
+        [algos=radix_batch,ring,...] [reps=50] [backend=gpu|gloo] [out=<file.csv>] [symmetric=1]
 
 Like the reference's drivers (testing/custom_implementations/work_dir/all_reduce/main.cpp:111-199,
 .../all_gather/main.cpp:109-201, .../reduce_scatter/main.cpp:169-264, testing/main.cpp:146-220):
@@ -14,7 +14,9 @@ CSV row ``algorithm_name,k,b,nprocs,send_count,time,is_correct`` (the same colum
 ``dtype,op,bytes,algbw_GBs,busbw_GBs,ngpus``).  An existing file is appended to unless ``--overwrite``
 is given, and rows are flushed one by one, so an interrupted sweep resumes where it stopped.
 Correctness is AND-reduced and time MAX-reduced over ranks, as in the reference's reduce-scatter
-driver (main.cpp:79-83).  Time is device time (CUDA events) on GPUs and wall time under gloo.
+driver (main.cpp:79-83).  ``symmetric=1`` places input and output in the peer-visible heap (registered
+buffers: nothing is staged, and the kernel-level algorithms ``ll``, ``ll2``, ``nvls``, ``bulk`` can be
+named in ``algos``).  Time is device time (CUDA events) on GPUs and wall time under gloo.
 """
 from __future__ import annotations
 
@@ -42,7 +44,8 @@ def parse(argv):
     if not argv or not argv[0].lstrip("-").isdigit():
         raise SystemExit(__doc__)
     o = {"n_iter": int(argv[0]), "overwrite": False, "b": 0, "base": 1, "num_nodes": 1, "radix_increment": 1,
-         "coll": "allreduce", "dtype": "int32", "op": "sum", "algos": "", "reps": 50, "backend": "", "out": ""}
+         "coll": "allreduce", "dtype": "int32", "op": "sum", "algos": "", "reps": 50, "backend": "", "out": "",
+         "symmetric": 0}
     for a in argv[1:]:
         if a == "--overwrite":
             o["overwrite"] = True
@@ -86,7 +89,13 @@ def main(argv=None):
     if backend == "gpu":
         from ..parallel.comm import Communicator
         total = max_n * P * esz
-        comm = Communicator.from_process_group(scratch_bytes=4 * total + (32 << 20), user_bytes=64 << 20)
+        comm = Communicator.from_process_group(scratch_bytes=4 * total + (32 << 20),
+                                               user_bytes=(64 << 20) + (2 * total + 4096 if o["symmetric"] else 0))
+    sym_in = sym_out = None
+    if comm is not None and o["symmetric"]:
+        # registered buffers: input and output live in the peer-visible heap, so nothing is staged
+        sym_in = comm.empty(max_n * (1 if coll == "allgather" else P), dtype)
+        sym_out = comm.empty(max_n * (1 if coll == "reduce_scatter" else P), dtype)
     from .. import all_gather, all_reduce, reduce_scatter
     from ..parallel import gloo_exec
 
@@ -110,14 +119,17 @@ def main(argv=None):
                 torch.cuda.synchronize()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
+                out = None
+                if sym_out is not None:
+                    out = sym_out[:n * (1 if coll == "reduce_scatter" else P)]
                 if algo == "vendor":
                     y = vendor(x)
                 elif coll == "allreduce":
-                    y = all_reduce(comm, x, op=op, algo=algo, k=kk, b=gb)
+                    y = all_reduce(comm, x, out=out, op=op, algo=algo, k=kk, b=gb)
                 elif coll == "reduce_scatter":
-                    y = reduce_scatter(comm, x, op=op, algo=algo, k=kk, b=gb)
+                    y = reduce_scatter(comm, x, out=out, op=op, algo=algo, k=kk, b=gb)
                 else:
-                    y = all_gather(comm, x, algo=algo, k=kk, b=gb)
+                    y = all_gather(comm, x, out=out, algo=algo, k=kk, b=gb)
                 e1.record()
                 torch.cuda.synchronize()
                 t = e0.elapsed_time(e1) * 1e-3
@@ -167,6 +179,9 @@ def main(argv=None):
         n = o["base"] << i                                   # elements per rank
         n_in = n if coll == "allgather" else n * P
         x = make_input(rank, n_in, dtype, device)
+        if sym_in is not None:
+            sym_in[:n_in].copy_(x)
+            x = sym_in[:n_in]
         ref = vendor(x)
         for algo in algos:
             name = f"{coll}_{algo}" if algo != "radix_batch" else {"allreduce": "all_reduce_radix_batch", "reduce_scatter": "reduce_scatter_radix_batch", "allgather": "allgather_radix_batch"}[coll]

@@ -10,6 +10,7 @@ on it): a few launches of one kernel, inputs larger than L2, about a GB held.
       adam_flat  AdamW on a flat fp32 master of --mib MiB with bf16 parameter copy (data-parallel optimizer)
       noalloc    allocation-free one-shot allreduce, 8 ranks x 8 KiB
       copy1      single rank, allreduce of --mib MiB (degenerates to the local copy, HBM bound)
+      bulk_ag    4 emulated ranks, allgather of --mib MiB per rank through the bulk-copy engine
       rs_adam    4 emulated ranks, reduce-scatter + AdamW on a shard of --mib MiB of gradients per rank
 Prints the CUDA-event time per launch so the same command line can be checked without a profiler first.
 """
@@ -46,6 +47,15 @@ def main():
               "ll_ar": dict(algo="ll"), "ll2_ar": dict(algo="ll2")}[a.case]
         fn = lambda: all_reduce(comm, xs, out=ys, **kw)
         nbytes = n * 4
+    elif a.case == "bulk_ag":
+        from .. import all_gather
+        P = 4
+        comm = Communicator.emulated(P, scratch_bytes=1 << 20, user_bytes=(P + 1) * n * 4 + (1 << 20))
+        xs, ys = comm.empty(n, torch.float32), comm.empty(n * P, torch.float32)
+        for i, x in enumerate(xs):
+            x.copy_(torch.rand(n, device="cuda") + i)
+        fn = lambda: all_gather(comm, xs, out=ys, algo="bulk")
+        nbytes = n * 4 * P
     elif a.case == "copy1":
         comm = Communicator.emulated(1, scratch_bytes=1 << 20, user_bytes=2 * n * 4 + (1 << 20))
         x, y = comm.empty(n, torch.float32), comm.empty(n, torch.float32)

@@ -57,8 +57,8 @@ def candidates(coll: str, P: int, nbytes: int, comm) -> list[tuple]:
             out.append(("nvls", 2, 1, n))
             if coll == "allreduce" and nbytes <= (4 << 20):
                 out.append(("nvls1", 2, 1, n))
-    if coll == "allgather" and nbytes % 16 == 0 and nbytes >= (16 << 10):
-        for n in ((4, 16) if nbytes <= (1 << 20) else (32, 64, 96)):
+    if coll == "allgather" and nbytes % 16 == 0 and nbytes >= (1 << 20):
+        for n in (64, 128):
             out.append(("bulk", 2, 1, n))
     if coll == "allreduce" and nbytes <= (4 << 20):
         out += [("recursive_doubling", 2, 1, 1 if nbytes <= (1 << 20) else 16)]

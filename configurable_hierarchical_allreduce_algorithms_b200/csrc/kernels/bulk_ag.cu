@@ -1,5 +1,5 @@
 // Allgather by bulk asynchronous copies (the TMA engine): one elected thread per
-// CTA streams 8 KiB chunks peer-global -> shared -> local-global through a ring
+// CTA streams 16 KiB chunks peer-global -> shared -> local-global through a ring
 // of shared-memory stages, completion tracked by mbarriers (loads) and bulk
 // groups (stores).  No register staging and almost no issue slots: the SMs
 // stay free for whatever runs next to the collective.  Every load is a plain
@@ -19,8 +19,10 @@
 namespace chb {
 
 constexpr int kBulkThreads = 128;
-constexpr int kBulkStages = 4;
-constexpr int kBulkChunk = 8192;   // bytes; multiple of 16
+constexpr int kBulkStages = 8;
+constexpr int kBulkChunk = 16384;  // bytes; multiple of 16
+constexpr int kBulkLag = 3;        // stores allowed in flight before a stage is refilled (< kBulkStages)
+constexpr int kBulkSmem = kBulkStages * kBulkChunk;
 
 struct BulkIo {
   const char* in[kMaxRanks];   // every rank's block (peer-mapped)
@@ -52,13 +54,14 @@ __device__ __forceinline__ void bulk_store(void* dst, unsigned src_smem, unsigne
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
-__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_lag() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kBulkLag) : "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // nbytes: bytes per block (multiple of 16); all pointers 16-byte aligned.
 __global__ void __launch_bounds__(kBulkThreads)
 ag_bulk_kernel(World w, BulkIo io, long long nbytes) {
-  __shared__ __align__(128) unsigned char stage[kBulkStages][kBulkChunk];
+  extern __shared__ __align__(128) unsigned char stage_mem[];
+  unsigned char (*stage)[kBulkChunk] = reinterpret_cast<unsigned char (*)[kBulkChunk]>(stage_mem);
   __shared__ __align__(8) unsigned long long bars[kBulkStages];
   const int rank = w.rank0 + (int)blockIdx.y;
   const int P = w.P;
@@ -78,13 +81,14 @@ ag_bulk_kernel(World w, BulkIo io, long long nbytes) {
     // the flags were read through the generic proxy, the copies below go through the async proxy
     asm volatile("fence.proxy.async;" ::: "memory");
     const long long nch = (nbytes + kBulkChunk - 1) / kBulkChunk;
-    const long long total = nch * P;
     const long long nct = gridDim.x;
-    const long long mine = (total > (long long)blockIdx.x) ? (total - blockIdx.x + nct - 1) / nct : 0;  // items of this CTA
+    // this CTA takes chunks blockIdx.x, blockIdx.x + nct, ... of every block and alternates between the
+    // owners, so that local copies and NVLink reads are in flight together
+    const long long mych = (nch > (long long)blockIdx.x) ? (nch - blockIdx.x + nct - 1) / nct : 0;
+    const long long mine = mych * P;
     auto item = [&](long long k, const char*& src, char*& dst, unsigned& bytes) {
-      const long long j = (long long)blockIdx.x + k * nct;
-      const int owner = (int)((rank + j / nch) % P);          // start with my own block, then the next ranks
-      const long long off = (j % nch) * kBulkChunk;
+      const int owner = (int)((rank + k % P) % P);            // my own block first, then the next ranks
+      const long long off = ((long long)blockIdx.x + (k / P) * nct) * kBulkChunk;
       const long long left = nbytes - off;
       bytes = (unsigned)(left < kBulkChunk ? left : kBulkChunk);
       src = io.in[owner] + off;
@@ -118,11 +122,14 @@ ag_bulk_kernel(World w, BulkIo io, long long nbytes) {
       const char* src; char* dst; unsigned bytes;
       item(k, src, dst, bytes);
       bulk_store(dst, smem_addr(stage[s]), bytes);
-      if (k + kBulkStages < mine) {
-        bulk_wait_read_all();                        // the store has read the stage: it may be refilled
-        item(k + kBulkStages, src, dst, bytes);
-        mbar_expect_tx(bar, bytes);
-        bulk_load(smem_addr(stage[s]), src, bytes, bar);
+      const long long j = k - kBulkLag;              // its store is kBulkLag groups back
+      if (j >= 0 && j + kBulkStages < mine) {
+        bulk_wait_read_lag();                        // store j has read its stage: it may be refilled
+        const int sj = (int)(j % kBulkStages);
+        const unsigned barj = smem_addr(&bars[sj]);
+        item(j + kBulkStages, src, dst, bytes);
+        mbar_expect_tx(barj, bytes);
+        bulk_load(smem_addr(stage[sj]), src, bytes, barj);
       }
     }
     bulk_wait_all();                                 // all my stores have landed
@@ -167,18 +174,28 @@ int chb_ag_bulk(chb_comm* c, const void* const* in, void* const* out, long long 
   }
   if (nbytes == 0) return CHB_SUCCESS;
   const int max_pair_ctas = (kSigSlots - kSigNvlsBase) / kMaxRanks;
-  int budget = (c->max_ctas * 2) / c->nlocal;     // 128-thread CTAs with 33 KiB of shared memory: two per SM
-  const long long items = ((nbytes + kBulkChunk - 1) / kBulkChunk) * c->P;
-  if (nctas <= 0) nctas = (int)((items + 7) / 8);
-  if (nctas > 96) nctas = 96;
+  int budget = c->max_ctas / c->nlocal;           // 128 KiB of shared memory: one CTA per SM
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute((const void*)ag_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmem) != cudaSuccess) {
+      c->last_error = "bulk allgather: cannot reserve shared memory";
+      return CHB_ERR_CUDA;
+    }
+    attr_set[dev] = true;
+  }
+  const long long chunks = (nbytes + kBulkChunk - 1) / kBulkChunk;
+  if (nctas <= 0 || nctas > chunks) nctas = (int)(chunks < 128 ? chunks : 128);
+  if (nctas > 128) nctas = 128;
   if (nctas > max_pair_ctas) nctas = max_pair_ctas;
   if (nctas > budget) nctas = budget;
   if (nctas < 1) nctas = 1;
   World w = c->world;
   dim3 grid((unsigned)nctas, (unsigned)c->nlocal, 1), block(kBulkThreads, 1, 1);
   void* args[] = {&w, &io, &nbytes};
-  cudaError_t e = c->nlocal > 1 ? cudaLaunchCooperativeKernel((const void*)ag_bulk_kernel, grid, block, args, 0, stream)
-                                : cudaLaunchKernel((const void*)ag_bulk_kernel, grid, block, args, 0, stream);
+  cudaError_t e = c->nlocal > 1 ? cudaLaunchCooperativeKernel((const void*)ag_bulk_kernel, grid, block, args, kBulkSmem, stream)
+                                : cudaLaunchKernel((const void*)ag_bulk_kernel, grid, block, args, kBulkSmem, stream);
   if (e != cudaSuccess) { c->last_error = std::string("bulk allgather launch failed: ") + cudaGetErrorString(e); return CHB_ERR_CUDA; }
   return CHB_SUCCESS;
 }

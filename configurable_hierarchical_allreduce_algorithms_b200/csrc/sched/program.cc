@@ -340,7 +340,7 @@ int simulate_t(const Program& p, int rop, void* const* in, void* const* out, uin
   for (int r = 0; r < P; ++r) {
     work[r].resize((size_t)p.work_elems);
     // poison scratch so that reads of never-written scratch show up
-    std::memset(work[r].data(), 0xFF, work[r].size() * sizeof(T));
+    if (!work[r].empty()) std::memset(work[r].data(), 0xFF, work[r].size() * sizeof(T));
   }
   auto ptr = [&](int rank, int buf, int64_t off) -> T* {
     switch (buf) {

@@ -3,6 +3,7 @@
 // entry points declared in chb_compat.h.
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <string>
 #include <tuple>
 
@@ -13,6 +14,7 @@
 #include "program_handle.h"
 
 extern "C" {
+void chb_program_release(chb_comm* c, const chb_program* p);
 int chb_run_program(chb_comm* c, const chb_program* p, int dtype, int op, const void* const* in,
                     void* const* out, float scale, int nctas, cudaStream_t stream);
 int chb_ll_collective(chb_comm* c, int mode, int dtype, int op, const void* const* in, void* const* out,
@@ -30,11 +32,19 @@ struct Cache {
   std::map<Key, chb_program*> progs;
   ~Cache() { for (auto& kv : progs) delete kv.second; }
 };
-// one cache per communicator, owned here so that comm.h stays free of it
+// one cache per communicator, owned here so that comm.h stays free of it; the map itself is shared by
+// all host threads (calls on ONE communicator are not thread safe, calls on different ones are)
+std::mutex g_cache_mu;
 std::map<chb_comm*, Cache>& caches() {
   static std::map<chb_comm*, Cache> m;
   return m;
 }
+Cache& cache_of(chb_comm* c) {
+  std::lock_guard<std::mutex> g(g_cache_mu);
+  return caches()[c];     // references into a std::map stay valid when other keys are added
+}
+// A caller that sweeps message sizes compiles one program per size; beyond this many the cache starts over.
+constexpr size_t kMaxCachedPrograms = 1024;
 
 const char* coll_name(int coll) {
   switch (coll) {
@@ -59,9 +69,15 @@ bool all_symmetric(const chb_comm* c, const void* const* ptrs) {
 int get_program(chb_comm* c, int coll, const char* algo, int k, int b, int aux, int64_t count, int flags,
                 chb_program** out) {
   Key key(coll, algo, k, b, aux, count, flags);
-  Cache& ca = caches()[c];
+  Cache& ca = cache_of(c);
   auto it = ca.progs.find(key);
   if (it != ca.progs.end()) { *out = it->second; return CHB_SUCCESS; }
+  if (ca.progs.size() >= kMaxCachedPrograms) {
+    // launches that still read the device copies must finish first
+    if (cudaDeviceSynchronize() != cudaSuccess) { c->last_error = "device synchronisation failed"; return CHB_ERR_CUDA; }
+    for (auto& kv : ca.progs) { chb_program_release(c, kv.second); delete kv.second; }
+    ca.progs.clear();
+  }
   try {
     chb::AlgoSpec s;
     s.coll = coll_name(coll);
@@ -91,7 +107,10 @@ int get_program(chb_comm* c, int coll, const char* algo, int k, int b, int aux, 
 
 extern "C" {
 
-void chb_collective_cache_clear(chb_comm* c) { caches().erase(c); }
+void chb_collective_cache_clear(chb_comm* c) {
+  std::lock_guard<std::mutex> g(g_cache_mu);
+  caches().erase(c);
+}
 
 // Generic entry: in / out hold one pointer per local rank.  algo is a step
 // program name (chb_list_algorithms), "ll" or "nvls".  count as in chb.h.

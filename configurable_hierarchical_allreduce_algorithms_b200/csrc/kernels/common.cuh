@@ -263,6 +263,21 @@ union alignas(16) Vec16 {
 // 16-byte load that bypasses L1 (peer data must come from the owner's L2).
 __device__ __forceinline__ uint4 ld16_cg(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
 __device__ __forceinline__ void st16(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
+// 256-bit global accesses (sm_100): half the requests of the 128-bit form for the same bytes.
+// p must be 32-byte aligned.  Loads bypass L1 like ld16_cg (peers write this memory).
+__device__ __forceinline__ void ld32_cg(const void* p, uint4& lo, uint4& hi) {
+  unsigned long long a, b, c, d;
+  asm volatile("ld.global.cg.v4.b64 {%0,%1,%2,%3}, [%4];" : "=l"(a), "=l"(b), "=l"(c), "=l"(d) : "l"(p) : "memory");
+  lo = make_uint4((unsigned)a, (unsigned)(a >> 32), (unsigned)b, (unsigned)(b >> 32));
+  hi = make_uint4((unsigned)c, (unsigned)(c >> 32), (unsigned)d, (unsigned)(d >> 32));
+}
+__device__ __forceinline__ void st32(void* p, const uint4& lo, const uint4& hi) {
+  const unsigned long long a = (unsigned long long)lo.x | ((unsigned long long)lo.y << 32);
+  const unsigned long long b = (unsigned long long)lo.z | ((unsigned long long)lo.w << 32);
+  const unsigned long long c = (unsigned long long)hi.x | ((unsigned long long)hi.y << 32);
+  const unsigned long long d = (unsigned long long)hi.z | ((unsigned long long)hi.w << 32);
+  asm volatile("st.global.v4.b64 [%0], {%1,%2,%3,%4};" ::"l"(p), "l"(a), "l"(b), "l"(c), "l"(d) : "memory");
+}
 
 template <typename T>
 __device__ __forceinline__ void vec_to_acc(const uint4& v, typename Elem<T>::Acc* a) {

@@ -345,3 +345,29 @@ def test_bulk_copy_allgather(comms, P):
     outs = chb.all_gather(comm, loose, algo="bulk")
     assert torch.equal(outs[0], torch.cat(loose))
     comm.check()
+
+
+def test_single_rank_world_is_a_local_copy(cuda):
+    """P = 1: every collective degenerates to a copy; large aligned ones take the lean copy kernel,
+    the rest the interpreter; both keep the communicator's launch counter."""
+    comm = Communicator.emulated(1, scratch_bytes=1 << 20, user_bytes=(16 << 20) + 4096)
+    before = comm.status()["launches"]
+    calls = 0
+    for n in ((1 << 20) + 4, (1 << 20) + 3, 1 << 18, 5):
+        for dtype in (torch.float32, torch.bfloat16):
+            x = torch.randn(n, device="cuda").to(dtype)
+            for fn in (chb.all_reduce, chb.reduce_scatter, chb.all_gather):
+                y = fn(comm, x)
+                calls += 1
+                assert torch.equal(y, x), (n, dtype, fn.__name__)
+            y = chb.all_reduce(comm, x, scale=0.5)
+            calls += 1
+            assert torch.allclose(y.float(), x.float() * 0.5, rtol=1e-2)
+    xs, ys = comm.empty(1 << 21, torch.float32), comm.empty(1 << 21, torch.float32)
+    xs.copy_(torch.randn(1 << 21, device="cuda"))
+    chb.all_reduce(comm, xs, out=ys)
+    calls += 1
+    assert torch.equal(xs, ys)
+    assert comm.status()["launches"] - before == calls
+    comm.check()
+    comm.close()

@@ -1,0 +1,80 @@
+"""Two physical levels on GPUs: the box's GPUs are split into "boxes" of L ranks; inside
+a box the collectives are this library's kernels on a sub-communicator, across boxes the
+lanes use NCCL.  With 2 GPUs: 2 boxes of 1; with 4 or more also 2-rank boxes.  Needs >= 2 GPUs."""
+import os
+import socket
+import traceback
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.multigpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _inp(r, n):
+    g = torch.Generator(device="cuda").manual_seed(77 + r)
+    return torch.rand(n, generator=g, device="cuda") * 2 - 1
+
+
+def _worker(rank, P, port, q):
+    try:
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=P, device_id=torch.device("cuda", rank))
+        import configurable_hierarchical_allreduce_algorithms_b200 as chb
+        from configurable_hierarchical_allreduce_algorithms_b200.parallel import hierarchy as H
+
+        notes = []
+        for L in [l for l in (1, 2, 4) if P % l == 0 and l < P]:
+            intra_g, inter_g = H.split_world(L)
+            comm = chb.Communicator.from_process_group(group=intra_g, backend="ipc", scratch_bytes=64 << 20, user_bytes=8 << 20)
+            two = H.TwoLevel(H.DeviceLevel(comm), H.LibraryLevel(inter_g))
+            assert (two.P, two.rank) == (P, rank)
+            for n in (1, 1000, (1 << 18) + 5):
+                ins = [_inp(r, n * P) for r in range(P)]
+                exp = torch.stack([x.double() for x in ins]).sum(0)
+                y = two.all_reduce(ins[rank])
+                torch.testing.assert_close(y.double(), exp, rtol=1e-5, atol=1e-5 * P)
+                y = two.reduce_scatter(ins[rank])
+                torch.testing.assert_close(y.double(), exp[rank * n:(rank + 1) * n], rtol=1e-5, atol=1e-5 * P)
+                y = two.all_gather(ins[rank][:n].contiguous())
+                assert torch.equal(y, torch.cat([i[:n] for i in ins]))
+            comm.check()
+            torch.cuda.synchronize()
+            dist.barrier()
+            comm.close()
+            notes.append(f"L={L} ok")
+        dist.destroy_process_group()
+        q.put((rank, "ok", "; ".join(notes)))
+    except Exception:  # noqa: BLE001
+        q.put((rank, "fail", traceback.format_exc()))
+
+
+@pytest.mark.timeout(600)
+def test_two_level_on_gpus():
+    P = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    if P < 2:
+        pytest.skip("needs at least two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, P, port, q)) for r in range(P)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=500) for _ in range(P)]
+    for p in procs:
+        p.join(60)
+    bad = [r for r in res if r[1] != "ok"]
+    assert not bad, "\n".join(f"rank {r[0]}:\n{r[2]}" for r in bad)
+    print(res[0][2])

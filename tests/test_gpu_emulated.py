@@ -371,3 +371,17 @@ def test_single_rank_world_is_a_local_copy(cuda):
     assert comm.status()["launches"] - before == calls
     comm.check()
     comm.close()
+
+
+def test_program_cache_starts_over_when_full(cuda):
+    """More distinct message sizes than the per-communicator program cache holds: the cache
+    (host programs and their device copies) is dropped and refilled without disturbing results."""
+    comm = Communicator.emulated(2, scratch_bytes=1 << 20, user_bytes=1 << 20)
+    base = make_inputs(2, 1200, torch.int32)
+    for n in range(1, 1101):
+        ins = [t[:n] for t in base]
+        outs = chb.all_reduce(comm, ins, algo="recursive_doubling")
+        if n % 97 == 0 or n > 1090:
+            assert torch.equal(outs[0], ins[0] + ins[1]) and torch.equal(outs[1], outs[0])
+    comm.check()
+    comm.close()

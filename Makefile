@@ -13,7 +13,7 @@ RADIX_INCREMENT ?= 1
 PORT     ?= 29555
 TORCHRUN := $(PYTHON) -m torch.distributed.run --nnodes=1 --nproc-per-node $(NGPUS) --master-addr 127.0.0.1 --master-port $(PORT)
 
-.PHONY: build test test-gpu run-benchmark run-benchmark-cpu tune bench clean
+.PHONY: build test test-gpu run-benchmark run-benchmark-native run-benchmark-cpu tune bench clean
 
 build:                 ## compile libchb.so for sm_100a
 	$(PYTHON) -m $(PKG)._build -v
@@ -26,6 +26,10 @@ test-gpu:              ## GPU tests (run on a B200)
 
 run-benchmark:         ## sweep of one collective on NGPUS GPUs, CSV like the reference's drivers
 	$(TORCHRUN) -m $(PKG).bench.driver $(N_ITER) $(if $(filter 1,$(OVERWRITE)),--overwrite,) b=$(B) base=$(BASE) \
+	    coll=$(COLL) dtype=$(DTYPE) radix_increment=$(RADIX_INCREMENT) num_nodes=1
+
+run-benchmark-native:  ## the same sweep by the native launcher (no Python, no MPI: forks one process per GPU)
+	$(PKG)/bin/chb_bench $(N_ITER) $(if $(filter 1,$(OVERWRITE)),--overwrite,) ngpus=$(NGPUS) b=$(B) base=$(BASE) \
 	    coll=$(COLL) dtype=$(DTYPE) radix_increment=$(RADIX_INCREMENT) num_nodes=1
 
 run-benchmark-cpu:     ## the same sweep over gloo on the host (oversubscribed ranks, like SYSTEM_ENVIRONMENT=LOCAL)
@@ -42,4 +46,4 @@ debug-%:               ## make debug-allreduce.radix_batch P=8 B=2 : self-checki
 	$(PYTHON) -m $(PKG).bench.debug $(word 1,$(subst ., ,$*)) $(word 2,$(subst ., ,$*)) P=$(NGPUS) b=$(if $(filter $(NGPUS),$(B)),1,$(B))
 
 clean:
-	rm -rf $(PKG)/build $(PKG)/libchb.so
+	rm -rf $(PKG)/build $(PKG)/bin $(PKG)/libchb.so

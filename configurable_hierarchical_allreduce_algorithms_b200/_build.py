@@ -23,6 +23,8 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OBJ = HERE / "build" / "obj"
 LIB = HERE / "libchb.so"
+TOOLS = CSRC / "tools"              # stand-alone programs linked against the library
+BIN = HERE / "bin"
 
 NVCC = os.environ.get("CHB_NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
 CXX = os.environ.get("CXX") or shutil.which("g++") or "g++"
@@ -35,8 +37,8 @@ CXX_FLAGS = ["-O2", "-fPIC", "-std=c++17", "-Wall", "-Wno-sign-compare"]
 
 
 def _sources():
-    cc = sorted(CSRC.rglob("*.cc"))
-    cu = sorted(CSRC.rglob("*.cu"))
+    cc = sorted(p for p in CSRC.rglob("*.cc") if TOOLS not in p.parents)
+    cu = sorted(p for p in CSRC.rglob("*.cu") if TOOLS not in p.parents)
     return cc, cu
 
 
@@ -94,9 +96,25 @@ def build(verbose: bool = False, force: bool = False) -> Path:
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+    if cu:
+        _build_tools(hdr_t, force)
     if verbose and logs:
         print("\n".join(logs))
     return LIB
+
+
+def _build_tools(hdr_t: float, force: bool) -> None:
+    """``bin/<name>`` from every ``csrc/tools/<name>.cu`` (run-path relative, so the tree can be moved)."""
+    BIN.mkdir(exist_ok=True)
+    for src in sorted(TOOLS.glob("*.cu")):
+        exe = BIN / src.stem
+        if not force and exe.exists() and exe.stat().st_mtime >= max(src.stat().st_mtime, hdr_t, LIB.stat().st_mtime):
+            continue
+        cmd = [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-I", str(CSRC),
+               str(src), "-o", str(exe), "-L", str(HERE), "-lchb", "-ldl", "-Xlinker", "-rpath=$ORIGIN/.."]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"tool build failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
 
 
 if __name__ == "__main__":

@@ -93,6 +93,13 @@ size_t chb_heap_bytes(int P, size_t ll_payload_bytes, size_t scratch_bytes, size
 struct chb_comm* chb_comm_create(int rank, int P, int nlocal, void* const* heap_ptrs, void* mc_ptr,
                                  size_t ll_payload_bytes, size_t scratch_bytes, size_t user_bytes,
                                  char* err, int errlen);
+/* Native constructors that own their heaps (see boot/bootstrap.h for the rendezvous):
+ * all P ranks on the current GPU in this process / one rank per process and GPU of one box. */
+struct chb_bootstrap;
+struct chb_comm* chb_comm_create_emulated(int P, size_t ll_payload_bytes, size_t scratch_bytes, size_t user_bytes,
+                                          char* err, int errlen);
+struct chb_comm* chb_comm_create_ipc(struct chb_bootstrap* boot, size_t ll_payload_bytes, size_t scratch_bytes,
+                                     size_t user_bytes, char* err, int errlen);
 void chb_comm_destroy(struct chb_comm* c);
 const char* chb_comm_last_error(const struct chb_comm* c);
 int chb_comm_set_timeout_us(struct chb_comm* c, unsigned long long us);

@@ -5,6 +5,7 @@
 #include <string>
 
 #include "../api/chb.h"
+#include "../boot/bootstrap.h"
 #include "comm.h"
 
 using namespace chb;
@@ -124,6 +125,8 @@ void chb_comm_destroy(chb_comm* c) {
   for (auto& kv : c->blobs) cudaFree(kv.second);
   if (c->ctrl) cudaFree(c->ctrl);
   if (c->trace) cudaFree(c->trace);
+  for (void* q : c->ipc_opened) cudaIpcCloseMemHandle(q);
+  if (c->owned_heap) cudaFree(c->owned_heap);
   delete c;
 }
 
@@ -249,5 +252,71 @@ int chb_dev_alloc(size_t bytes, void** ptr) {
   return cudaDeviceSynchronize() == cudaSuccess ? CHB_SUCCESS : CHB_ERR_CUDA;
 }
 int chb_dev_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? CHB_SUCCESS : CHB_ERR_CUDA; }
+
+// ---- native constructors: no Python, no torch.distributed ------------------------------------------
+// All P ranks on the current GPU (one process): one allocation split P ways.
+chb_comm* chb_comm_create_emulated(int P, size_t ll_payload_bytes, size_t scratch_bytes, size_t user_bytes,
+                                   char* err, int errlen) {
+  auto fail = [&](const char* m) -> chb_comm* {
+    if (err && errlen > 0) std::snprintf(err, (size_t)errlen, "%s", m);
+    return nullptr;
+  };
+  if (P < 1 || P > kMaxRanks) return fail("number of ranks must be between 1 and 16");
+  const size_t hb = chb_heap_bytes(P, ll_payload_bytes, scratch_bytes, user_bytes);
+  void* base = nullptr;
+  if (cudaMalloc(&base, hb * (size_t)P) != cudaSuccess) return fail("cudaMalloc(heap) failed");
+  cudaMemset(base, 0, hb * (size_t)P);
+  void* ptrs[kMaxRanks];
+  for (int p = 0; p < P; ++p) ptrs[p] = (char*)base + hb * (size_t)p;
+  chb_comm* c = chb_comm_create(0, P, P, ptrs, nullptr, ll_payload_bytes, scratch_bytes, user_bytes, err, errlen);
+  if (!c) { cudaFree(base); return nullptr; }
+  c->owned_heap = base;
+  return c;
+}
+
+// One rank per process and per GPU of one box: every rank allocates its heap on the current device,
+// the cudaIpc handles travel through the bootstrap's allgather, peers' heaps are mapped.
+chb_comm* chb_comm_create_ipc(chb_bootstrap* boot, size_t ll_payload_bytes, size_t scratch_bytes, size_t user_bytes,
+                              char* err, int errlen) {
+  auto fail = [&](const std::string& m) -> chb_comm* {
+    if (err && errlen > 0) std::snprintf(err, (size_t)errlen, "%s", m.c_str());
+    if (boot) chb_bootstrap_abort(boot);
+    return nullptr;
+  };
+  if (!boot) return fail("null bootstrap");
+  const int P = chb_bootstrap_world(boot), rank = chb_bootstrap_rank(boot);
+  if (P < 1 || P > kMaxRanks) return fail("number of ranks must be between 1 and 16");
+  const size_t hb = chb_heap_bytes(P, ll_payload_bytes, scratch_bytes, user_bytes);
+  void* mine = nullptr;
+  char handle[64];
+  if (chb_ipc_alloc(hb, &mine, handle) != CHB_SUCCESS) return fail("cudaIpc allocation of the heap failed");
+  std::vector<char> all(64 * (size_t)P);
+  if (chb_bootstrap_allgather(boot, handle, all.data(), 64) != CHB_SUCCESS) { cudaFree(mine); return fail("handle exchange failed"); }
+  void* ptrs[kMaxRanks];
+  std::vector<void*> opened;
+  for (int p = 0; p < P; ++p) {
+    if (p == rank) { ptrs[p] = mine; continue; }
+    void* q = nullptr;
+    if (chb_ipc_open(all.data() + 64 * (size_t)p, &q) != CHB_SUCCESS) {
+      for (void* o : opened) cudaIpcCloseMemHandle(o);
+      cudaFree(mine);
+      return fail("cannot map the heap of rank " + std::to_string(p) + " (no peer access?)");
+    }
+    opened.push_back(q);
+    ptrs[p] = q;
+  }
+  chb_comm* c = chb_comm_create(rank, P, 1, ptrs, nullptr, ll_payload_bytes, scratch_bytes, user_bytes, err, errlen);
+  if (!c) {
+    for (void* o : opened) cudaIpcCloseMemHandle(o);
+    cudaFree(mine);
+    chb_bootstrap_abort(boot);
+    return nullptr;
+  }
+  c->owned_heap = mine;
+  c->ipc_opened = opened;
+  // nobody signals into a heap before every rank has set up
+  if (chb_bootstrap_barrier(boot) != CHB_SUCCESS) { chb_comm_destroy(c); return fail("ranks did not all finish the set-up"); }
+  return c;
+}
 
 }  // extern "C"

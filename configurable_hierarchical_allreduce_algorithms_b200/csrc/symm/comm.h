@@ -39,6 +39,9 @@ struct chb_comm {
   // device copies of compiled programs, keyed by the program's unique id
   std::map<uint64_t, void*> blobs;
   std::string last_error;
+  // set only by the native constructors (chb_comm_create_ipc / chb_comm_create_emulated), which own the heap
+  void* owned_heap = nullptr;
+  std::vector<void*> ipc_opened;
 
   char* sig_ptr(int p) const { return heap[p]; }
   char* ll_ptr(int p) const { return heap[p] + sig_bytes; }

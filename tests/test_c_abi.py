@@ -30,3 +30,17 @@ def test_c_example_runs(tmp_path, cuda):
     exe = _build(tmp_path)
     r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and "C ABI OK" in r.stdout, r.stdout + r.stderr
+
+
+def test_native_bootstrap_rendezvous(tmp_path):
+    """Forked C ranks meet through the shared-memory bootstrap; a missing rank ends in a timeout, not a hang."""
+    from configurable_hierarchical_allreduce_algorithms_b200 import _native
+    _native.lib()
+    cc = shutil.which("gcc") or "gcc"
+    exe = tmp_path / "bootstrap_test"
+    cmd = [cc, str(ROOT / "tests" / "native" / "bootstrap_test.c"), "-I", str(PKG / "csrc" / "boot"),
+           "-L", str(PKG), "-lchb", f"-Wl,-rpath,{PKG}", "-o", str(exe)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "BOOTSTRAP OK" in r.stdout, r.stdout + r.stderr

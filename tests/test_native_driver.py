@@ -1,0 +1,68 @@
+"""The native launcher + benchmark driver (`bin/chb_bench`, no Python and no MPI in its call path):
+argument grammar on CPU, an emulated world on one GPU, forked one-rank-per-GPU processes on several."""
+import subprocess
+from pathlib import Path
+
+import pandas as pd
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+EXE = ROOT / "configurable_hierarchical_allreduce_algorithms_b200" / "bin" / "chb_bench"
+COLS = ["algorithm_name", "k", "b", "nprocs", "send_count", "time", "is_correct"]
+
+
+@pytest.fixture(scope="module")
+def exe():
+    from configurable_hierarchical_allreduce_algorithms_b200 import _build
+    _build.build()
+    assert EXE.exists()
+    return str(EXE)
+
+
+def test_argument_grammar(exe, tmp_path):
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 2 and "usage" in r.stderr
+    r = subprocess.run([exe, "2", "bogus=1"], capture_output=True, text=True)
+    assert r.returncode == 2 and "Unknown parameter: bogus=1" in r.stderr
+    r = subprocess.run([exe, "2", "coll=broadcast"], capture_output=True, text=True)
+    assert r.returncode == 2
+    r = subprocess.run([exe, "2", "emulate=4", "b=3"], capture_output=True, text=True)
+    assert r.returncode == 2 and "divide" in r.stderr
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("coll,dtype,op", [("allreduce", "int32", "sum"), ("allreduce", "bf16", "max"),
+                                           ("reduce_scatter", "fp32", "sum"), ("allgather", "fp64", "sum")])
+def test_emulated_world(exe, tmp_path, cuda, coll, dtype, op):
+    out = tmp_path / "r.csv"
+    args = [exe, "3", "--overwrite", "emulate=4", "b=2", "base=1000", f"coll={coll}", f"dtype={dtype}", f"op={op}", "reps=2", f"out={out}"]
+    r = subprocess.run(args, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    df = pd.read_csv(out)
+    assert list(df.columns[:7]) == COLS
+    assert (df.is_correct == 1).all() and (df.nprocs == 4).all() and set(df.send_count) == {1000, 2000, 4000}
+    assert len(set(df.algorithm_name)) >= 3
+    n1 = len(df)
+    r = subprocess.run(args[:2] + args[3:] + ["symmetric=1", "algos=radix_batch,ll"], capture_output=True, text=True, timeout=300)   # appends
+    assert r.returncode == 0, r.stdout + r.stderr
+    df2 = pd.read_csv(out)
+    assert len(df2) > n1 and (df2.is_correct == 1).all()
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("coll", ["allreduce", "reduce_scatter", "allgather"])
+def test_forked_ranks_one_per_gpu(exe, tmp_path, coll):
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    n = 2 if n < 4 else 4
+    out = tmp_path / "r.csv"
+    r = subprocess.run([exe, "3", "--overwrite", f"ngpus={n}", f"b={n}", "base=4096", f"coll={coll}", "dtype=fp32", "reps=3",
+                        "symmetric=1", f"out={out}"], capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout + r.stderr
+    df = pd.read_csv(out)
+    assert (df.is_correct == 1).all() and (df.nprocs == n).all()
+    names = set(df.algorithm_name)
+    assert any("radix_batch" in x for x in names)
+    assert names & {"MPICH_allreduce", "reduce_scatter_standard", "allgather_standard"}, names     # the NCCL row

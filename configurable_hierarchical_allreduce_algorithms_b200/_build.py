@@ -33,6 +33,8 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
 ]
+if os.environ.get("CHB_CHECK_BOUNDS") == "1":   # checked build: in-kernel range test of every step
+    NVCC_FLAGS.append("-DCHB_CHECK_BOUNDS")
 CXX_FLAGS = ["-O2", "-fPIC", "-std=c++17", "-Wall", "-Wno-sign-compare"]
 
 

@@ -33,6 +33,7 @@ enum StatusCode : unsigned {
   ST_TIMEOUT_GRID = 4,    // a CTA of this rank never reached the rank-local barrier
   ST_TIMEOUT_LL = 5,      // a flagged line never arrived
   ST_TIMEOUT_BARRIER = 6, // stand-alone barrier
+  ST_OUT_OF_RANGE = 7,    // a step would touch memory outside its buffer (checked builds only); the step is skipped
 };
 
 // Per-rank control block in the rank's own device memory.

@@ -36,6 +36,7 @@ struct DevRound { int step_begin, step_end, wait_begin, wait_end, sig_begin, sig
 struct DevHeader {
   int P, nrounds, nsteps, nsrcs, nwaits, nsigs;
   long long off_rounds, off_steps, off_srcs, off_waits, off_sigs, off_exit;
+  long long limit[3];   // elements of the caller input, caller output and scratch (for range checks)
 };
 
 struct IoTable {
@@ -43,10 +44,31 @@ struct IoTable {
   char* out[kMaxRanks];
 };
 
+// Every range a program touches lies inside the buffer it names: checked once per program before
+// its schedule is uploaded, so that a generator bug cannot turn into a stray peer access.
+static bool ranges_ok(const Program& p, std::string* why) {
+  const int64_t lim[3] = {p.in_elems, p.out_elems, p.work_elems};
+  for (size_t i = 0; i < p.ops.size(); ++i) {
+    const Op& o = p.ops[i];
+    bool ok = o.rank >= 0 && o.rank < p.P && o.dst_buf >= 0 && o.dst_buf <= 2 && o.count >= 0 && o.dst_off >= 0 &&
+              o.dst_off + o.count <= lim[o.dst_buf];
+    for (const Src& x : o.srcs)
+      ok = ok && x.peer >= 0 && x.peer < p.P && x.buf >= 0 && x.buf <= 2 && x.off >= 0 && x.off + o.count <= lim[x.buf];
+    if (!ok) {
+      *why = "step " + std::to_string(i) + " of " + p.name + " addresses memory outside its buffer";
+      return false;
+    }
+  }
+  return true;
+}
+
 static std::vector<char> make_blob(const Program& p) {
   DevHeader h{};
   h.P = p.P;
   h.nrounds = p.nrounds;
+  h.limit[0] = p.in_elems;
+  h.limit[1] = p.out_elems;
+  h.limit[2] = p.work_elems;
   std::vector<DevRound> rounds((size_t)p.P * p.nrounds);
   std::vector<DevStep> steps;
   std::vector<DevSrc> srcs;
@@ -111,7 +133,7 @@ static std::vector<char> make_blob(const Program& p) {
 template <typename T>
 __device__ __forceinline__ void run_step(const DevStep& st, const DevSrc* __restrict__ srcs, const World& w,
                                          const IoTable& io, int rank, unsigned part, unsigned nparts,
-                                         int op, float scale, const char** s_ptr, int* s_meta) {
+                                         int op, float scale, const char** s_ptr, int* s_meta, const long long* limit) {
   using Acc = typename Elem<T>::Acc;
   constexpr int VE = Elem<T>::kPerVec;
   const int tid = threadIdx.x;
@@ -131,6 +153,20 @@ __device__ __forceinline__ void run_step(const DevStep& st, const DevSrc* __rest
       s_ptr[tid] = base + s.off * (long long)sizeof(T);
     }
   }
+#ifdef CHB_CHECK_BOUNDS
+  // checked build: the same range test as on the host, on the values the kernel actually uses
+  if (tid == 0) {
+    bool ok = st.dst_off >= 0 && st.dst_off + st.count <= limit[st.dst_buf];
+    for (int j = 0; j < st.nsrc; ++j) {
+      const DevSrc s = srcs[st.src_begin + j];
+      ok = ok && s.off >= 0 && s.off + st.count <= limit[s.buf] && s.peer >= 0 && s.peer < w.P;
+    }
+    s_meta[0] = ok ? 0 : -1;
+    if (!ok) record_timeout(w.ctrl[rank], ST_OUT_OF_RANGE, rank, -1, -1, (unsigned long long)st.dst_off, (unsigned long long)st.count);
+  }
+  __syncthreads();
+  if (s_meta[0] < 0) return;
+#endif
   __syncthreads();
   if (tid == 0) {
     unsigned long long m = (unsigned long long)s_ptr[kMaxSrc];
@@ -328,14 +364,14 @@ interp_kernel(World w, const char* __restrict__ blob, IoTable io, int op, float 
       const bool small = st.count * (long long)sizeof(T) < kSmallStepBytes;
       if (small) {
         if ((unsigned)(s - R.step_begin) % nct == cta)
-          run_step<T>(st, srcs, w, io, rank, 0u, 1u, op, scale, s_ptr, s_meta);
+          run_step<T>(st, srcs, w, io, rank, 0u, 1u, op, scale, s_ptr, s_meta, h->limit);
       } else if (na == 0) {
-        run_step<T>(st, srcs, w, io, rank, cta, nct, op, scale, s_ptr, s_meta);
+        run_step<T>(st, srcs, w, io, rank, cta, nct, op, scale, s_ptr, s_meta, h->limit);
       } else {
         bool remote = false;
         for (int j = 0; j < st.nsrc; ++j) remote |= (srcs[st.src_begin + j].peer != rank);
-        if (remote && cta < na) run_step<T>(st, srcs, w, io, rank, cta, na, op, scale, s_ptr, s_meta);
-        if (!remote && cta >= na) run_step<T>(st, srcs, w, io, rank, cta - na, nct - na, op, scale, s_ptr, s_meta);
+        if (remote && cta < na) run_step<T>(st, srcs, w, io, rank, cta, na, op, scale, s_ptr, s_meta, h->limit);
+        if (!remote && cta >= na) run_step<T>(st, srcs, w, io, rank, cta - na, nct - na, op, scale, s_ptr, s_meta, h->limit);
       }
     }
     ok = rank_barrier(c, nct, gen, w.timeout_ns, rank, t);
@@ -417,6 +453,7 @@ static int get_blob(chb_comm* c, const chb_program* p, void** out) {
   auto it = c->blobs.find(p->uid);
   if (it != c->blobs.end()) { *out = it->second; return CHB_SUCCESS; }
   if (p->prog.stats.max_nsrc > kMaxSrc) { c->last_error = "program has a step with too many sources"; return CHB_ERR_UNSUPPORTED; }
+  if (!ranges_ok(p->prog, &c->last_error)) return CHB_ERR_ARG;
   std::vector<char> blob = make_blob(p->prog);
   void* d = nullptr;
   if (cudaMalloc(&d, blob.size()) != cudaSuccess) { c->last_error = "cudaMalloc(program blob) failed"; return CHB_ERR_NO_MEM; }

@@ -62,7 +62,7 @@ STATUS_NAMES = {
     0: "ok", 1: "timeout waiting for a peer to leave the previous collective",
     2: "timeout waiting for a peer's round", 3: "timeout waiting for peers to finish reading",
     4: "timeout at the rank-local barrier", 5: "timeout waiting for a flagged line",
-    6: "timeout in barrier",
+    6: "timeout in barrier", 7: "a step addressed memory outside its buffer (checked build)",
 }
 
 

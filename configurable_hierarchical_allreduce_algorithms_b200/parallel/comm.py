@@ -51,6 +51,10 @@ N.optional("chb_run_program", i32, [vp, vp, i32, i32, C.POINTER(vp), C.POINTER(v
 N.optional("chb_ll_max_bytes", C.c_longlong, [vp])
 N.optional("chb_ll_collective", i32, [vp, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), C.c_longlong, f32, i32, vp])
 N.optional("chb_collective", i32, [vp, i32, C.c_char_p, i32, i32, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), i64, f32, i32, vp])
+N.optional("chb_bootstrap_create", i32, [C.c_char_p, i32, i32, i32, C.POINTER(vp)])
+N.optional("chb_bootstrap_barrier", i32, [vp])
+N.optional("chb_bootstrap_destroy", None, [vp])
+N.optional("chb_comm_create_ipc", vp, [vp, C.c_size_t, C.c_size_t, C.c_size_t, C.c_char_p, i32])
 N.optional("chb_nvls_collective", i32, [vp, i32, i32, vp, vp, C.c_longlong, f32, i32, vp])
 
 DTYPES = {
@@ -177,6 +181,35 @@ class Communicator:
         dist.barrier(group)  # nobody signals into a heap before every rank has set up
         return self
 
+    @classmethod
+    def from_shared_memory(cls, name: str, rank: int, world: int, ll_bytes: int = 1 << 20,
+                           scratch_bytes: int = 256 << 20, user_bytes: int = 64 << 20,
+                           timeout_us: int = 10_000_000, rendezvous_timeout_ms: int = 60_000):
+        """One rank per process without ``torch.distributed``: the ranks of one box meet through the
+        native shared-memory bootstrap (``name`` = "/something", the same on every rank, unique per job)
+        and exchange cudaIpc handles of their heaps there.  The path the native launcher uses."""
+        L = N.lib()
+        if not hasattr(L, "chb_comm_create_ipc"):
+            raise N.NativeLibraryMissing("libchb.so was built without its CUDA half")
+        self = cls._new()
+        dev = torch.cuda.current_device()
+        torch.cuda.init()
+        torch.zeros(1, device=f"cuda:{dev}")          # the primary context exists before the native side allocates
+        boot = vp()
+        rc = L.chb_bootstrap_create(name.encode(), rank, world, rendezvous_timeout_ms, C.byref(boot))
+        if rc:
+            raise CollectiveError(rc, f"rendezvous '{name}' of {world} ranks failed")
+        self._boot = boot
+        err = C.create_string_buffer(256)
+        h = L.chb_comm_create_ipc(boot, ll_bytes, scratch_bytes, user_bytes, err, len(err))
+        if not h:
+            L.chb_bootstrap_destroy(boot)
+            self._boot = None
+            raise CollectiveError(N.ERR_OTHER, err.value.decode())
+        self.backend = "ipc-native"
+        self._adopt(h, world, rank, 1, dev, timeout_us)
+        return self
+
     def _heap_symm_mem(self, group, heap_bytes, dev):
         import torch.distributed._symmetric_memory as symm_mem
 
@@ -231,6 +264,10 @@ class Communicator:
         h = L.chb_comm_create(rank, P, nlocal, ptrs, mc or None, ll_bytes, scratch_bytes, user_bytes, err, len(err))
         if not h:
             raise CollectiveError(N.ERR_ARG, err.value.decode())
+        self._adopt(h, P, rank, nlocal, dev, timeout_us)
+
+    def _adopt(self, h, P, rank, nlocal, dev, timeout_us):
+        L = N.lib()
         self._h = h
         self.P, self.rank, self.nlocal, self.device = P, rank, nlocal, dev
         info = (i64 * 11)()
@@ -245,6 +282,8 @@ class Communicator:
         if self._h:
             L = N.lib()
             torch.cuda.synchronize()
+            if getattr(self, "_boot", None):
+                L.chb_bootstrap_barrier(self._boot)      # nobody frees a heap that a peer may still read
             L.chb_comm_destroy(self._h)
             self._h = None
             for q in self._ipc_opened:
@@ -253,6 +292,9 @@ class Communicator:
             if self._own_heap_ptr:
                 L.chb_dev_free(self._own_heap_ptr)
                 self._own_heap_ptr = None
+            if getattr(self, "_boot", None):
+                L.chb_bootstrap_destroy(self._boot)
+                self._boot = None
             self._keep = []
 
     def __del__(self):

@@ -78,3 +78,47 @@ def test_two_level_on_gpus():
     bad = [r for r in res if r[1] != "ok"]
     assert not bad, "\n".join(f"rank {r[0]}:\n{r[2]}" for r in bad)
     print(res[0][2])
+
+
+def _native_worker(rank, P, name, q):
+    try:
+        torch.cuda.set_device(rank)
+        import configurable_hierarchical_allreduce_algorithms_b200 as chb
+
+        # no torch.distributed anywhere in this process
+        comm = chb.Communicator.from_shared_memory(name, rank, P, scratch_bytes=64 << 20, user_bytes=8 << 20)
+        assert (comm.P, comm.rank, comm.backend) == (P, rank, "ipc-native")
+        for n in (5, 4096, (1 << 18) + 1):
+            ins = [_inp(r, n * P) for r in range(P)]
+            exp = torch.stack([x.double() for x in ins]).sum(0)
+            for algo in ("auto", "radix_batch", "ring"):
+                y = chb.all_reduce(comm, ins[rank], algo=algo)
+                torch.testing.assert_close(y.double(), exp, rtol=1e-5, atol=1e-5 * P)
+            y = chb.all_gather(comm, ins[rank][:n].contiguous())
+            assert torch.equal(y, torch.cat([i[:n] for i in ins]))
+        comm.barrier()
+        comm.check()
+        comm.close()
+        q.put((rank, "ok", ""))
+    except Exception:  # noqa: BLE001
+        q.put((rank, "fail", traceback.format_exc()))
+
+
+@pytest.mark.timeout(600)
+def test_communicator_over_the_native_bootstrap():
+    """One rank per GPU, rendezvous through POSIX shared memory: no process group is ever created."""
+    P = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    if P < 2:
+        pytest.skip("needs at least two GPUs")
+    P = min(P, 4)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    name = f"/chb_test_{os.getpid()}"
+    procs = [ctx.Process(target=_native_worker, args=(r, P, name, q)) for r in range(P)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=500) for _ in range(P)]
+    for p in procs:
+        p.join(60)
+    bad = [r for r in res if r[1] != "ok"]
+    assert not bad, "\n".join(f"rank {r[0]}:\n{r[2]}" for r in bad)

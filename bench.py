@@ -341,13 +341,16 @@ def main():
                                   (N - 1) / N, ne_rs * N * esz),
                 }
                 for name, (ours, theirs, factor, total_bytes) in cases.items():
-                    for _ in range(3):
+                    # about 30 ms of back-to-back calls first (the same count on every rank): after the small
+                    # sizes of the sweep the links and clocks need more than three calls to be back at speed
+                    n_warm = min(200, max(3, int(30e-3 / (20e-6 + total_bytes / 2e11))))
+                    for _ in range(n_warm):
                         ours()
                     t = [max_over_ranks(v) for v in per_call_ms(ours, args.sweep_iters, flush, barrier)]
                     p50 = statistics.median(t)
                     row[name] = {"p50_us": p50 * 1e3, "busbw_GBps": total_bytes / (p50 * 1e-3) / 1e9 * factor}
                     if theirs is not None and not args.no_nccl:
-                        for _ in range(3):
+                        for _ in range(n_warm):
                             theirs()
                         t = [max_over_ranks(v) for v in per_call_ms(theirs, args.sweep_iters, flush, barrier)]
                         p50n = statistics.median(t)

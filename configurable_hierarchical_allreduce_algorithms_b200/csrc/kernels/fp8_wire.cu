@@ -17,6 +17,7 @@ namespace chb {
 
 constexpr int kFp8Threads = 512;
 constexpr int kGroup = 128;  // elements per scale
+constexpr int kPeerBatch = 4; // peers whose wire data is loaded together in the pull phase
 
 struct Fp8Io {
   const char* in[kMaxRanks];
@@ -32,6 +33,24 @@ template <> __device__ __forceinline__ void load8<float>(const float* p, float* 
 template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* x) {
   const uint4 v = *reinterpret_cast<const uint4*>(p);
   const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(e[i]); x[2 * i] = f.x; x[2 * i + 1] = f.y; }
+}
+// Eight elements as loaded, before conversion: lets the next iteration's loads be issued early at
+// a quarter (bf16) or the same (fp32) register cost of the converted values.
+template <typename T> struct Raw8;
+template <> struct Raw8<float> { float4 a, b; };
+template <> struct Raw8<__nv_bfloat16> { uint4 v; };
+__device__ __forceinline__ void load_raw(const float* p, Raw8<float>& r) {
+  r.a = reinterpret_cast<const float4*>(p)[0];
+  r.b = reinterpret_cast<const float4*>(p)[1];
+}
+__device__ __forceinline__ void load_raw(const __nv_bfloat16* p, Raw8<__nv_bfloat16>& r) { r.v = *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void unpack(const Raw8<float>& r, float* x) {
+  x[0] = r.a.x; x[1] = r.a.y; x[2] = r.a.z; x[3] = r.a.w; x[4] = r.b.x; x[5] = r.b.y; x[6] = r.b.z; x[7] = r.b.w;
+}
+__device__ __forceinline__ void unpack(const Raw8<__nv_bfloat16>& r, float* x) {
+  const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&r.v);
 #pragma unroll
   for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(e[i]); x[2 * i] = f.x; x[2 * i + 1] = f.y; }
 }
@@ -89,17 +108,30 @@ fp8_rs_kernel(World w, Fp8Io io, long long n, float out_scale) {
     ok = ok && s_entry_ok != 0;
   }
   constexpr int U = 4;   // groups in flight per half-warp
-  // ---- quantise the blocks owed to the peers
-  if (ok)
-    for (long long gw = warp * 2 * U; gw < gpb * P; gw += nwarps * 2 * U) {   // trip count uniform per warp (shuffles below)
+  // ---- quantise the blocks owed to the peers (the loads of the next iteration are issued before the
+  // arithmetic of this one: the phase is bound by bytes in flight, not by instructions)
+  if (ok) {
+    const long long total = gpb * P, stride = nwarps * 2 * U;
+    Raw8<T> cur[U], nxt[U];
+    auto fetch = [&](long long gw, Raw8<T>* r) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long g = gw + hw * U + u;
+        if (g < total && g / gpb != rank) load_raw(in + g * kGroup + sub * 8, r[u]);
+      }
+    };
+    long long gw = warp * 2 * U;
+    if (gw < total) fetch(gw, cur);
+    for (; gw < total; gw += stride) {   // trip count uniform per warp (shuffles below)
+      if (gw + stride < total) fetch(gw + stride, nxt);
       const long long g0 = gw + hw * U;
       float x[U][8];
       bool live[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const long long g = g0 + u;
-        live[u] = g < gpb * P && g / gpb != rank;
-        if (live[u]) load8<T>(in + g * kGroup + sub * 8, x[u]);
+        live[u] = g < total && g / gpb != rank;
+        if (live[u]) unpack(cur[u], x[u]);
         else {
 #pragma unroll
           for (int i = 0; i < 8; ++i) x[u][i] = 0.f;
@@ -129,11 +161,14 @@ fp8_rs_kernel(World w, Fp8Io io, long long n, float out_scale) {
         *reinterpret_cast<uint2*>(wire + g * kGroup + sub * 8) = make_uint2(q[0] | (q[1] << 16), q[2] | (q[3] << 16));
         if (sub == 0) scales[g] = sc;
       }
+#pragma unroll
+      for (int u = 0; u < U; ++u) cur[u] = nxt[u];
     }
+  }
   unsigned gen = 0;
   ok = rank_barrier(c, nct, gen, w.timeout_ns, rank, 0) && ok;
   ok = ok && (P == 1 || cta_barrier(w, c, rank, seq + 1ull));
-  // ---- pull my block from every peer, dequantise, accumulate in rank order
+  // ---- pull my block from every peer, dequantise, accumulate in a fixed order
   if (ok) {
     T* out = reinterpret_cast<T*>(io.out[rank]);
     for (long long gw = warp * 2 * U; gw < gpb; gw += nwarps * 2 * U) {
@@ -143,38 +178,49 @@ fp8_rs_kernel(World w, Fp8Io io, long long n, float out_scale) {
       for (int u = 0; u < U; ++u)
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[u][i] = 0.f;
-      for (int q = 0; q < P; ++q) {
-        if (q == rank) {
+      // my own block never goes through fp8
 #pragma unroll
-          for (int u = 0; u < U; ++u) {
-            if (g0 + u >= gpb) continue;
-            float x[8];
-            load8<T>(in + ((long long)rank * gpb + g0 + u) * kGroup + sub * 8, x);
+      for (int u = 0; u < U; ++u) {
+        if (g0 + u >= gpb) continue;
+        float x[8];
+        load8<T>(in + ((long long)rank * gpb + g0 + u) * kGroup + sub * 8, x);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[u][i] += x[i];
-          }
-        } else {
-          const unsigned char* pw = reinterpret_cast<const unsigned char*>(w.work[q]);
+        for (int i = 0; i < 8; ++i) acc[u][i] += x[i];
+      }
+      // the peers' contributions, kPeerBatch peers at a time so that their loads are in flight together
+      // (order: rank+1, rank+2, ... - fixed, so results repeat bit for bit; it also spreads the peers'
+      // egress instead of every rank starting at rank 0)
+      for (int j0 = 0; j0 < P - 1; j0 += kPeerBatch) {
+        uint2 packed[kPeerBatch][U];
+        float sc[kPeerBatch][U];
+#pragma unroll
+        for (int jj = 0; jj < kPeerBatch; ++jj) {
+          const int j = j0 + jj;
+          const bool pv = j < P - 1;
+          int q = rank + 1 + j;
+          if (q >= P) q -= P;
+          const unsigned char* pw = reinterpret_cast<const unsigned char*>(w.work[pv ? q : rank]);
           const float* ps = reinterpret_cast<const float*>(pw + (long long)P * n);
-          uint2 packed[U];
-          float sc[U];
 #pragma unroll
           for (int u = 0; u < U; ++u) {
             const long long gg = (long long)rank * gpb + g0 + u;
-            const bool lv = g0 + u < gpb;
-            packed[u] = lv ? __ldcg(reinterpret_cast<const uint2*>(pw + gg * kGroup + sub * 8)) : make_uint2(0u, 0u);
-            sc[u] = lv ? __ldcg(ps + gg) : 0.f;
-          }
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const float2 a0 = fp8x2_to_float2((unsigned short)(packed[u].x & 0xffffu));
-            const float2 a1 = fp8x2_to_float2((unsigned short)(packed[u].x >> 16));
-            const float2 a2 = fp8x2_to_float2((unsigned short)(packed[u].y & 0xffffu));
-            const float2 a3 = fp8x2_to_float2((unsigned short)(packed[u].y >> 16));
-            acc[u][0] += a0.x * sc[u]; acc[u][1] += a0.y * sc[u]; acc[u][2] += a1.x * sc[u]; acc[u][3] += a1.y * sc[u];
-            acc[u][4] += a2.x * sc[u]; acc[u][5] += a2.y * sc[u]; acc[u][6] += a3.x * sc[u]; acc[u][7] += a3.y * sc[u];
+            const bool lv = pv && g0 + u < gpb;
+            packed[jj][u] = lv ? __ldcg(reinterpret_cast<const uint2*>(pw + gg * kGroup + sub * 8)) : make_uint2(0u, 0u);
+            sc[jj][u] = lv ? __ldcg(ps + gg) : 0.f;
           }
         }
+#pragma unroll
+        for (int jj = 0; jj < kPeerBatch; ++jj)
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const float2 a0 = fp8x2_to_float2((unsigned short)(packed[jj][u].x & 0xffffu));
+            const float2 a1 = fp8x2_to_float2((unsigned short)(packed[jj][u].x >> 16));
+            const float2 a2 = fp8x2_to_float2((unsigned short)(packed[jj][u].y & 0xffffu));
+            const float2 a3 = fp8x2_to_float2((unsigned short)(packed[jj][u].y >> 16));
+            const float f = sc[jj][u];
+            acc[u][0] += a0.x * f; acc[u][1] += a0.y * f; acc[u][2] += a1.x * f; acc[u][3] += a1.y * f;
+            acc[u][4] += a2.x * f; acc[u][5] += a2.y * f; acc[u][6] += a3.x * f; acc[u][7] += a3.y * f;
+          }
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {

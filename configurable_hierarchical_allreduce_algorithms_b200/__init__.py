@@ -20,7 +20,7 @@ from .parallel.program import Program, ProgramError, list_algorithms, cached_pro
 __all__ = ["Program", "ProgramError", "list_algorithms", "cached_program", "Communicator", "CollectiveError",
            "all_reduce", "reduce_scatter", "all_gather", "all_to_all", "gather",
            "allgather_radix_batch", "reduce_scatter_radix_batch", "all_reduce_radix_batch",
-           "TwoLevel", "DeviceLevel", "LibraryLevel", "GlooLevel", "split_world"]
+           "all_reduce_host", "HostAllReduce", "TwoLevel", "DeviceLevel", "LibraryLevel", "GlooLevel", "split_world"]
 
 _LAZY = {
     "Communicator": ("parallel.comm", "Communicator"),
@@ -33,6 +33,8 @@ _LAZY = {
     "allgather_radix_batch": ("ops.collectives", "allgather_radix_batch"),
     "reduce_scatter_radix_batch": ("ops.collectives", "reduce_scatter_radix_batch"),
     "all_reduce_radix_batch": ("ops.collectives", "all_reduce_radix_batch"),
+    "all_reduce_host": ("ops.host", "all_reduce_host"),
+    "HostAllReduce": ("ops.host", "HostAllReduce"),
     "TwoLevel": ("parallel.hierarchy", "TwoLevel"),
     "DeviceLevel": ("parallel.hierarchy", "DeviceLevel"),
     "LibraryLevel": ("parallel.hierarchy", "LibraryLevel"),

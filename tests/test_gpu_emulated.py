@@ -385,3 +385,23 @@ def test_program_cache_starts_over_when_full(cuda):
             assert torch.equal(outs[0], ins[0] + ins[1]) and torch.equal(outs[1], outs[0])
     comm.check()
     comm.close()
+
+
+def test_host_buffer_allreduce_pipeline(cuda):
+    """Pinned host -> device -> allreduce -> pinned host in chunks on three streams (world of one rank)."""
+    from configurable_hierarchical_allreduce_algorithms_b200.ops.host import HostAllReduce
+
+    comm = Communicator.emulated(1, scratch_bytes=1 << 20, user_bytes=8 << 20)
+    pipe = HostAllReduce(comm, torch.float32, chunk_elems=1 << 16, depth=2)
+    for n in (5, 1 << 16, (7 << 15) + 3):          # less than a chunk, exactly one, several with a ragged tail
+        hx = torch.randn(n).pin_memory()
+        hy = pipe(hx, scale=2.0)
+        torch.cuda.current_stream().synchronize()
+        assert torch.equal(hy, hx * 2.0)
+        hy2 = torch.empty(n).pin_memory()
+        assert chb.all_reduce_host(comm, hx, hy2, chunk_elems=1 << 15, depth=3) is hy2
+        torch.cuda.synchronize()
+        assert torch.equal(hy2, hx)
+    assert pipe.h2d_bytes == pipe.d2h_bytes == 4 * (5 + (1 << 16) + (7 << 15) + 3)
+    comm.check()
+    comm.close()

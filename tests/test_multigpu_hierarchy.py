@@ -96,6 +96,12 @@ def _native_worker(rank, P, name, q):
                 torch.testing.assert_close(y.double(), exp, rtol=1e-5, atol=1e-5 * P)
             y = chb.all_gather(comm, ins[rank][:n].contiguous())
             assert torch.equal(y, torch.cat([i[:n] for i in ins]))
+        # host buffers: chunked upload / allreduce / download pipeline
+        ins = [_inp(r, (5 << 15) + 7) for r in range(P)]
+        exp = torch.stack([x.double() for x in ins]).sum(0)
+        hy = chb.all_reduce_host(comm, ins[rank].cpu().pin_memory(), chunk_elems=1 << 16, depth=2)
+        torch.cuda.synchronize()
+        torch.testing.assert_close(hy.double(), exp.cpu(), rtol=1e-5, atol=1e-5 * P)
         comm.barrier()
         comm.check()
         comm.close()

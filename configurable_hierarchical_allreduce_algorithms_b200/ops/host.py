@@ -17,7 +17,8 @@ from . import collectives as ops
 
 
 class HostAllReduce:
-    """Reusable pipeline for allreduces of pinned host tensors of one dtype.
+    """Reusable pipeline for collectives on pinned host tensors of one dtype (allreduce by call,
+    :meth:`reduce_scatter` and :meth:`all_gather` as methods).
 
     ``chunk_elems`` elements per chunk, ``depth`` chunks in flight (device memory:
     ``2 * depth * chunk`` from the communicator's registered region).  One rank per
@@ -46,31 +47,102 @@ class HostAllReduce:
             hy = torch.empty_like(hx).pin_memory()
         hx1, hy1 = hx.view(-1), hy.view(-1)
         n = hx1.numel()
+
+        def upload(slot, a, e):
+            self.xin[slot][:e - a].copy_(hx1[a:e], non_blocking=True)
+
+        def collective(slot, m):
+            ops.all_reduce(self.comm, self.xin[slot][:m], out=self.yout[slot][:m], op=op, scale=scale, algo=algo, k=k, b=b)
+
+        def download(slot, a, e):
+            hy1[a:e].copy_(self.yout[slot][:e - a], non_blocking=True)
+
+        self._pipeline(n, self.chunk, upload, collective, download)
+        self.h2d_bytes += n * hx.element_size()
+        self.d2h_bytes += n * hx.element_size()
+        return hy
+
+    def _pipeline(self, n, m_max, upload, collective, download):
+        """Chunks [a, e) of at most m_max elements through upload (side stream), collective (current
+        stream) and download (other side stream); a slot is reused only when its previous user is done."""
         main = torch.cuda.current_stream()
-        self.s_in.wait_stream(main)          # earlier work of the caller that produced hx / reads hy
+        self.s_in.wait_stream(main)          # earlier work of the caller that produced the input / reads the output
         self.s_out.wait_stream(main)
-        nchunks = (n + self.chunk - 1) // self.chunk
-        for c in range(nchunks):
-            a, e = c * self.chunk, min(n, (c + 1) * self.chunk)
-            m, slot = e - a, c % self.depth
+        for c in range((n + m_max - 1) // m_max):
+            a, e = c * m_max, min(n, (c + 1) * m_max)
+            slot = c % self.depth
             if c >= self.depth:
                 self.s_in.wait_event(self.done[slot])      # the collective has consumed this input slot
             with torch.cuda.stream(self.s_in):
-                self.xin[slot][:m].copy_(hx1[a:e], non_blocking=True)
+                upload(slot, a, e)
                 self.h2d[slot].record(self.s_in)
             main.wait_event(self.h2d[slot])
             if c >= self.depth:
                 main.wait_event(self.d2h[slot])            # the download has drained this output slot
-            ops.all_reduce(self.comm, self.xin[slot][:m], out=self.yout[slot][:m], op=op, scale=scale, algo=algo, k=k, b=b)
+            collective(slot, e - a)
             self.done[slot].record(main)
             self.s_out.wait_event(self.done[slot])
             with torch.cuda.stream(self.s_out):
-                hy1[a:e].copy_(self.yout[slot][:m], non_blocking=True)
+                download(slot, a, e)
                 self.d2h[slot].record(self.s_out)
         main.wait_stream(self.s_out)
         main.wait_stream(self.s_in)
-        self.h2d_bytes += n * hx.element_size()
+
+    # ---- the other two collectives: block structure kept by 2-D copies
+    def reduce_scatter(self, hx: torch.Tensor, hy: torch.Tensor | None = None, op: str = "sum", scale: float = 1.0,
+                       algo: str = "auto", k: int = 2, b: int = 1) -> torch.Tensor:
+        """hx: P blocks of n elements (pinned host); hy: this rank's reduced block of n elements."""
+        P = self.comm.P
+        n = hx.numel() // P
+        if hx.numel() != n * P or n == 0:
+            raise ValueError("reduce-scatter input must hold one non-empty block per rank")
+        if hy is None:
+            hy = torch.empty(n, dtype=hx.dtype).pin_memory()
+        hx2, hy1 = hx.view(P, n), hy.view(-1)
+        m_max = self.chunk // P
+        if m_max < 1:
+            raise ValueError("chunk smaller than one element per rank")
+
+        def upload(slot, a, e):
+            self.xin[slot][:P * (e - a)].view(P, e - a).copy_(hx2[:, a:e], non_blocking=True)
+
+        def collective(slot, m):
+            ops.reduce_scatter(self.comm, self.xin[slot][:P * m], out=self.yout[slot][:m], op=op, scale=scale, algo=algo, k=k, b=b)
+
+        def download(slot, a, e):
+            hy1[a:e].copy_(self.yout[slot][:e - a], non_blocking=True)
+
+        self._pipeline(n, m_max, upload, collective, download)
+        self.h2d_bytes += hx.numel() * hx.element_size()
         self.d2h_bytes += n * hx.element_size()
+        return hy
+
+    def all_gather(self, hx: torch.Tensor, hy: torch.Tensor | None = None, algo: str = "auto", k: int = 2,
+                   b: int = 1) -> torch.Tensor:
+        """hx: this rank's n elements (pinned host); hy: the P blocks in rank order."""
+        P = self.comm.P
+        n = hx.numel()
+        if n == 0:
+            raise ValueError("allgather input must not be empty")
+        if hy is None:
+            hy = torch.empty(n * P, dtype=hx.dtype).pin_memory()
+        hx1, hy2 = hx.view(-1), hy.view(P, n)
+        m_max = self.chunk // P
+        if m_max < 1:
+            raise ValueError("chunk smaller than one element per rank")
+
+        def upload(slot, a, e):
+            self.xin[slot][:e - a].copy_(hx1[a:e], non_blocking=True)
+
+        def collective(slot, m):
+            ops.all_gather(self.comm, self.xin[slot][:m], out=self.yout[slot][:P * m], algo=algo, k=k, b=b)
+
+        def download(slot, a, e):
+            hy2[:, a:e].copy_(self.yout[slot][:P * (e - a)].view(P, e - a), non_blocking=True)
+
+        self._pipeline(n, m_max, upload, collective, download)
+        self.h2d_bytes += n * hx.element_size()
+        self.d2h_bytes += n * P * hx.element_size()
         return hy
 
 

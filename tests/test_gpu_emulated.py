@@ -403,5 +403,9 @@ def test_host_buffer_allreduce_pipeline(cuda):
         torch.cuda.synchronize()
         assert torch.equal(hy2, hx)
     assert pipe.h2d_bytes == pipe.d2h_bytes == 4 * (5 + (1 << 16) + (7 << 15) + 3)
+    hx = torch.randn((5 << 15) + 1).pin_memory()
+    a, g = pipe.reduce_scatter(hx), pipe.all_gather(hx)
+    torch.cuda.synchronize()
+    assert torch.equal(a, hx) and torch.equal(g, hx)       # one rank: both are the identity
     comm.check()
     comm.close()

@@ -102,6 +102,16 @@ def _native_worker(rank, P, name, q):
         hy = chb.all_reduce_host(comm, ins[rank].cpu().pin_memory(), chunk_elems=1 << 16, depth=2)
         torch.cuda.synchronize()
         torch.testing.assert_close(hy.double(), exp.cpu(), rtol=1e-5, atol=1e-5 * P)
+        from configurable_hierarchical_allreduce_algorithms_b200.ops.host import HostAllReduce
+        pipe = HostAllReduce(comm, torch.float32, chunk_elems=1 << 14, depth=2)
+        n = (3 << 13) + 5                                   # several chunks with a ragged tail
+        ins = [_inp(r, n * P) for r in range(P)]
+        exp = torch.stack([x.double() for x in ins]).sum(0)
+        part = pipe.reduce_scatter(ins[rank].cpu().pin_memory())
+        full = pipe.all_gather(ins[rank][:n].cpu().pin_memory())
+        torch.cuda.synchronize()
+        torch.testing.assert_close(part.double(), exp[rank * n:(rank + 1) * n].cpu(), rtol=1e-5, atol=1e-5 * P)
+        assert torch.equal(full, torch.cat([i[:n] for i in ins]).cpu())
         comm.barrier()
         comm.check()
         comm.close()

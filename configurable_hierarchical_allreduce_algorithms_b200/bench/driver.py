@@ -4,6 +4,7 @@
         <n_iter> [--overwrite] [b=<group>] [base=<elements>] [num_nodes=<n>] [radix_increment=<step>]
         [coll=allreduce|reduce_scatter|allgather] [dtype=int32|fp32|bf16|fp64] [op=sum|max|min]
         [algos=radix_batch,ring,...] [reps=50] [backend=gpu|gloo] [out=<file.csv>] [symmetric=1]
+        [local_size=<ranks per box>] [inter_algo=ring|library|...]
 
 Like the reference's drivers (testing/custom_implementations/work_dir/all_reduce/main.cpp:111-199,
 .../all_gather/main.cpp:109-201, .../reduce_scatter/main.cpp:169-264, testing/main.cpp:146-220):
@@ -16,7 +17,10 @@ is given, and rows are flushed one by one, so an interrupted sweep resumes where
 Correctness is AND-reduced and time MAX-reduced over ranks, as in the reference's reduce-scatter
 driver (main.cpp:79-83).  ``symmetric=1`` places input and output in the peer-visible heap (registered
 buffers: nothing is staged, and the kernel-level algorithms ``ll``, ``ll2``, ``nvls``, ``bulk`` can be
-named in ``algos``).  Time is device time (CUDA events) on GPUs and wall time under gloo.
+named in ``algos``).  ``local_size=L`` (implied when torchrun reports fewer local than global ranks, i.e.
+several machines) runs every collective on two physical levels: the swept algorithm inside each box of
+``L`` ranks, ``inter_algo`` along the lanes across boxes (``library`` = NCCL / gloo's own collective,
+anything else a step program over host copies).  Time is device time (CUDA events) on GPUs and wall time under gloo.
 """
 from __future__ import annotations
 
@@ -45,7 +49,7 @@ def parse(argv):
         raise SystemExit(__doc__)
     o = {"n_iter": int(argv[0]), "overwrite": False, "b": 0, "base": 1, "num_nodes": 1, "radix_increment": 1,
          "coll": "allreduce", "dtype": "int32", "op": "sum", "algos": "", "reps": 50, "backend": "", "out": "",
-         "symmetric": 0}
+         "symmetric": 0, "local_size": 0, "inter_algo": "ring"}
     for a in argv[1:]:
         if a == "--overwrite":
             o["overwrite"] = True
@@ -86,10 +90,24 @@ def main(argv=None):
     esz = torch.empty((), dtype=dtype).element_size()
     max_n = o["base"] << max(0, o["n_iter"] - 1)
     comm = None
+    from ..parallel import hierarchy as H
+    L = o["local_size"] or int(os.environ.get("LOCAL_WORLD_SIZE", P))
+    if L >= P or L < 1 or P % L:
+        L = 0                                               # one box: a single level
+    intra_group = inter_group = inter_prog_group = None
+    if L:
+        intra_group, inter_group = H.split_world(L)
+        inter_prog_group = inter_group
+        if backend == "gpu" and o["inter_algo"] != "library":
+            _, inter_prog_group = H.split_world(L, backend="gloo")   # step programs on host copies need a CPU group
+        if not o["b"] or L % b:
+            b = L                                           # the group size of the swept algorithm lives inside a box
+        o["symmetric"] = 0                                  # the levels exchange intermediate tensors of their own
+    PL = L or P                                             # ranks of the level the swept algorithm runs on
     if backend == "gpu":
         from ..parallel.comm import Communicator
         total = max_n * P * esz
-        comm = Communicator.from_process_group(scratch_bytes=4 * total + (32 << 20),
+        comm = Communicator.from_process_group(group=intra_group, scratch_bytes=4 * total + (32 << 20),
                                                user_bytes=(64 << 20) + (2 * total + 4096 if o["symmetric"] else 0))
     sym_in = sym_out = None
     if comm is not None and o["symmetric"]:
@@ -98,7 +116,17 @@ def main(argv=None):
         sym_out = comm.empty(max_n * (1 if coll == "reduce_scatter" else P), dtype)
     from .. import all_gather, all_reduce, reduce_scatter
     from ..parallel.comm import CollectiveError
+    from ..parallel.program import ProgramError
     from ..parallel import gloo_exec
+
+    def two_level(algo, k, gb):
+        """The swept algorithm inside a box, inter_algo along the lanes."""
+        intra = H.DeviceLevel(comm, algo, k, gb) if backend == "gpu" else H.GlooLevel(intra_group, algo, k, gb)
+        if o["inter_algo"] == "library":
+            inter = H.LibraryLevel(inter_group)
+        else:
+            inter = H.GlooLevel(inter_prog_group, o["inter_algo"], 2, 1)
+        return H.TwoLevel(intra, inter)
 
     path = o["out"] or f"results{P}_{o['num_nodes']}_{b}.csv"
     csv = None
@@ -108,7 +136,7 @@ def main(argv=None):
         if fresh:
             csv.write(HEADER + "\n")
     redop = {"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN}[op]
-    algos = [a for a in o["algos"].split(",") if a] or (["radix_batch"] + BASELINES[coll])
+    algos = [a for a in o["algos"].split(",") if a] or (["radix_batch", "ring"] if L else ["radix_batch"] + BASELINES[coll])
 
     def run_one(name, algo, k, bb, n, x, ref):
         """`reps` timed, checked repetitions of one configuration."""
@@ -126,13 +154,17 @@ def main(argv=None):
                 try:
                     if algo == "vendor":
                         y = vendor(x)
+                    elif L:
+                        lvl = two_level(algo, kk, gb)
+                        y = lvl.all_reduce(x, op) if coll == "allreduce" else (
+                            lvl.reduce_scatter(x, op) if coll == "reduce_scatter" else lvl.all_gather(x))
                     elif coll == "allreduce":
                         y = all_reduce(comm, x, out=out, op=op, algo=algo, k=kk, b=gb)
                     elif coll == "reduce_scatter":
                         y = reduce_scatter(comm, x, out=out, op=op, algo=algo, k=kk, b=gb)
                     else:
                         y = all_gather(comm, x, out=out, algo=algo, k=kk, b=gb)
-                except CollectiveError as e:
+                except (CollectiveError, ProgramError) as e:
                     # a capability this communicator lacks (no multicast alias, message too large for the
                     # flagged-line inbox ...): the same on every rank, so all of them skip the configuration
                     if rank == 0:
@@ -144,11 +176,20 @@ def main(argv=None):
             else:
                 dist.barrier()
                 t0 = time.perf_counter()
-                if algo == "vendor":
-                    y = vendor(x)
-                else:
-                    count = n * P if coll == "allreduce" else n
-                    y = gloo_exec.run_collective(coll, algo, x, count, kk, gb, op=op)
+                try:
+                    if algo == "vendor":
+                        y = vendor(x)
+                    elif L:
+                        lvl = two_level(algo, kk, gb)
+                        y = lvl.all_reduce(x, op) if coll == "allreduce" else (
+                            lvl.reduce_scatter(x, op) if coll == "reduce_scatter" else lvl.all_gather(x))
+                    else:
+                        count = n * P if coll == "allreduce" else n
+                        y = gloo_exec.run_collective(coll, algo, x, count, kk, gb, op=op)
+                except ProgramError as e:     # e.g. an allreduce-only algorithm asked to serve as a level's reduce-scatter
+                    if rank == 0:
+                        print(f"skipped {name} k={k} b={bb} count={n}: {e}", file=sys.stderr, flush=True)
+                    return
                 dist.barrier()
                 t = time.perf_counter() - t0
             ok = torch.equal(y, ref) if not dtype.is_floating_point else bool(
@@ -194,7 +235,7 @@ def main(argv=None):
         for algo in algos:
             name = f"{coll}_{algo}" if algo != "radix_batch" else {"allreduce": "all_reduce_radix_batch", "reduce_scatter": "reduce_scatter_radix_batch", "allgather": "allgather_radix_batch"}[coll]
             if algo in K_ALGOS:
-                hi = max(3, b) if algo == "radix_batch" else max(3, P)
+                hi = max(3, b) if algo == "radix_batch" else max(3, PL)
                 for k in range(2, hi, max(1, o["radix_increment"])):
                     run_one(name, algo, k, b if algo in ("radix_batch", "semi_radix_batch", "custom", "radix_block") else 0, n, x, ref)
             else:

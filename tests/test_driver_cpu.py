@@ -53,3 +53,30 @@ def test_driver_writes_reference_schema_and_appends(tmp_path):
     bad.to_csv(badp, index=False)
     with pytest.raises(SystemExit):
         plots.median_best(str(badp), outdir=str(tmp_path))
+
+
+@pytest.mark.timeout(900)
+def test_driver_two_levels_and_launcher(tmp_path):
+    """4 gloo ranks as 2 boxes of 2: the swept algorithm inside a box, a ring program along the lanes;
+    and the launcher's command lines for the three environments."""
+    out = tmp_path / "two.csv"
+    for coll in ("allreduce", "reduce_scatter", "allgather"):
+        _run(["2", "base=8", "reps=2", "backend=gloo", f"out={out}", "local_size=2", "inter_algo=ring", f"coll={coll}",
+              "algos=radix_batch,ring,reduce_scatter_allgather"], tmp_path)
+    df = pd.read_csv(out)
+    assert (df.is_correct == 1).all() and (df.nprocs == 4).all() and (df.b[df.algorithm_name.str.contains("radix_batch")] == 2).all()
+    assert {"all_reduce_radix_batch", "allreduce_ring", "reduce_scatter_ring", "allgather_radix_batch"} <= set(df.algorithm_name)
+    assert "allreduce_reduce_scatter_allgather" not in set(df.algorithm_name)      # cannot serve as a level's reduce-scatter: skipped
+    _run(["1", "base=8", "reps=1", "backend=gloo", f"out={out}", "local_size=2", "inter_algo=library"], tmp_path)
+    assert (pd.read_csv(out).is_correct == 1).all()
+
+    from configurable_hierarchical_allreduce_algorithms_b200.bench import launch
+    cmd = launch.build_command("LOCAL", 2, 2, 0, "127.0.0.1:29577", ["3", "b=2"])
+    assert "--nproc-per-node=4" in cmd and "backend=gloo" in cmd and "num_nodes=2" in cmd and "b=2" in cmd
+    cmd = launch.build_command("MULTINODE", 8, 2, 1, "node0:29500", ["3", "backend=gpu"])
+    assert "--nnodes=2" in cmd and "--node-rank=1" in cmd and cmd.count("backend=gpu") == 1 and "node0" in cmd
+    cmd = launch.build_command("B200", 8, 1, 0, "127.0.0.1:29500", ["3"])
+    assert "--nproc-per-node=8" in cmd and "backend=gpu" in cmd
+    with pytest.raises(SystemExit):
+        launch.build_command("MOON", 1, 1, 0, "127.0.0.1:1", [])
+    assert launch.main(["--env", "LOCAL", "--ranks-per-node", "2", "--dry-run", "--", "2", "b=2"]) == 0

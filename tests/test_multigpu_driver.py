@@ -44,3 +44,21 @@ def test_driver_on_symmetric_buffers(tmp_path, coll, algos):
     for a in algos.split(","):
         if a != "nvls":      # needs a multicast alias, skipped by the driver where there is none
             assert any(a in x for x in names), (a, names)
+
+
+@pytest.mark.timeout(600)
+def test_driver_two_levels_on_gpus(tmp_path):
+    """Boxes of L GPUs (L = 1 with two GPUs, 2 with four): kernels inside a box, NCCL or a ring program along the lanes."""
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    n = 2 if n < 4 else 4
+    out = tmp_path / "two.csv"
+    for inter in ("library", "ring"):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(n), "--master-addr",
+               "127.0.0.1", "--master-port", str(_free_port()), "-m", MOD, "2", "base=4096", "dtype=fp32", "coll=allreduce",
+               "algos=radix_batch,ring", "reps=2", f"local_size={n // 2}", f"inter_algo={inter}", f"out={out}"]
+        r = subprocess.run(cmd, cwd=tmp_path, env=dict(os.environ, PYTHONPATH=str(ROOT)), capture_output=True, text=True, timeout=500)
+        assert r.returncode == 0, r.stderr[-3000:]
+    df = pd.read_csv(out)
+    assert (df.is_correct == 1).all() and (df.nprocs == n).all() and len(df) >= 16

@@ -33,7 +33,7 @@ typedef int CHB_Datatype; /* CHB_F32 ... */
 typedef int CHB_Op;       /* CHB_SUM ... */
 #define CHB_IN_PLACE ((void*)-1)
 
-enum { CHB_ALLREDUCE = 0, CHB_REDUCE_SCATTER = 1, CHB_ALLGATHER = 2, CHB_ALLTOALL = 3, CHB_GATHER = 4 };
+enum { CHB_ALLREDUCE = 0, CHB_REDUCE_SCATTER = 1, CHB_ALLGATHER = 2, CHB_ALLTOALL = 3, CHB_GATHER = 4, CHB_PHASE = 5 };
 
 void chb_set_stream(cudaStream_t s);
 
@@ -53,6 +53,23 @@ int all_reduce_semi_radix_batch(char* sendbuf, char* recvbuf, int count, CHB_Dat
 int reduce_scatter_radix_block(char* sendbuf, char* recvbuf, int count, CHB_Datatype datatype, CHB_Op op, CHB_Comm comm, int r, int b);
 int allgather_k_brucks(char* sendbuf, int sendcount, CHB_Datatype datatype, char* recvbuf, CHB_Comm comm, int k);
 int gather_k_nomial(char* sendbuf, int sendcount, CHB_Datatype datatype, char* recvbuf, CHB_Comm comm, int k, int root);
+
+/* the phases of the hierarchical collectives as calls of their own, with the reference's buffer layouts
+ * (c = count argument, T = ceil((P/b) / b) stages; see csrc/sched/gen_chiara.cc "stand-alone phases"):
+ *   intra_gather_k_nomial             send c        recv b*c     at the group root (slot group % b)
+ *   inter_allgather_linear            send b*c      recv T*b*c
+ *   intra_allgather_k_brucks          send T*c      recv (P/b)*c
+ *   intra_reduce_scatter_radix_batch  send P*c      recv T*b*c
+ *   inter_reduce_linear               send T*b*c    recv b*c     at the lane roots
+ *   intra_scatter_radix_batch         send b*c      recv c */
+int intra_gather_k_nomial(char* sendbuf, int count, CHB_Datatype datatype, char* recvbuf, CHB_Comm comm, int k, int b);
+int intra_allgather_k_brucks(char* sendbuf, int count, CHB_Datatype datatype, char* recvbuf, CHB_Comm comm, int k, int b);
+int inter_allgather_linear(char* sendbuf, int sendcount, CHB_Datatype datatype, char* recvbuf, CHB_Comm comm, int b);
+int intra_reduce_scatter_radix_batch(const void* sendbuf, void* recvbuf, int64_t recvcount, CHB_Datatype datatype, CHB_Op op,
+                                     CHB_Comm comm, int k, int b);
+int inter_reduce_linear(const void* sendbuf, void* recvbuf, int64_t recvcount, CHB_Datatype datatype, CHB_Op op,
+                        CHB_Comm comm, int b);
+int intra_scatter_radix_batch(char* sendbuf, int recvcount, CHB_Datatype datatype, char* recvbuf, CHB_Comm comm, int k, int b);
 
 /* MPICH-style baselines */
 int MPICH_Allreduce_recursive_doubling(const char* sendbuf, char* recvbuf, int count, CHB_Datatype datatype, CHB_Op op, CHB_Comm comm);

@@ -53,6 +53,7 @@ const char* coll_name(int coll) {
     case CHB_ALLGATHER: return "allgather";
     case CHB_ALLTOALL: return "alltoall";
     case CHB_GATHER: return "gather";
+    case CHB_PHASE: return "phase";
   }
   return "";
 }
@@ -198,6 +199,29 @@ int allgather_k_brucks(char* sendbuf, int sendcount, CHB_Datatype datatype, char
 }
 int gather_k_nomial(char* sendbuf, int sendcount, CHB_Datatype datatype, char* recvbuf, CHB_Comm comm, int k, int root) {
   return one(comm, CHB_GATHER, "k_nomial", sendbuf, recvbuf, sendcount, datatype, CHB_SUM, k, 1, root);
+}
+
+// stand-alone phases (reference: all_gather_0_3_beta.cpp:36,141,377; intra_reduce_scatter_radix.cpp:208;
+// inter_linear_reduce.cpp:11; intra_scatter_radix_batch.cpp:11)
+int intra_gather_k_nomial(char* sendbuf, int count, CHB_Datatype datatype, char* recvbuf, CHB_Comm comm, int k, int b) {
+  return one(comm, CHB_PHASE, "intra_gather_k_nomial", sendbuf, recvbuf, count, datatype, CHB_SUM, k, b, 0);
+}
+int intra_allgather_k_brucks(char* sendbuf, int count, CHB_Datatype datatype, char* recvbuf, CHB_Comm comm, int k, int b) {
+  return one(comm, CHB_PHASE, "intra_allgather_k_brucks", sendbuf, recvbuf, count, datatype, CHB_SUM, k, b, 0);
+}
+int inter_allgather_linear(char* sendbuf, int sendcount, CHB_Datatype datatype, char* recvbuf, CHB_Comm comm, int b) {
+  return one(comm, CHB_PHASE, "inter_allgather_linear", sendbuf, recvbuf, sendcount, datatype, CHB_SUM, 2, b, 0);
+}
+int intra_reduce_scatter_radix_batch(const void* sendbuf, void* recvbuf, int64_t recvcount, CHB_Datatype datatype, CHB_Op op,
+                                     CHB_Comm comm, int k, int b) {
+  return one(comm, CHB_PHASE, "intra_reduce_scatter_radix_batch", sendbuf, recvbuf, recvcount, datatype, op, k, b, 0);
+}
+int inter_reduce_linear(const void* sendbuf, void* recvbuf, int64_t recvcount, CHB_Datatype datatype, CHB_Op op,
+                        CHB_Comm comm, int b) {
+  return one(comm, CHB_PHASE, "inter_reduce_linear", sendbuf, recvbuf, recvcount, datatype, op, 2, b, 0);
+}
+int intra_scatter_radix_batch(char* sendbuf, int recvcount, CHB_Datatype datatype, char* recvbuf, CHB_Comm comm, int k, int b) {
+  return one(comm, CHB_PHASE, "intra_scatter_radix_batch", sendbuf, recvbuf, recvcount, datatype, CHB_SUM, k, b, 0);
 }
 
 #define CHB_AR0(NAME, ALGO)                                                                                   \

@@ -10,6 +10,7 @@ Builder gen_ag_radix_batch(int P, int64_t n, int k, int b);
 Builder gen_rs_radix_batch(int P, int64_t n, int k, int b);
 Builder gen_ar_radix_batch(int P, int64_t N, int k, int b);
 void emit_ag_radix_batch(Builder& B, int P, int64_t n, int k, int b, int IB, int64_t IO);
+Builder gen_phase(const std::string& name, int P, int64_t c, int k, int b);
 // gen_baselines.cc
 Builder gen_ar_recursive_doubling(int P, int64_t N);
 Builder gen_ar_ring(int P, int64_t N);
@@ -85,6 +86,9 @@ std::vector<std::string> list_algorithms(const std::string& coll) {
     return {"radix_batch", "k_brucks", "ring", "recursive_doubling", "linear"};
   if (coll == "alltoall") return {"tuna", "linear"};
   if (coll == "gather") return {"k_nomial"};
+  if (coll == "phase")
+    return {"intra_gather_k_nomial", "inter_allgather_linear", "intra_allgather_k_brucks",
+            "intra_reduce_scatter_radix_batch", "inter_reduce_linear", "intra_scatter_radix_batch"};
   return {};
 }
 
@@ -126,6 +130,8 @@ Builder build_algorithm(const AlgoSpec& s) {
     if (a == "linear") return gen_a2a_linear(s.P, s.count);
   } else if (c == "gather") {
     if (a == "k_nomial") return gen_gather_knomial(s.P, s.count, s.k, s.aux);
+  } else if (c == "phase") {
+    return gen_phase(a, s.P, s.count, s.k, s.b);
   }
   // phases as stand-alone collectives on sub-communicators: "intra_<flat algorithm>" runs it inside
   // every group of b consecutive ranks, "inter_<flat algorithm>" along every lane of stride b

@@ -273,6 +273,44 @@ void rs_lane_reduce(Builder& B, const Geo& g, const RsIntra& ri, int dst_buf, bo
   }
 }
 
+// ---- k-nomial scatter inside every group from the rotating root (slot grp % b), whose b blocks sit
+// in `src_buf` in slot order: every rank ends with its own block in OUT; SC (b*n per rank,
+// normalised order) carries the runs that a subtree root hands on.  Children pull their run.
+void rs_knomial_scatter(Builder& B, const Geo& g, int src_buf, int SC) {
+  const int64_t n = g.n;
+  for (int grp = 0; grp < g.G; ++grp) {
+    int root_local = grp % g.b;
+    int root = g.rank_of(grp, root_local);
+    B.copy(root, L_OUT, 0, root, src_buf, (int64_t)root_local * n, n);
+    for (int p = g.L - 1; p >= 0; --p) {
+      int64_t delta = ipow(g.k, p), gsz = delta * g.k;
+      for (int64_t x = 0; x < g.b; x += gsz) {
+        int64_t block_end = std::min<int64_t>(x + gsz, g.b);
+        int parent = g.rank_of(grp, (int)((x + root_local) % g.b));
+        for (int j = 1; j < g.k; ++j) {
+          int64_t c = x + j * delta;
+          if (c >= block_end) break;
+          int64_t len = std::min<int64_t>(delta, block_end - c);
+          int child = g.rank_of(grp, (int)((c + root_local) % g.b));
+          if (x == 0) {
+            // parent is the root: blocks live in src_buf in slot order
+            int slot = (int)((c + root_local) % g.b);
+            B.copy(child, L_OUT, 0, root, src_buf, (int64_t)slot * n, n);
+            if (len > 1)
+              cyclic_runs((int)((c + 1 + root_local) % g.b), (int)len - 1, g.b, g.b, [&](int s0, int run) {
+                int64_t xpos = ((s0 - root_local + g.b) % g.b);
+                B.copy(child, SC, xpos * n, root, src_buf, (int64_t)s0 * n, (int64_t)run * n);
+              });
+          } else {
+            B.copy(child, L_OUT, 0, parent, SC, c * n, n);
+            if (len > 1) B.copy(child, SC, (c + 1) * n, parent, SC, (c + 1) * n, (len - 1) * n);
+          }
+        }
+      }
+    }
+  }
+}
+
 }  // namespace
 
 // =============================== allgather ======================================
@@ -321,37 +359,7 @@ Builder gen_rs_radix_batch(int P, int64_t n, int k, int b) {
   RsIntra ri = rs_intra(B, g, ACC, chunk);
   rs_lane_reduce(B, g, ri, RED, false, chunk, OPF_FINAL);
   // phase 3: k-nomial scatter from the rotating root, children pull their run
-  for (int grp = 0; grp < g.G; ++grp) {
-    int root_local = grp % g.b;
-    int root = g.rank_of(grp, root_local);
-    B.copy(root, L_OUT, 0, root, RED, (int64_t)root_local * n, n);
-    for (int p = g.L - 1; p >= 0; --p) {
-      int64_t delta = ipow(g.k, p), gsz = delta * g.k;
-      for (int64_t x = 0; x < g.b; x += gsz) {
-        int64_t block_end = std::min<int64_t>(x + gsz, g.b);
-        int parent = g.rank_of(grp, (int)((x + root_local) % g.b));
-        for (int j = 1; j < g.k; ++j) {
-          int64_t c = x + j * delta;
-          if (c >= block_end) break;
-          int64_t len = std::min<int64_t>(delta, block_end - c);
-          int child = g.rank_of(grp, (int)((c + root_local) % g.b));
-          if (x == 0) {
-            // parent is the root: blocks live in RED in slot order
-            int slot = (int)((c + root_local) % g.b);
-            B.copy(child, L_OUT, 0, root, RED, (int64_t)slot * n, n);
-            if (len > 1)
-              cyclic_runs((int)((c + 1 + root_local) % g.b), (int)len - 1, g.b, g.b, [&](int s0, int run) {
-                int64_t xpos = ((s0 - root_local + g.b) % g.b);
-                B.copy(child, SC, xpos * n, root, RED, (int64_t)s0 * n, (int64_t)run * n);
-              });
-          } else {
-            B.copy(child, L_OUT, 0, parent, SC, c * n, n);
-            if (len > 1) B.copy(child, SC, (c + 1) * n, parent, SC, (c + 1) * n, (len - 1) * n);
-          }
-        }
-      }
-    }
-  }
+  rs_knomial_scatter(B, g, RED, SC);
   return B;
 }
 
@@ -381,6 +389,105 @@ Builder gen_ar_radix_batch(int P, int64_t N, int k, int b) {
   // intra-group k-ary Bruck per stage
   ag_kbruck_stages(B, g, chunk);
   return B;
+}
+
+// =============================== stand-alone phases ==============================
+// The reference keeps the phases of its hierarchical collectives as functions of their own, with
+// their own buffer layouts, to test them one at a time:
+//   testing/custom_implementations/work_dir/all_gather/outdated_versions/all_gather_0_3_beta.cpp:36 (intra_gather_k_nomial),
+//   :141 (intra_allgather_k_brucks), :377 (inter_allgather_linear);
+//   testing/custom_implementations/work_dir/reduce_scatter/intra_reduce_scatter_radix.cpp:208-541,
+//   .../inter_linear_reduce.cpp:11-73, .../intra_scatter_radix_batch.cpp:11-110.
+// Here each is a program with the same inputs and outputs (c = elements per block or chunk):
+//   intra_gather_k_nomial            in c            out b*c        group root: the group's blocks in slot order
+//   inter_allgather_linear           in b*c          out T*b*c      entry s: the chunk of group s*b + lane, from its lane root
+//   intra_allgather_k_brucks         in T*c          out G*c        stage s: block s of every slot, in slot order
+//   intra_reduce_scatter_radix_batch in P*c          out T*b*c      entry s: chunk of group s*b + slot summed over my group
+//   inter_reduce_linear              in T*b*c        out b*c        lane root of group d: entry d/b summed over the lane
+//   intra_scatter_radix_batch        in b*c          out c          block `slot` of the group root's input
+// with T = ceil(G / b) stages; entries without a source (the last stage when G % b != 0) stay untouched.
+Builder gen_phase(const std::string& name, int P, int64_t c, int k, int b) {
+  Geo g(P, b, k, c);
+  const int T = g.nstages();
+  const int64_t chunk = (int64_t)g.b * c;
+  if (name == "intra_gather_k_nomial") {
+    Builder B(P, c, chunk, name);
+    if (g.b == 1) {
+      for (int r = 0; r < P; ++r) B.copy(r, L_OUT, 0, r, L_IN, 0, c);
+      return B;
+    }
+    int KG = B.tmp(chunk);
+    ag_knomial_gather(B, g, KG, L_IN, 0);
+    for (int grp = 0; grp < g.G; ++grp) {   // the root un-rotates once (own block from its input)
+      int root_local = grp % g.b, root = g.rank_of(grp, root_local);
+      B.copy(root, L_OUT, (int64_t)root_local * c, root, L_IN, 0, c);
+      int64_t run1 = g.b - root_local - 1;
+      if (run1 > 0) B.copy(root, L_OUT, (int64_t)(root_local + 1) * c, root, KG, c, run1 * c);
+      if (root_local > 0) B.copy(root, L_OUT, 0, root, KG, (int64_t)(g.b - root_local) * c, (int64_t)root_local * c);
+    }
+    return B;
+  }
+  if (name == "inter_allgather_linear") {
+    Builder B(P, chunk, (int64_t)T * chunk, name);
+    for (int d = 0; d < g.G; ++d) {
+      int lane = d % g.b, root = g.rank_of(d, lane);
+      for (int q = 0; q < g.G; ++q) B.copy(g.rank_of(q, lane), L_OUT, (int64_t)(d / g.b) * chunk, root, L_IN, 0, chunk);
+    }
+    return B;
+  }
+  if (name == "intra_allgather_k_brucks") {
+    Builder B(P, (int64_t)T * c, (int64_t)g.G * c, name);
+    Geo gc(P, b, k, c);
+    for (int grp = 0; grp < g.G; ++grp)
+      for (int s = 0; s < T; ++s)
+        for (int slot = 0; slot < g.stage_width(s); ++slot) {
+          int me = g.rank_of(grp, slot);
+          B.copy(me, L_OUT, ((int64_t)s * g.b + slot) * c, me, L_IN, (int64_t)s * c, c);
+        }
+    ag_kbruck_stages(B, gc, c);
+    return B;
+  }
+  if (name == "intra_reduce_scatter_radix_batch") {
+    Builder B(P, (int64_t)P * c, (int64_t)T * chunk, name);
+    if (g.b == 1) {
+      for (int r = 0; r < P; ++r) B.copy(r, L_OUT, 0, r, L_IN, 0, (int64_t)P * c);
+      return B;
+    }
+    int ACC = B.tmp((int64_t)P * c);
+    RsIntra ri = rs_intra(B, g, ACC, chunk);
+    for (int grp = 0; grp < g.G; ++grp)
+      for (int slot = 0; slot < g.b; ++slot) {
+        int h = ri.holder[slot];
+        for (int s = 0; s < T; ++s) {
+          int d = s * g.b + slot;
+          if (d >= g.G) continue;
+          B.copy(g.rank_of(grp, slot), L_OUT, (int64_t)s * chunk, g.rank_of(grp, h), ri.cur_buf[h], (int64_t)d * chunk, chunk);
+        }
+      }
+    return B;
+  }
+  if (name == "inter_reduce_linear") {
+    Builder B(P, (int64_t)T * chunk, chunk, name);
+    for (int d = 0; d < g.G; ++d) {
+      int lane = d % g.b, root = g.rank_of(d, lane);
+      std::vector<Src> srcs{Src{root, L_IN, (int64_t)(d / g.b) * chunk}};     // own contribution first, like the reference
+      for (int q = 0; q < g.G; ++q)
+        if (q != d) srcs.push_back(Src{g.rank_of(q, lane), L_IN, (int64_t)(d / g.b) * chunk});
+      B.reduce(root, L_OUT, 0, srcs, chunk, false, OPF_FINAL);
+    }
+    return B;
+  }
+  if (name == "intra_scatter_radix_batch") {
+    Builder B(P, chunk, c, name);
+    if (g.b == 1) {
+      for (int r = 0; r < P; ++r) B.copy(r, L_OUT, 0, r, L_IN, 0, c);
+      return B;
+    }
+    int SC = B.tmp(chunk);
+    rs_knomial_scatter(B, g, L_IN, SC);
+    return B;
+  }
+  throw std::runtime_error("unknown phase: " + name);
 }
 
 }  // namespace chb

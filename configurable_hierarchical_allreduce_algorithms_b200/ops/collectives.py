@@ -51,7 +51,7 @@ def _ll_ok(comm, ins, outs, payload_bytes):
     return all((t.data_ptr() % 8) == 0 for t in ins + outs)
 
 
-_COLL = {"allreduce": 0, "reduce_scatter": 1, "allgather": 2, "alltoall": 3, "gather": 4}
+_COLL = {"allreduce": 0, "reduce_scatter": 1, "allgather": 2, "alltoall": 3, "gather": 4, "phase": 5}
 _ALGO_BYTES: dict = {}
 _NVTX = __import__("os").environ.get("CHB_NVTX", "0") == "1"   # NVTX range around every launch
 
@@ -151,6 +151,25 @@ def gather(comm: Communicator, x, root: int = 0, out=None, k: int = 2, nctas: in
     n = ins[0].numel()
     outs = _as_list(comm, out) if out is not None else _alloc_like(comm, ins, n * comm.P)
     _run(comm, "gather", ins, outs, n, "sum", "k_nomial", k, 1, root, 1.0, nctas, stream, 1 << 62, LL_AG)
+    return _ret(comm, outs)
+
+
+def phase(comm: Communicator, name: str, x, count: int, k: int = 2, b: int = 1, op: str = "sum", out=None,
+          nctas: int = 0, stream=None):
+    """One phase of the hierarchical collectives as a call of its own (``name``: see
+    ``list_algorithms("phase")``), with the buffer layouts of the reference's stand-alone phase
+    functions (testing/custom_implementations/work_dir/reduce_scatter/intra_reduce_scatter_radix.cpp:208,
+    inter_linear_reduce.cpp:11, intra_scatter_radix_batch.cpp:11,
+    all_gather/outdated_versions/all_gather_0_3_beta.cpp:36,141,377).  Output entries that the phase does
+    not define (non-root ranks, missing stages) are left as they were."""
+    from ..parallel.program import cached_program
+
+    prog = cached_program("phase", name, comm.P, count, k, b)
+    ins = _as_list(comm, x)
+    if ins[0].numel() != prog.in_elems:
+        raise ValueError(f"{name}: input must hold {prog.in_elems} elements")
+    outs = _as_list(comm, out) if out is not None else _alloc_like(comm, ins, prog.out_elems)
+    _run(comm, "phase", ins, outs, count, op, name, k, b, 0, 1.0, nctas, stream, 1 << 62, LL_AG)
     return _ret(comm, outs)
 
 

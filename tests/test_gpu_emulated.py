@@ -409,3 +409,27 @@ def test_host_buffer_allreduce_pipeline(cuda):
     assert torch.equal(a, hx) and torch.equal(g, hx)       # one rank: both are the identity
     comm.check()
     comm.close()
+
+
+@pytest.mark.parametrize("P,b,k", [(8, 4, 2), (8, 2, 3), (6, 3, 2), (4, 1, 2)])
+def test_stand_alone_phases_chain_on_the_gpu(comms, P, b, k):
+    """intra reduce-scatter -> lane reduce -> scatter equals the reduce-scatter; gather -> lane allgather ->
+    Bruck allgather equals the allgather (the layouts between the phases are the reference's)."""
+    from configurable_hierarchical_allreduce_algorithms_b200.ops.collectives import phase
+
+    comm = comms(P)
+    n = 1000
+    xs = make_inputs(P, P * n, torch.int32, seed=3)
+    total = torch.stack(xs).sum(0)
+    y = phase(comm, "intra_reduce_scatter_radix_batch", xs, n, k=k, b=b)
+    y = phase(comm, "inter_reduce_linear", y, n, k=k, b=b)
+    y = phase(comm, "intra_scatter_radix_batch", y, n, k=k, b=b)
+    for r in range(P):
+        assert torch.equal(y[r], total[r * n:(r + 1) * n])
+    blocks = [x[:n].contiguous() for x in xs]
+    g = phase(comm, "intra_gather_k_nomial", blocks, n, k=k, b=b)
+    g = phase(comm, "inter_allgather_linear", g, n, k=k, b=b)
+    g = phase(comm, "intra_allgather_k_brucks", g, n * b, k=k, b=b)
+    for r in range(P):
+        assert torch.equal(g[r], torch.cat(blocks))
+    comm.check()

@@ -87,6 +87,13 @@ int MPICH_reduce_scatter_rec_halving(const void* sendbuf, void* recvbuf, int64_t
 int MPICH_reduce_scatter_rec_doubling(const void* sendbuf, void* recvbuf, int64_t recvcount, CHB_Datatype datatype, CHB_Op op, CHB_Comm comm);
 int MPICH_reduce_scatter_pairwise(const void* sendbuf, void* recvbuf, int64_t recvcount, CHB_Datatype datatype, CHB_Op op, CHB_Comm comm);
 int MPICH_reduce_scatter_radix(const void* sendbuf, void* recvbuf, int64_t recvcount, CHB_Datatype datatype, CHB_Op op, CHB_Comm comm, int k);
+int MPICH_reduce_scatter_k_nomial(const char* sendbuf, char* recvbuf, int count, CHB_Datatype datatype, CHB_Op op, CHB_Comm comm, int k);
+
+/* all-to-all-v with the radix-r / batch-b store-and-forward routing.  The blocks must be packed
+ * (sdispls / rdispls are the running sums of the counts) and sendtype == recvtype.  The ranks first
+ * exchange their count rows on the device, which synchronises the calling thread with the stream. */
+int tuna2_algorithm(int r, int b, char* sendbuf, int* sendcounts, int* sdispls, CHB_Datatype sendtype,
+                    char* recvbuf, int* recvcounts, int* rdispls, CHB_Datatype recvtype, CHB_Comm comm);
 
 #ifdef __cplusplus
 }

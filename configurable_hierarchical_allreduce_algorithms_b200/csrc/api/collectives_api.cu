@@ -6,6 +6,7 @@
 #include <mutex>
 #include <string>
 #include <tuple>
+#include <vector>
 
 #include "../sched/algos.h"
 #include "../symm/comm.h"
@@ -25,12 +26,18 @@ int chb_nvls_collective(chb_comm* c, int mode, int dtype, const void* in, void* 
                         float scale, int nctas, cudaStream_t stream);
 }
 
+namespace chb { Builder gen_a2av_tuna(int P, const std::vector<int64_t>& counts, int r, int b); }
+
 namespace {
 
 using Key = std::tuple<int, std::string, int, int, int, int64_t, int>;
 struct Cache {
   std::map<Key, chb_program*> progs;
-  ~Cache() { for (auto& kv : progs) delete kv.second; }
+  std::map<std::vector<int64_t>, chb_program*> a2av;   // key: r, b, then the P x P count matrix
+  ~Cache() {
+    for (auto& kv : progs) delete kv.second;
+    for (auto& kv : a2av) delete kv.second;
+  }
 };
 // one cache per communicator, owned here so that comm.h stays free of it; the map itself is shared by
 // all host threads (calls on ONE communicator are not thread safe, calls on different ones are)
@@ -263,6 +270,71 @@ CHB_RS0(MPICH_reduce_scatter_pairwise, "pairwise")
 int MPICH_reduce_scatter_radix(const void* sendbuf, void* recvbuf, int64_t recvcount, CHB_Datatype datatype, CHB_Op op,
                                CHB_Comm comm, int k) {
   return one(comm, CHB_REDUCE_SCATTER, "radix", sendbuf, recvbuf, recvcount, datatype, op, k, 1, 0);
+}
+
+int MPICH_reduce_scatter_k_nomial(const char* sendbuf, char* recvbuf, int count, CHB_Datatype datatype, CHB_Op op, CHB_Comm comm, int k) {
+  return one(comm, CHB_REDUCE_SCATTER, "k_nomial", sendbuf, recvbuf, count, datatype, op, k, 1, 0);
+}
+
+// Reference: testing/custom_implementations/work_dir/reduce_scatter/debug/tuna.cpp:9-270.
+int tuna2_algorithm(int r, int b, char* sendbuf, int* sendcounts, int* sdispls, CHB_Datatype sendtype,
+                    char* recvbuf, int* recvcounts, int* rdispls, CHB_Datatype recvtype, CHB_Comm comm) {
+  if (!comm || !sendbuf || !recvbuf || !sendcounts || !recvcounts || !sdispls || !rdispls) return CHB_ERR_ARG;
+  chb_comm* c = comm;
+  if (c->nlocal != 1) { c->last_error = "reference-compatible calls need one rank per process"; return CHB_ERR_ARG; }
+  if (sendtype != recvtype) { c->last_error = "tuna2_algorithm: send and receive types must match"; return CHB_ERR_UNSUPPORTED; }
+  const int P = c->P;
+  int64_t s = 0, q = 0;
+  for (int i = 0; i < P; ++i) {
+    if (sendcounts[i] < 0 || recvcounts[i] < 0) return CHB_ERR_COUNT;
+    if (sdispls[i] != s || rdispls[i] != q) { c->last_error = "tuna2_algorithm: blocks must be packed"; return CHB_ERR_UNSUPPORTED; }
+    s += sendcounts[i];
+    q += recvcounts[i];
+  }
+  // every rank needs the whole count matrix to know where its blocks sit in the peers' buffers
+  std::vector<int> all((size_t)P * P);
+  {
+    int *d_in = nullptr, *d_out = nullptr;
+    if (cudaMalloc(&d_in, sizeof(int) * P) != cudaSuccess || cudaMalloc(&d_out, sizeof(int) * P * P) != cudaSuccess) {
+      cudaFree(d_in);
+      return CHB_ERR_NO_MEM;
+    }
+    cudaMemcpyAsync(d_in, sendcounts, sizeof(int) * P, cudaMemcpyHostToDevice, g_compat_stream);
+    const void* in1 = d_in;
+    void* out1 = d_out;
+    int rc = chb_collective(c, CHB_ALLGATHER, "radix_batch", 2, 1, 0, CHB_I32, CHB_SUM, &in1, &out1, P, 1.0f, 0, g_compat_stream);
+    if (rc == CHB_SUCCESS) {
+      cudaMemcpyAsync(all.data(), d_out, sizeof(int) * P * P, cudaMemcpyDeviceToHost, g_compat_stream);
+      if (cudaStreamSynchronize(g_compat_stream) != cudaSuccess) rc = CHB_ERR_CUDA;
+    }
+    cudaFree(d_in);
+    cudaFree(d_out);
+    if (rc) return rc;
+  }
+  for (int i = 0; i < P; ++i)
+    if (all[(size_t)i * P + c->rank] != recvcounts[i]) { c->last_error = "tuna2_algorithm: recvcounts disagree with the senders' counts"; return CHB_ERR_COUNT; }
+  std::vector<int64_t> key{r, b};
+  key.insert(key.end(), all.begin(), all.end());
+  Cache& ca = cache_of(c);
+  chb_program* p = nullptr;
+  auto it = ca.a2av.find(key);
+  if (it != ca.a2av.end()) {
+    p = it->second;
+  } else {
+    try {
+      std::vector<int64_t> m(all.begin(), all.end());
+      chb::Builder B = chb::gen_a2av_tuna(P, m, r < 2 ? 2 : r, (b <= 0 || b > P) ? P : b);
+      p = new chb_program;
+      p->prog = B.lower(chb::LowerOpts{});
+      ca.a2av[key] = p;
+    } catch (const std::exception& e) {
+      c->last_error = e.what();
+      return CHB_ERR_ARG;
+    }
+  }
+  const void* in = sendbuf;
+  void* out = recvbuf;
+  return chb_run_program(c, p, sendtype, CHB_SUM, &in, &out, 1.0f, 0, g_compat_stream);
 }
 
 }  // extern "C"

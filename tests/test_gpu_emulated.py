@@ -433,3 +433,29 @@ def test_stand_alone_phases_chain_on_the_gpu(comms, P, b, k):
     for r in range(P):
         assert torch.equal(g[r], torch.cat(blocks))
     comm.check()
+
+
+def test_alltoallv_c_entry_point_in_a_world_of_one(cuda):
+    """tuna2_algorithm through its exported symbol: count exchange on the device, packed-layout checks, error codes."""
+    import ctypes as C
+    from configurable_hierarchical_allreduce_algorithms_b200 import _native as NN
+
+    comm = Communicator.emulated(1, scratch_bytes=1 << 20, user_bytes=1 << 20)
+    L = C.CDLL(str(NN._LIB_PATH))
+    vp, i32, ip = C.c_void_p, C.c_int, C.POINTER(C.c_int)
+    L.chb_set_stream.argtypes = [vp]
+    L.chb_set_stream(torch.cuda.current_stream().cuda_stream)
+    L.tuna2_algorithm.argtypes = [i32, i32, vp, ip, ip, i32, vp, ip, ip, i32, vp]
+    x = torch.arange(1000, device="cuda", dtype=torch.int32)
+    y = torch.zeros(1000, device="cuda", dtype=torch.int32)
+    one, zero = (C.c_int * 1)(1000), (C.c_int * 1)(0)
+    assert L.tuna2_algorithm(2, 1, x.data_ptr(), one, zero, NN.I32, y.data_ptr(), one, zero, NN.I32, comm.handle) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(x, y)
+    bad = (C.c_int * 1)(8)
+    assert L.tuna2_algorithm(2, 1, x.data_ptr(), one, bad, NN.I32, y.data_ptr(), one, zero, NN.I32, comm.handle) == NN.ERR_UNSUPPORTED
+    assert L.tuna2_algorithm(2, 1, x.data_ptr(), one, zero, NN.I32, y.data_ptr(), one, zero, NN.F32, comm.handle) == NN.ERR_UNSUPPORTED
+    wrong = (C.c_int * 1)(999)
+    assert L.tuna2_algorithm(2, 1, x.data_ptr(), one, zero, NN.I32, y.data_ptr(), wrong, zero, NN.I32, comm.handle) == NN.ERR_COUNT
+    comm.check()
+    comm.close()

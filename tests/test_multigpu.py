@@ -126,6 +126,30 @@ def _worker(rank, P, port, backend, q):
         torch.cuda.synchronize()
         assert torch.equal(og, torch.cat([_inp(r, cnt, torch.float32)[:4096] for r in range(P)]))
         assert L.all_reduce_radix_batch(a.data_ptr(), o.data_ptr(), cnt - 1, NN.F32, NN.SUM, comm.handle, 2, 1) == NN.ERR_COUNT
+        L.MPICH_reduce_scatter_k_nomial.argtypes = [vp, vp, i32, i32, i32, vp, i32]
+        okn = torch.zeros(4096, device="cuda")
+        assert L.MPICH_reduce_scatter_k_nomial(a.data_ptr(), okn.data_ptr(), 4096, NN.F32, NN.SUM, comm.handle, 3) == 0
+        close(okn, full[rank * 4096:(rank + 1) * 4096], torch.float32)
+        # all-to-all-v: rank s sends 100 * (s + 1) + 10 * d elements to rank d, packed
+        cnt_of = lambda s_, d_: 100 * (s_ + 1) + 10 * d_
+        sc = (C.c_int * P)(*[cnt_of(rank, d) for d in range(P)])
+        rc_ = (C.c_int * P)(*[cnt_of(s_, rank) for s_ in range(P)])
+        sd = (C.c_int * P)(*[sum(cnt_of(rank, d) for d in range(j)) for j in range(P)])
+        rd = (C.c_int * P)(*[sum(cnt_of(s_, rank) for s_ in range(j)) for j in range(P)])
+        src_of = lambda s_: torch.arange(sum(cnt_of(s_, d) for d in range(P)), device="cuda", dtype=torch.int32) + 100000 * s_
+        mine = src_of(rank)
+        got = torch.full((sum(cnt_of(s_, rank) for s_ in range(P)),), -1, device="cuda", dtype=torch.int32)
+        L.tuna2_algorithm.argtypes = [i32, i32, vp, C.POINTER(C.c_int), C.POINTER(C.c_int), i32, vp, C.POINTER(C.c_int),
+                                      C.POINTER(C.c_int), i32, vp]
+        for radix, batch in ((2, 1), (3, 2)):
+            got.fill_(-1)
+            assert L.tuna2_algorithm(radix, batch, mine.data_ptr(), sc, sd, NN.I32, got.data_ptr(), rc_, rd, NN.I32, comm.handle) == 0
+            torch.cuda.synchronize()
+            exp_parts = []
+            for s_ in range(P):
+                off = sum(cnt_of(s_, d) for d in range(rank))
+                exp_parts.append(src_of(s_)[off:off + cnt_of(s_, rank)])
+            assert torch.equal(got, torch.cat(exp_parts)), (radix, batch)
         # ---- fp8 block-scaled wire reduce-scatter against the exact result
         from configurable_hierarchical_allreduce_algorithms_b200.ops import fused
         nb = 128 * 512

@@ -51,3 +51,29 @@ def test_incorrect_rows_are_refused():
     bad[0]["is_correct"] = 0
     with pytest.raises(ValueError, match="incorrect"):
         autotune.winners(bad)
+
+
+def test_tuner_candidates_cover_the_kernel_families():
+    """Every cell's candidate list names only runnable configurations and offers each kernel family where it applies."""
+    from configurable_hierarchical_allreduce_algorithms_b200.bench import tune
+
+    class Comm:
+        ll_max_bytes, ll2_max_bytes, has_multicast = 1 << 20, 4 << 20, True
+
+    for P in (2, 4, 8):
+        for coll in ("allreduce", "reduce_scatter", "allgather"):
+            for nbytes in (8, 1 << 10, 1 << 16, 1 << 20, 1 << 24, 1 << 30):
+                cands = tune.candidates(coll, P, nbytes, Comm)
+                assert cands and len(set(cands)) == len(cands)
+                for algo, k, b, nctas in cands:
+                    assert k >= 2 and P % b == 0 and nctas >= 0
+                    assert algo in {"ll", "ll2", "radix_batch", "nvls", "nvls1", "bulk", "recursive_doubling"}
+                    assert algo != "ll2" or coll == "allreduce"
+                    assert algo != "bulk" or (coll == "allgather" and nbytes >= 1 << 20)
+                algos = {c[0] for c in cands}
+                assert "radix_batch" in algos
+                assert ("ll" in algos) == (nbytes <= Comm.ll_max_bytes)
+                if nbytes >= 1 << 24:
+                    assert "nvls" in algos and ("bulk" in algos) == (coll == "allgather")
+    Comm.has_multicast = False
+    assert all(c[0] not in ("nvls", "nvls1") for c in tune.candidates("allreduce", 8, 1 << 24, Comm))

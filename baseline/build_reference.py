@@ -24,6 +24,12 @@ W = REF / "testing" / "custom_implementations" / "work_dir"
 SOURCES = [W / "all_gather" / "all_gather_radix_batch_1_0.cpp",
            W / "reduce_scatter" / "reduce_scatter_radix_batch.cpp",
            W / "all_reduce" / "all_reduce_radix_batch.cpp"]
+# the stand-alone phase functions live in files of their own; the allgather ones come with a test main and an
+# older allgather_radix_batch, so they go into a second binary (renamed by -D, the sources stay untouched)
+PHASE_SOURCES = [W / "reduce_scatter" / "intra_reduce_scatter_radix.cpp",
+                 W / "reduce_scatter" / "inter_linear_reduce.cpp",
+                 W / "reduce_scatter" / "intra_scatter_radix_batch.cpp"]
+AG_BETA = W / "all_gather" / "outdated_versions" / "all_gather_0_3_beta.cpp"
 
 
 def build() -> Path:
@@ -39,6 +45,27 @@ def build() -> Path:
     cmd = ["g++", "-O3", "-std=c++17", "-w", "-pthread", "-I", str(HERE / "shim"),
            str(HERE / "shim" / "ref_driver.cpp"), str(HERE / "shim" / "shim.cpp"), *copied, "-o", str(exe)]
     subprocess.run(cmd, check=True)
+    build_phases()
+    return exe
+
+
+def build_phases() -> Path:
+    out = HERE / "_ref"
+    src = out / "src"
+    src.mkdir(parents=True, exist_ok=True)
+    objs = []
+    for s in PHASE_SOURCES + [AG_BETA]:
+        d = src / s.name
+        shutil.copyfile(s, d)
+        o = d.with_suffix(".o")
+        extra = ["-Dmain=reference_test_main"] if s == AG_BETA else []
+        subprocess.run(["g++", "-O2", "-std=c++17", "-w", "-pthread", "-I", str(HERE / "shim"), *extra, "-c", str(d),
+                        "-o", str(o)], check=True)
+        objs.append(str(o))
+    exe = out / "ref_phase_driver"
+    subprocess.run(["g++", "-O2", "-std=c++17", "-w", "-pthread", "-I", str(HERE / "shim"),
+                    str(HERE / "shim" / "ref_phase_driver.cpp"), str(HERE / "shim" / "shim.cpp"), *objs, "-o", str(exe)],
+                   check=True)
     return exe
 
 

@@ -1,5 +1,5 @@
 // Minimal single-process stand-in for <mpi.h>: every MPI rank is a thread of
-// one process.  Only what the reference's three collectives call is provided
+// one process.  Only what the reference's collectives and stand-alone phases call is provided
 // (rank / size / type size, Isend / Irecv / Wait / Waitall, Reduce_local,
 // Barrier, Wtime).  Sends are eager (the payload is copied into the
 // destination's mailbox), receives match on (source, tag) in arrival order.
@@ -8,6 +8,8 @@
 #pragma once
 #include <cstddef>
 #include <cstdint>
+#include <cstdlib>
+#include <cstring>   // the reference's older sources rely on their MPI header bringing these in
 
 typedef int MPI_Comm;
 typedef int MPI_Datatype;   // value = element size in bytes, except the tags below
@@ -45,6 +47,16 @@ int MPI_Waitall(int, MPI_Request*, MPI_Status*);
 int MPI_Reduce_local(const void*, void*, int, MPI_Datatype, MPI_Op);
 int MPI_Barrier(MPI_Comm);
 double MPI_Wtime();
+// blocking forms (the stand-alone phase sources use them)
+int MPI_Send(const void*, int, MPI_Datatype, int, int, MPI_Comm);
+int MPI_Recv(void*, int, MPI_Datatype, int, int, MPI_Comm, MPI_Status*);
+// Only the reference's own test mains call these; the mains are compiled (one of them is not behind a
+// macro) but never run, so the stubs just flag a failure.
+int MPI_Init(int*, char***);
+int MPI_Finalize();
+int MPI_Abort(MPI_Comm, int);
+int MPI_Allgather(const void*, int, MPI_Datatype, void*, int, MPI_Datatype, MPI_Comm);
+int MPI_Allreduce(const void*, void*, int, MPI_Datatype, MPI_Op, MPI_Comm);
 
 // shim control (not MPI): world size, per-thread rank, failure flag
 void shim_init(int nprocs);

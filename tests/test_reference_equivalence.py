@@ -46,3 +46,41 @@ def test_same_results_as_reference(ref_driver, P, b):
             ours = prog.simulate(ins)
             for r in range(P):
                 np.testing.assert_array_equal(ours[r], ref[r], err_msg=f"{coll} P={P} k={k} b={b} rank {r}")
+
+
+PHASE_EXE = ROOT / "baseline" / "_ref" / "ref_phase_driver"
+PHASES = ["intra_gather_k_nomial", "inter_allgather_linear", "intra_allgather_k_brucks",
+          "intra_reduce_scatter_radix_batch", "inter_reduce_linear", "intra_scatter_radix_batch"]
+
+
+@pytest.fixture(scope="module")
+def ref_phase_driver(ref_driver):
+    if not PHASE_EXE.exists():
+        from baseline import build_reference
+        if not (build_reference.REF / "testing").exists():
+            pytest.skip("reference sources are not available on this machine")
+        build_reference.build_phases()
+    return PHASE_EXE
+
+
+def reference_phase(exe, phase, P, k, b, c, seed, nout):
+    r = subprocess.run([str(exe), phase, str(P), str(k), str(b), str(c), str(seed)], capture_output=True, text=True, timeout=120)
+    vals = [int(v) for v in r.stdout.split()]
+    assert vals and vals[0] == 0, f"the reference's {phase} itself failed for P={P} k={k} b={b}"
+    return [np.array(vals[1 + i * nout:1 + (i + 1) * nout], dtype=np.int32) for i in range(P)]
+
+
+@pytest.mark.parametrize("P,b", [(4, 2), (8, 2), (8, 4), (9, 3), (12, 2), (12, 3), (16, 4), (18, 3), (6, 6), (4, 1), (10, 2), (15, 3),
+                                 (20, 4), (14, 2), (24, 4), (21, 3)])
+def test_stand_alone_phases_match_the_reference(ref_phase_driver, P, b):
+    """Each phase function of the reference (built unmodified) against the program of the same name: every entry
+    the reference defines must be identical, and entries it leaves alone must be left alone here too."""
+    seed, c = 3, 2
+    for k in (2, 3, 4):
+        for phase in PHASES:
+            prog = Program("phase", phase, P, c, k, b)
+            ref = reference_phase(ref_phase_driver, phase, P, k, b, c, seed, prog.out_elems)
+            ins = [((seed * 31 + r * 1009 + np.arange(prog.in_elems) * 7) % 97).astype(np.int32) for r in range(P)]
+            ours = prog.simulate(ins)
+            for r in range(P):
+                np.testing.assert_array_equal(ours[r], ref[r], err_msg=f"{phase} P={P} k={k} b={b} rank {r}")

@@ -48,7 +48,7 @@ Recexch::Recexch(int n_, int k_) : n(n_), k(k_) {
   rem = n - p_of_k;
   T = (int)((int64_t)rem * k / (k - 1));
 }
-bool Recexch::participates(int r) const { return !(r < T && r % k != k - 1) || false; }
+bool Recexch::participates(int r) const { return !(r < T && r % k != k - 1); }
 int Recexch::partner(int r) const {
   int p = r + (k - 1 - r % k);
   return p > T - 1 ? T : p;

@@ -127,14 +127,14 @@ void run_case(const AlgoSpec& s, bool threads_only) {
 
 int main(int argc, char** argv) {
   const bool threads_only = argc > 1 && !std::strcmp(argv[1], "threads-only");
-  const char* colls[] = {"allreduce", "reduce_scatter", "allgather", "alltoall", "gather"};
+  const char* colls[] = {"allreduce", "reduce_scatter", "allgather", "alltoall", "gather", "phase"};   // phases: memory safety only
   const int Ps_full[] = {1, 2, 3, 4, 6, 8, 12};
   const int Ps_thr[] = {2, 4, 6};
   const int* Ps = threads_only ? Ps_thr : Ps_full;
   const int nP = threads_only ? 3 : 7;
   for (const char* coll : colls) {
     std::vector<std::string> algos = list_algorithms(coll);
-    if (std::string(coll) != "alltoall" && std::string(coll) != "gather") {
+    if (std::string(coll) != "alltoall" && std::string(coll) != "gather" && std::string(coll) != "phase") {
       algos.push_back("intra_ring");
       algos.push_back("inter_ring");
     }

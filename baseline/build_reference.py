@@ -30,6 +30,14 @@ PHASE_SOURCES = [W / "reduce_scatter" / "intra_reduce_scatter_radix.cpp",
                  W / "reduce_scatter" / "inter_linear_reduce.cpp",
                  W / "reduce_scatter" / "intra_scatter_radix_batch.cpp"]
 AG_BETA = W / "all_gather" / "outdated_versions" / "all_gather_0_3_beta.cpp"
+M = REF / "testing" / "mpich_implementations"
+# MPICH-style baselines whose MPI calls the shim covers (the recursive-doubling reduce-scatter needs derived
+# datatypes and the SMP allreduce sub-communicators: not built)
+MPICH_SOURCES = [M / "all_reduce" / f for f in (
+    "allreduce_recursive_doubling.cpp", "allreduce_ring.cpp", "allreduce_reduce_scatter_allgather.cpp",
+    "allreduce_recursive_multiplying.cpp", "allreduce_k_reduce_scatter_allgather.cpp", "allreduce_recexch.cpp")] + [
+    M / "reduce_scatter" / f for f in ("reduce_scatter_recursive_halving.cpp", "reduce_scatter_pairwise.cpp",
+                                       "reduce_scatter_radix.cpp")]
 
 
 def build() -> Path:
@@ -46,6 +54,25 @@ def build() -> Path:
            str(HERE / "shim" / "ref_driver.cpp"), str(HERE / "shim" / "shim.cpp"), *copied, "-o", str(exe)]
     subprocess.run(cmd, check=True)
     build_phases()
+    build_mpich()
+    return exe
+
+
+def build_mpich() -> Path:
+    out = HERE / "_ref"
+    src = out / "src" / "mpich"
+    src.mkdir(parents=True, exist_ok=True)
+    for h in (M / "all_reduce" / "common.hpp", M / "reduce_scatter" / "reduce_scatter.hpp"):
+        shutil.copyfile(h, src / h.name)
+    copied = []
+    for s in MPICH_SOURCES:
+        d = src / s.name
+        shutil.copyfile(s, d)
+        copied.append(str(d))
+    exe = out / "ref_mpich_driver"
+    subprocess.run(["g++", "-O2", "-std=c++17", "-w", "-pthread", "-I", str(HERE / "shim"), "-I", str(src),
+                    str(HERE / "shim" / "ref_mpich_driver.cpp"), str(HERE / "shim" / "shim.cpp"), *copied, "-o", str(exe)],
+                   check=True)
     return exe
 
 

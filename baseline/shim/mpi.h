@@ -34,6 +34,7 @@ typedef ShimRequest* MPI_Request;
 #define MPI_MAX 1
 #define MPI_MIN 2
 #define MPI_IN_PLACE ((void*)-1)
+#define MPI_DATATYPE_NULL 0
 #define MPI_STATUS_IGNORE ((MPI_Status*)0)
 #define MPI_STATUSES_IGNORE ((MPI_Status*)0)
 
@@ -50,6 +51,10 @@ double MPI_Wtime();
 // blocking forms (the stand-alone phase sources use them)
 int MPI_Send(const void*, int, MPI_Datatype, int, int, MPI_Comm);
 int MPI_Recv(void*, int, MPI_Datatype, int, int, MPI_Comm, MPI_Status*);
+int MPI_Sendrecv(const void*, int, MPI_Datatype, int, int, void*, int, MPI_Datatype, int, int, MPI_Comm, MPI_Status*);
+int MPI_Op_commutative(MPI_Op, int*);
+// in-place form only (what the reference's ring allreduce uses): every rank's block already sits at displs[rank]
+int MPI_Allgatherv(const void*, int, MPI_Datatype, void*, const int*, const int*, MPI_Datatype, MPI_Comm);
 // Only the reference's own test mains call these; the mains are compiled (one of them is not behind a
 // macro) but never run, so the stubs just flag a failure.
 int MPI_Init(int*, char***);

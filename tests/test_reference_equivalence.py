@@ -84,3 +84,49 @@ def test_stand_alone_phases_match_the_reference(ref_phase_driver, P, b):
             ours = prog.simulate(ins)
             for r in range(P):
                 np.testing.assert_array_equal(ours[r], ref[r], err_msg=f"{phase} P={P} k={k} b={b} rank {r}")
+
+
+MPICH_EXE = ROOT / "baseline" / "_ref" / "ref_mpich_driver"
+MPICH = {  # reference entry point -> (collective, algorithm here, takes a radix)
+    "ar_recursive_doubling": ("allreduce", "recursive_doubling", False),
+    "ar_ring": ("allreduce", "ring", False),
+    "ar_reduce_scatter_allgather": ("allreduce", "reduce_scatter_allgather", False),
+    "ar_recursive_multiplying": ("allreduce", "recursive_multiplying", True),
+    "ar_k_reduce_scatter_allgather": ("allreduce", "k_reduce_scatter_allgather", True),
+    "ar_recursive_exchange": ("allreduce", "recursive_exchange", True),
+    "rs_rec_halving": ("reduce_scatter", "recursive_halving", False),
+    "rs_pairwise": ("reduce_scatter", "pairwise", False),
+    "rs_radix": ("reduce_scatter", "radix", True),
+}
+
+
+@pytest.fixture(scope="module")
+def ref_mpich_driver(ref_driver):
+    if not MPICH_EXE.exists():
+        from baseline import build_reference
+        if not (build_reference.REF / "testing").exists():
+            pytest.skip("reference sources are not available on this machine")
+        build_reference.build_mpich()
+    return MPICH_EXE
+
+
+@pytest.mark.parametrize("name", sorted(MPICH))
+def test_mpich_style_baselines_match_the_reference(ref_mpich_driver, name):
+    """The reference's MPICH-style baselines (built unmodified; the two that need derived datatypes or
+    sub-communicators are left out) and the programs of the same algorithms: identical results, also where
+    the number of ranks is not a power of the radix, and for the reference's in-place form."""
+    coll, algo, has_k = MPICH[name]
+    seed, n = 3, 3
+    for P in (2, 3, 4, 5, 6, 7, 8, 12):
+        nout = n * P if coll == "allreduce" else n
+        ins = [((seed * 31 + q * 1009 + np.arange(n * P) * 7) % 97).astype(np.int32) for q in range(P)]
+        for k in ((2, 3, 4) if has_k else (2,)):
+            ours = Program(coll, algo, P, n * P if coll == "allreduce" else n, k, 1).simulate(ins)
+            for mode in ([], ["inplace"]):
+                r = subprocess.run([str(ref_mpich_driver), name, str(P), str(k), str(n), str(seed)] + mode,
+                                   capture_output=True, text=True, timeout=120)
+                vals = [int(v) for v in r.stdout.split()]
+                assert vals and vals[0] == 0, f"the reference's {name} itself failed for P={P} k={k} {mode}"
+                for q in range(P):
+                    np.testing.assert_array_equal(ours[q], np.array(vals[1 + q * nout:1 + (q + 1) * nout], dtype=np.int32),
+                                                  err_msg=f"{name} P={P} k={k} {mode} rank {q}")

@@ -38,6 +38,11 @@ MPICH_SOURCES = [M / "all_reduce" / f for f in (
     "allreduce_recursive_multiplying.cpp", "allreduce_k_reduce_scatter_allgather.cpp", "allreduce_recexch.cpp")] + [
     M / "reduce_scatter" / f for f in ("reduce_scatter_recursive_halving.cpp", "reduce_scatter_pairwise.cpp",
                                        "reduce_scatter_radix.cpp")]
+# earlier variants kept in the reference tree; three of them come with a test main, renamed by -D
+EARLIER = {W / "reduce_scatter" / "tuna_based_outdated" / "reduce_scatter_radix_block_0_1.cpp": None,
+           W / "reduce_scatter" / "tuna_based_outdated" / "reduce_scatter_k_nomial.cpp": "k_nomial_test_main",
+           W / "reduce_scatter" / "debug" / "tuna.cpp": "tuna_test_main",
+           W / "all_gather" / "outdated_versions" / "all_gather_0_1_alpha.cpp": "ag_alpha_test_main"}
 
 
 def build() -> Path:
@@ -64,14 +69,17 @@ def build_mpich() -> Path:
     src.mkdir(parents=True, exist_ok=True)
     for h in (M / "all_reduce" / "common.hpp", M / "reduce_scatter" / "reduce_scatter.hpp"):
         shutil.copyfile(h, src / h.name)
-    copied = []
-    for s in MPICH_SOURCES:
+    objs = []
+    for s, rename in [(m, None) for m in MPICH_SOURCES] + list(EARLIER.items()):
         d = src / s.name
         shutil.copyfile(s, d)
-        copied.append(str(d))
+        o = d.with_suffix(".o")
+        subprocess.run(["g++", "-O2", "-std=c++17", "-w", "-pthread", "-I", str(HERE / "shim"), "-I", str(src),
+                        *([f"-Dmain={rename}"] if rename else []), "-c", str(d), "-o", str(o)], check=True)
+        objs.append(str(o))
     exe = out / "ref_mpich_driver"
-    subprocess.run(["g++", "-O2", "-std=c++17", "-w", "-pthread", "-I", str(HERE / "shim"), "-I", str(src),
-                    str(HERE / "shim" / "ref_mpich_driver.cpp"), str(HERE / "shim" / "shim.cpp"), *copied, "-o", str(exe)],
+    subprocess.run(["g++", "-O2", "-std=c++17", "-w", "-pthread", "-I", str(HERE / "shim"),
+                    str(HERE / "shim" / "ref_mpich_driver.cpp"), str(HERE / "shim" / "shim.cpp"), *objs, "-o", str(exe)],
                    check=True)
     return exe
 

@@ -8,6 +8,8 @@
 #pragma once
 #include <cstddef>
 #include <cstdint>
+#include <climits>
+#include <cmath>
 #include <cstdlib>
 #include <cstring>   // the reference's older sources rely on their MPI header bringing these in
 
@@ -62,6 +64,12 @@ int MPI_Finalize();
 int MPI_Abort(MPI_Comm, int);
 int MPI_Allgather(const void*, int, MPI_Datatype, void*, int, MPI_Datatype, MPI_Comm);
 int MPI_Allreduce(const void*, void*, int, MPI_Datatype, MPI_Op, MPI_Comm);
+int MPI_Reduce(const void*, void*, int, MPI_Datatype, MPI_Op, int, MPI_Comm);
+int MPI_Bcast(void*, int, MPI_Datatype, int, MPI_Comm);
+int MPI_Gather(const void*, int, MPI_Datatype, void*, int, MPI_Datatype, int, MPI_Comm);
+int MPI_Scatter(const void*, int, MPI_Datatype, void*, int, MPI_Datatype, int, MPI_Comm);
+int MPI_Reduce_scatter(const void*, void*, const int*, MPI_Datatype, MPI_Op, MPI_Comm);
+int MPI_Alltoallv(const void*, const int*, const int*, MPI_Datatype, void*, const int*, const int*, MPI_Datatype, MPI_Comm);
 
 // shim control (not MPI): world size, per-thread rank, failure flag
 void shim_init(int nprocs);

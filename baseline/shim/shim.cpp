@@ -136,7 +136,27 @@ int MPI_Init(int*, char***) { g_fail = true; return MPI_ERR_OTHER; }
 int MPI_Finalize() { return MPI_SUCCESS; }
 int MPI_Abort(MPI_Comm, int) { g_fail = true; return MPI_ERR_OTHER; }
 int MPI_Allgather(const void*, int, MPI_Datatype, void*, int, MPI_Datatype, MPI_Comm) { g_fail = true; return MPI_ERR_OTHER; }
-int MPI_Allreduce(const void*, void*, int, MPI_Datatype, MPI_Op, MPI_Comm) { g_fail = true; return MPI_ERR_OTHER; }
+int MPI_Allreduce(const void* sendbuf, void* recvbuf, int n, MPI_Datatype d, MPI_Op op, MPI_Comm c) {
+  // (the store-and-forward all-to-all-v agrees on its largest block this way)
+  if (sendbuf == MPI_IN_PLACE) { g_fail = true; return MPI_ERR_OTHER; }
+  static std::vector<const void*> bufs;
+  { std::lock_guard<std::mutex> l(g_bar_m); if ((int)bufs.size() != g_n) bufs.assign(g_n, nullptr); bufs[t_rank] = sendbuf; }
+  MPI_Barrier(c);
+  std::memcpy(recvbuf, bufs[0], (size_t)n * type_bytes(d));
+  int rc = MPI_SUCCESS;
+  for (int q = 1; q < g_n && rc == MPI_SUCCESS; ++q) rc = MPI_Reduce_local(bufs[q], recvbuf, n, d, op);
+  MPI_Barrier(c);
+  return rc;
+}
+int MPI_Reduce(const void*, void*, int, MPI_Datatype, MPI_Op, int, MPI_Comm) { g_fail = true; return MPI_ERR_OTHER; }
+int MPI_Bcast(void*, int, MPI_Datatype, int, MPI_Comm) { g_fail = true; return MPI_ERR_OTHER; }
+int MPI_Gather(const void*, int, MPI_Datatype, void*, int, MPI_Datatype, int, MPI_Comm) { g_fail = true; return MPI_ERR_OTHER; }
+int MPI_Scatter(const void*, int, MPI_Datatype, void*, int, MPI_Datatype, int, MPI_Comm) { g_fail = true; return MPI_ERR_OTHER; }
+int MPI_Reduce_scatter(const void*, void*, const int*, MPI_Datatype, MPI_Op, MPI_Comm) { g_fail = true; return MPI_ERR_OTHER; }
+int MPI_Alltoallv(const void*, const int*, const int*, MPI_Datatype, void*, const int*, const int*, MPI_Datatype, MPI_Comm) {
+  g_fail = true;
+  return MPI_ERR_OTHER;
+}
 double MPI_Wtime() {
   return std::chrono::duration<double>(std::chrono::steady_clock::now().time_since_epoch()).count();
 }

@@ -130,3 +130,61 @@ def test_mpich_style_baselines_match_the_reference(ref_mpich_driver, name):
                 for q in range(P):
                     np.testing.assert_array_equal(ours[q], np.array(vals[1 + q * nout:1 + (q + 1) * nout], dtype=np.int32),
                                                   err_msg=f"{name} P={P} k={k} {mode} rank {q}")
+
+
+def _ref_earlier(exe, name, P, k, n, seed, extra, nout):
+    r = subprocess.run([str(exe), name, str(P), str(k), str(n), str(seed)] + ([str(extra)] if extra is not None else []),
+                       capture_output=True, text=True, timeout=30)
+    vals = [int(v) for v in r.stdout.split()]
+    assert vals and vals[0] == 0, f"the reference's {name} itself failed for P={P} k={k} extra={extra}"
+    return [np.array(vals[1 + q * nout:1 + (q + 1) * nout], dtype=np.int32) for q in range(P)]
+
+
+def test_earlier_variants_match_the_reference(ref_mpich_driver):
+    """The earlier variants the reference keeps in its tree, built unmodified: the store-and-forward
+    reduce-scatter (radix r <= P - 2, batch b), the flat radix-k Bruck allgather, the flat k-nomial gather, the k-nomial
+    reduce-scatter (on the shapes where the reference's own copy works: P a power of k) and the
+    all-to-all-v with ragged counts."""
+    seed, n = 5, 3
+    pat = lambda q, m: ((seed * 31 + q * 1009 + np.arange(m) * 7) % 97).astype(np.int32)
+    for P in (2, 3, 4, 5, 6, 8, 9, 12):
+        full = [pat(q, n * P) for q in range(P)]
+        for r_ in (2, 3, 4):
+            if r_ > P - 2:
+                continue                      # the reference's copy does not terminate once the radix reaches P - 1
+            for batch in (1, 2, P):
+                ours = Program("reduce_scatter", "radix_block", P, n, r_, batch).simulate(full)
+                ref = _ref_earlier(ref_mpich_driver, "rs_radix_block", P, r_, n, seed, batch, n)
+                for q in range(P):
+                    np.testing.assert_array_equal(ours[q], ref[q], err_msg=f"radix_block P={P} r={r_} b={batch} rank {q}")
+        for k in (2, 3):
+            if P not in {2: (2, 4, 8), 3: (3, 9)}[k]:
+                continue      # elsewhere the reference's copy returns another rank's block (P=3, k=2) or an error code
+            ours = Program("reduce_scatter", "k_nomial", P, n, k, 1).simulate(full)
+            ref = _ref_earlier(ref_mpich_driver, "rs_k_nomial", P, k, n, seed, None, n)
+            for q in range(P):
+                np.testing.assert_array_equal(ours[q], ref[q], err_msg=f"k_nomial P={P} k={k} rank {q}")
+        blocks = [pat(q, n) for q in range(P)]
+        for k in (2, 3, 4):
+            ours = Program("allgather", "k_brucks", P, n, k, 1).simulate(blocks)
+            ref = _ref_earlier(ref_mpich_driver, "ag_k_brucks", P, k, n, seed, None, n * P)
+            for q in range(P):
+                np.testing.assert_array_equal(ours[q], ref[q], err_msg=f"k_brucks P={P} k={k} rank {q}")
+            ours = Program("gather", "k_nomial", P, n, k, 1, aux=0).simulate(blocks)
+            ref = _ref_earlier(ref_mpich_driver, "gather_k_nomial", P, k, n, seed, None, n * P)
+            np.testing.assert_array_equal(ours[0], ref[0], err_msg=f"gather_k_nomial P={P} k={k}")
+        # all-to-all-v: rank s sends n + (s + 2 d) % 3 elements to rank d
+        cnt = lambda s_, d_: n + (s_ + 2 * d_) % 3
+        counts = [[cnt(s_, d_) for d_ in range(P)] for s_ in range(P)]
+        nin = max(sum(row) for row in counts)
+        nout = max(sum(counts[s_][d_] for s_ in range(P)) for d_ in range(P))
+        for r_, batch in ((2, 1), (3, 2)):
+            if P < 3:
+                continue
+            prog = Program.alltoallv(counts, r=r_, b=batch)
+            ours = prog.simulate([pat(q, prog.in_elems) for q in range(P)])
+            ref = _ref_earlier(ref_mpich_driver, "a2av_tuna2", P, r_, n, seed, batch, nout)
+            assert prog.in_elems == nin
+            for q in range(P):
+                m = sum(counts[s_][q] for s_ in range(P))
+                np.testing.assert_array_equal(ours[q][:m], ref[q][:m], err_msg=f"alltoallv P={P} r={r_} b={batch} rank {q}")

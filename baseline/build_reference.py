@@ -23,7 +23,9 @@ REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(
 W = REF / "testing" / "custom_implementations" / "work_dir"
 SOURCES = [W / "all_gather" / "all_gather_radix_batch_1_0.cpp",
            W / "reduce_scatter" / "reduce_scatter_radix_batch.cpp",
-           W / "all_reduce" / "all_reduce_radix_batch.cpp"]
+           W / "all_reduce" / "all_reduce_radix_batch.cpp",
+           W / "all_reduce" / "all_reduce_semi_custom_0_1.cpp"]
+CUSTOM = W / "all_reduce" / "all_reduce_custom_0_2.cpp"    # defines its own all_reduce_radix_batch: a binary of its own
 # the stand-alone phase functions live in files of their own; the allgather ones come with a test main and an
 # older allgather_radix_batch, so they go into a second binary (renamed by -D, the sources stay untouched)
 PHASE_SOURCES = [W / "reduce_scatter" / "intra_reduce_scatter_radix.cpp",
@@ -60,6 +62,19 @@ def build() -> Path:
     subprocess.run(cmd, check=True)
     build_phases()
     build_mpich()
+    build_custom()
+    return exe
+
+
+def build_custom() -> Path:
+    out = HERE / "_ref"
+    src = out / "src"
+    d = src / CUSTOM.name
+    shutil.copyfile(CUSTOM, d)
+    exe = out / "ref_custom_driver"
+    subprocess.run(["g++", "-O2", "-std=c++17", "-w", "-pthread", "-I", str(HERE / "shim"),
+                    str(HERE / "shim" / "ref_custom_driver.cpp"), str(HERE / "shim" / "shim.cpp"), str(d), "-o", str(exe)],
+                   check=True)
     return exe
 
 

@@ -1,7 +1,8 @@
 // Runs the reference's own collectives (compiled unmodified against the
 // thread-per-rank shim) for timing and for golden checks.
 //   ref_driver time  <ar|rs|ag> P k b bytes_per_rank steps warmup
-//   ref_driver check <ar|rs|ag> P k b elems_per_rank seed      (int32 pattern, prints the rank-0 result)
+//   ref_driver check <ar|rs|ag|semi> P k b elems_per_rank seed (int32 pattern, prints every rank's result;
+//                    semi = all_reduce_semi_radix_batch)
 // Timing follows the reference's drivers: Barrier; t0; call; Barrier; t1
 // (testing/custom_implementations/work_dir/all_reduce/main.cpp:56-66), here
 // taken as the maximum over ranks.
@@ -17,6 +18,7 @@
 int allgather_radix_batch(char*, int, MPI_Datatype, char*, MPI_Comm, int, int);
 int reduce_scatter_radix_batch(const void*, void*, MPI_Aint, MPI_Datatype, MPI_Op, MPI_Comm, int, int);
 int all_reduce_radix_batch(char*, char*, int, MPI_Datatype, MPI_Op, MPI_Comm, int, int);
+int all_reduce_semi_radix_batch(char*, char*, int, MPI_Datatype, MPI_Op, MPI_Comm, int, int);   // "semi" in check mode
 
 static int pattern(int seed, int r, long i) { return (int)((seed * 31L + r * 1009L + i) % 97); }
 
@@ -43,7 +45,8 @@ int main(int argc, char** argv) {
       } else {
         std::vector<int> s(n * P); out[r].assign(n * P, -1);
         for (long i = 0; i < n * P; ++i) s[i] = pattern(seed, r, i);
-        all_reduce_radix_batch((char*)s.data(), (char*)out[r].data(), (int)(n * P), MPI_INT, MPI_SUM, 0, k, b);
+        if (coll == "semi") all_reduce_semi_radix_batch((char*)s.data(), (char*)out[r].data(), (int)(n * P), MPI_INT, MPI_SUM, 0, k, b);
+        else all_reduce_radix_batch((char*)s.data(), (char*)out[r].data(), (int)(n * P), MPI_INT, MPI_SUM, 0, k, b);
       }
     });
     for (auto& t : th) t.join();

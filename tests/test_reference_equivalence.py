@@ -30,7 +30,7 @@ def reference_result(exe, coll, P, k, b, n, seed):
                        capture_output=True, text=True, timeout=120)
     vals = [int(v) for v in r.stdout.split()]
     assert vals[0] == 0, "the reference itself failed (timeout / bad destination / truncation)"
-    per = {"ag": n * P, "rs": n, "ar": n * P}[coll]
+    per = {"ag": n * P, "rs": n, "ar": n * P, "semi": n * P}[coll]
     return [np.array(vals[1 + i * per:1 + (i + 1) * per], dtype=np.int32) for i in range(P)]
 
 
@@ -188,3 +188,29 @@ def test_earlier_variants_match_the_reference(ref_mpich_driver):
             for q in range(P):
                 m = sum(counts[s_][q] for s_ in range(P))
                 np.testing.assert_array_equal(ours[q][:m], ref[q][:m], err_msg=f"alltoallv P={P} r={r_} b={batch} rank {q}")
+
+
+@pytest.mark.parametrize("P,b", [(4, 2), (8, 2), (8, 4), (8, 8), (6, 3), (12, 3), (12, 2), (16, 4)])
+def test_semi_custom_and_custom_allreduce_match_the_reference(ref_driver, P, b):
+    """all_reduce_semi_radix_batch (recursive-halving reduce-scatter + hierarchical allgather,
+    all_reduce_semi_custom_0_1.cpp:159-193) and the earlier custom allreduce (store-and-forward reduce-scatter +
+    hierarchical allgather, all_reduce_custom_0_2.cpp:49-663), both built unmodified."""
+    seed, n = 5, 2
+    custom_exe = ROOT / "baseline" / "_ref" / "ref_custom_driver"
+    if not custom_exe.exists():
+        from baseline import build_reference
+        build_reference.build_custom()
+    ins = [((seed * 31 + r * 1009 + np.arange(n * P)) % 97).astype(np.int32) for r in range(P)]
+    for k in (2, 3):
+        ref = reference_result(ref_driver, "semi", P, k, b, n, seed)
+        ours = Program("allreduce", "semi_radix_batch", P, n * P, k, b).simulate(ins)
+        for r in range(P):
+            np.testing.assert_array_equal(ours[r], ref[r], err_msg=f"semi P={P} k={k} b={b} rank {r}")
+        if k <= P - 2:       # the store-and-forward half of the reference does not terminate with a radix of P - 1 or more
+            out = subprocess.run([str(custom_exe), str(P), str(k), str(b), str(n), str(seed)], capture_output=True, text=True, timeout=30)
+            vals = [int(v) for v in out.stdout.split()]
+            assert vals and vals[0] == 0, f"the reference's custom allreduce failed for P={P} r={k} b={b}"
+            ours = Program("allreduce", "custom", P, n * P, k, b).simulate(ins)
+            for r in range(P):
+                np.testing.assert_array_equal(ours[r], np.array(vals[1 + r * n * P:1 + (r + 1) * n * P], dtype=np.int32),
+                                              err_msg=f"custom P={P} r={k} b={b} rank {r}")

@@ -33,13 +33,13 @@ PHASE_SOURCES = [W / "reduce_scatter" / "intra_reduce_scatter_radix.cpp",
                  W / "reduce_scatter" / "intra_scatter_radix_batch.cpp"]
 AG_BETA = W / "all_gather" / "outdated_versions" / "all_gather_0_3_beta.cpp"
 M = REF / "testing" / "mpich_implementations"
-# MPICH-style baselines whose MPI calls the shim covers (the recursive-doubling reduce-scatter needs derived
-# datatypes and the SMP allreduce sub-communicators: not built)
+# the MPICH-style baselines (the SMP allreduce fixes its node size at compile time: built with RANKS_PER_NODE=2)
 MPICH_SOURCES = [M / "all_reduce" / f for f in (
     "allreduce_recursive_doubling.cpp", "allreduce_ring.cpp", "allreduce_reduce_scatter_allgather.cpp",
-    "allreduce_recursive_multiplying.cpp", "allreduce_k_reduce_scatter_allgather.cpp", "allreduce_recexch.cpp")] + [
+    "allreduce_recursive_multiplying.cpp", "allreduce_k_reduce_scatter_allgather.cpp", "allreduce_recexch.cpp",
+    "allreduce_inter_reduce_exchange_bcast.cpp")] + [
     M / "reduce_scatter" / f for f in ("reduce_scatter_recursive_halving.cpp", "reduce_scatter_pairwise.cpp",
-                                       "reduce_scatter_radix.cpp")]
+                                       "reduce_scatter_radix.cpp", "reduce_scatter_recursive_doubling.cpp")]
 # earlier variants kept in the reference tree; three of them come with a test main, renamed by -D
 EARLIER = {W / "reduce_scatter" / "tuna_based_outdated" / "reduce_scatter_radix_block_0_1.cpp": None,
            W / "reduce_scatter" / "tuna_based_outdated" / "reduce_scatter_k_nomial.cpp": "k_nomial_test_main",
@@ -90,7 +90,7 @@ def build_mpich() -> Path:
         shutil.copyfile(s, d)
         o = d.with_suffix(".o")
         subprocess.run(["g++", "-O2", "-std=c++17", "-w", "-pthread", "-I", str(HERE / "shim"), "-I", str(src),
-                        *([f"-Dmain={rename}"] if rename else []), "-c", str(d), "-o", str(o)], check=True)
+                        "-DRANKS_PER_NODE=2", *([f"-Dmain={rename}"] if rename else []), "-c", str(d), "-o", str(o)], check=True)
         objs.append(str(o))
     exe = out / "ref_mpich_driver"
     subprocess.run(["g++", "-O2", "-std=c++17", "-w", "-pthread", "-I", str(HERE / "shim"),

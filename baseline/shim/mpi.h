@@ -14,7 +14,7 @@
 #include <cstring>   // the reference's older sources rely on their MPI header bringing these in
 
 typedef int MPI_Comm;
-typedef int MPI_Datatype;   // value = element size in bytes, except the tags below
+typedef int MPI_Datatype;   // value = element size in bytes, except the tags below; >= 1000: derived type
 typedef int MPI_Op;
 typedef long MPI_Aint;
 struct MPI_Status { int MPI_SOURCE, MPI_TAG, MPI_ERROR; };
@@ -37,6 +37,8 @@ typedef ShimRequest* MPI_Request;
 #define MPI_MIN 2
 #define MPI_IN_PLACE ((void*)-1)
 #define MPI_DATATYPE_NULL 0
+#define MPI_COMM_NULL (-1)
+#define MPI_UNDEFINED (-32766)
 #define MPI_STATUS_IGNORE ((MPI_Status*)0)
 #define MPI_STATUSES_IGNORE ((MPI_Status*)0)
 
@@ -55,10 +57,18 @@ int MPI_Send(const void*, int, MPI_Datatype, int, int, MPI_Comm);
 int MPI_Recv(void*, int, MPI_Datatype, int, int, MPI_Comm, MPI_Status*);
 int MPI_Sendrecv(const void*, int, MPI_Datatype, int, int, void*, int, MPI_Datatype, int, int, MPI_Comm, MPI_Status*);
 int MPI_Op_commutative(MPI_Op, int*);
+int MPI_Comm_split(MPI_Comm, int, int, MPI_Comm*);
+int MPI_Comm_free(MPI_Comm*);
+// derived datatypes: lists of byte segments of a basic type (what the recursive-doubling reduce-scatter builds)
+int MPI_Type_create_hindexed(int, const int*, const MPI_Aint*, MPI_Datatype, MPI_Datatype*);
+int MPI_Type_commit(MPI_Datatype*);
+int MPI_Type_free(MPI_Datatype*);
+int MPI_Type_get_extent(MPI_Datatype, MPI_Aint*, MPI_Aint*);
+int MPI_Type_get_true_extent(MPI_Datatype, MPI_Aint*, MPI_Aint*);
 // in-place form only (what the reference's ring allreduce uses): every rank's block already sits at displs[rank]
 int MPI_Allgatherv(const void*, int, MPI_Datatype, void*, const int*, const int*, MPI_Datatype, MPI_Comm);
-// Only the reference's own test mains call these; the mains are compiled (one of them is not behind a
-// macro) but never run, so the stubs just flag a failure.
+// MPI_Reduce / MPI_Allreduce / MPI_Bcast are real (the SMP allreduce and the all-to-all-v use them); the rest of
+// this block is only called by the reference's own test mains, which are compiled but never run: stubs that flag a failure.
 int MPI_Init(int*, char***);
 int MPI_Finalize();
 int MPI_Abort(MPI_Comm, int);
@@ -69,6 +79,7 @@ int MPI_Bcast(void*, int, MPI_Datatype, int, MPI_Comm);
 int MPI_Gather(const void*, int, MPI_Datatype, void*, int, MPI_Datatype, int, MPI_Comm);
 int MPI_Scatter(const void*, int, MPI_Datatype, void*, int, MPI_Datatype, int, MPI_Comm);
 int MPI_Reduce_scatter(const void*, void*, const int*, MPI_Datatype, MPI_Op, MPI_Comm);
+int MPI_Reduce_scatter_block(const void*, void*, int, MPI_Datatype, MPI_Op, MPI_Comm);
 int MPI_Alltoallv(const void*, const int*, const int*, MPI_Datatype, void*, const int*, const int*, MPI_Datatype, MPI_Comm);
 
 // shim control (not MPI): world size, per-thread rank, failure flag

@@ -2,7 +2,8 @@
 // int32 pattern and prints every rank's output.
 //   ref_mpich_driver <name> P k n seed [inplace]
 // name: ar_recursive_doubling | ar_ring | ar_reduce_scatter_allgather | ar_recursive_multiplying |
-//       ar_k_reduce_scatter_allgather | ar_recursive_exchange | rs_rec_halving | rs_pairwise | rs_radix |
+//       ar_k_reduce_scatter_allgather | ar_recursive_exchange | ar_smp (2 ranks per node) | rs_rec_halving |
+//       rs_rec_doubling | rs_pairwise | rs_radix |
 //       the earlier variants rs_radix_block (k = radix, extra argument batch) | rs_k_nomial | ag_k_brucks |
 //       gather_k_nomial (root 0) | a2av_tuna2 (k = radix, extra argument batch; rank s sends n + (s + 2 d) % 3
 //       elements to rank d)
@@ -25,6 +26,8 @@ int MPICH_Allreduce_recursive_exchange(const char*, char*, int, MPI_Datatype, MP
 int MPICH_reduce_scatter_rec_halving(const char*, char*, int, MPI_Datatype, MPI_Op, MPI_Comm);
 int MPICH_reduce_scatter_pairwise(const void*, void*, MPI_Aint, MPI_Datatype, MPI_Op, MPI_Comm);
 int MPICH_reduce_scatter_radix(const void*, void*, MPI_Aint, MPI_Datatype, MPI_Op, MPI_Comm, int);
+int MPICH_reduce_scatter_rec_doubling(const void*, void*, MPI_Aint, MPI_Datatype, MPI_Op, MPI_Comm);
+int MPICH_Allreduce_inter_reduce_exchange_bcast(const char*, char*, int, MPI_Datatype, MPI_Op, MPI_Comm);   // built with RANKS_PER_NODE=2
 int reduce_scatter_radix_block(char*, char*, int, MPI_Datatype, MPI_Op, MPI_Comm, int, int);
 int MPICH_reduce_scatter_k_nomial(const char*, char*, int, MPI_Datatype, MPI_Op, MPI_Comm, int);
 int allgather_k_brucks(char*, int, MPI_Datatype, char*, MPI_Comm, int);
@@ -71,6 +74,8 @@ int main(int argc, char** argv) {
     else if (name == "rs_rec_halving") rcs[r] = MPICH_reduce_scatter_rec_halving(sb, rb, cnt, MPI_INT, MPI_SUM, 0);
     else if (name == "rs_pairwise") rcs[r] = MPICH_reduce_scatter_pairwise(sb, rb, n, MPI_INT, MPI_SUM, 0);
     else if (name == "rs_radix") rcs[r] = MPICH_reduce_scatter_radix(sb, rb, n, MPI_INT, MPI_SUM, 0, k);
+    else if (name == "rs_rec_doubling") rcs[r] = MPICH_reduce_scatter_rec_doubling(sb, rb, n, MPI_INT, MPI_SUM, 0);
+    else if (name == "ar_smp") rcs[r] = MPICH_Allreduce_inter_reduce_exchange_bcast(sb, rb, cnt, MPI_INT, MPI_SUM, 0);
     else if (name == "rs_radix_block") rcs[r] = reduce_scatter_radix_block((char*)s.data(), rb, (int)n, MPI_INT, MPI_SUM, 0, k, batch);
     else if (name == "rs_k_nomial") rcs[r] = MPICH_reduce_scatter_k_nomial(sb, rb, (int)n, MPI_INT, MPI_SUM, 0, k);
     else if (name == "ag_k_brucks") rcs[r] = allgather_k_brucks((char*)s.data(), (int)n, MPI_INT, rb, 0, k);

@@ -94,7 +94,9 @@ MPICH = {  # reference entry point -> (collective, algorithm here, takes a radix
     "ar_recursive_multiplying": ("allreduce", "recursive_multiplying", True),
     "ar_k_reduce_scatter_allgather": ("allreduce", "k_reduce_scatter_allgather", True),
     "ar_recursive_exchange": ("allreduce", "recursive_exchange", True),
+    "ar_smp": ("allreduce", "inter_reduce_exchange_bcast", False),          # built with 2 ranks per node
     "rs_rec_halving": ("reduce_scatter", "recursive_halving", False),
+    "rs_rec_doubling": ("reduce_scatter", "recursive_doubling", False),
     "rs_pairwise": ("reduce_scatter", "pairwise", False),
     "rs_radix": ("reduce_scatter", "radix", True),
 }
@@ -112,17 +114,19 @@ def ref_mpich_driver(ref_driver):
 
 @pytest.mark.parametrize("name", sorted(MPICH))
 def test_mpich_style_baselines_match_the_reference(ref_mpich_driver, name):
-    """The reference's MPICH-style baselines (built unmodified; the two that need derived datatypes or
-    sub-communicators are left out) and the programs of the same algorithms: identical results, also where
-    the number of ranks is not a power of the radix, and for the reference's in-place form."""
+    """The reference's MPICH-style baselines (built unmodified) and the programs of the same algorithms:
+    identical results, also where the number of ranks is not a power of the radix, and for the reference's
+    in-place form."""
     coll, algo, has_k = MPICH[name]
     seed, n = 3, 3
     for P in (2, 3, 4, 5, 6, 7, 8, 12):
         nout = n * P if coll == "allreduce" else n
         ins = [((seed * 31 + q * 1009 + np.arange(n * P) * 7) % 97).astype(np.int32) for q in range(P)]
+        if name == "ar_smp" and P % 2:
+            continue                                   # whole nodes of two ranks
         for k in ((2, 3, 4) if has_k else (2,)):
-            ours = Program(coll, algo, P, n * P if coll == "allreduce" else n, k, 1).simulate(ins)
-            for mode in ([], ["inplace"]):
+            ours = Program(coll, algo, P, n * P if coll == "allreduce" else n, k, 1, aux=2 if name == "ar_smp" else 0).simulate(ins)
+            for mode in ([], ["inplace"]) if name != "ar_smp" else ([],):
                 r = subprocess.run([str(ref_mpich_driver), name, str(P), str(k), str(n), str(seed)] + mode,
                                    capture_output=True, text=True, timeout=120)
                 vals = [int(v) for v in r.stdout.split()]

@@ -1,0 +1,49 @@
+"""Randomised shapes: any registered algorithm, any rank count up to 24, any radix, any group size that
+divides the ranks, ragged element counts, random interleavings - the simulated result is the definition
+of the collective and the schedule has no unsynchronised hazard."""
+import numpy as np
+from hypothesis import HealthCheck, given, settings, strategies as st
+
+from configurable_hierarchical_allreduce_algorithms_b200 import Program, ProgramError, list_algorithms
+
+COLLS = ["allreduce", "reduce_scatter", "allgather"]
+
+
+@st.composite
+def cases(draw):
+    coll = draw(st.sampled_from(COLLS))
+    algo = draw(st.sampled_from(list_algorithms(coll)))
+    P = draw(st.integers(1, 24))
+    b = draw(st.sampled_from([d for d in range(1, P + 1) if P % d == 0]))
+    k = draw(st.integers(2, 9))
+    n = draw(st.integers(1, 7))
+    op = draw(st.sampled_from(["sum", "max", "min"]))
+    seed = draw(st.integers(0, 2 ** 31))
+    return coll, algo, P, k, b, n, op, seed
+
+
+@settings(max_examples=500, deadline=None, suppress_health_check=list(HealthCheck))
+@given(cases())
+def test_random_shapes(case):
+    coll, algo, P, k, b, n, op, seed = case
+    count = n * P if coll == "allreduce" else n
+    aux = 0
+    if algo == "inter_reduce_exchange_bcast":
+        aux = b                                     # ranks per node
+    try:
+        p = Program(coll, algo, P, count, k=k, b=b, aux=aux)
+    except ProgramError as e:
+        # a documented precondition (power-of-two ranks for recursive doubling allgather, ...), never a crash
+        assert any(w in str(e) for w in ("power", "divide", "multiple", "must", "needs", "radix", "ranks")), str(e)
+        return
+    p.verify()
+    rng = np.random.default_rng(seed)
+    ins = [rng.integers(-40, 40, p.in_elems).astype(np.int64) for _ in range(P)]
+    outs = p.simulate(ins, op=op, seed=seed)
+    if coll == "allgather":
+        exp = [np.concatenate(ins)] * P
+    else:
+        red = {"sum": np.sum, "max": np.max, "min": np.min}[op](np.stack(ins), axis=0)
+        exp = [red] * P if coll == "allreduce" else [red[r * n:(r + 1) * n] for r in range(P)]
+    for r in range(P):
+        np.testing.assert_array_equal(outs[r], exp[r], err_msg=f"{case} rank {r}")

@@ -1,5 +1,6 @@
 """Randomised shapes: any registered algorithm, any rank count up to 24, any radix, any group size that
-divides the ranks, ragged element counts, random interleavings - the simulated result is the definition
+divides the ranks, ragged element counts, every way of lowering (private, peer-visible or aliased caller
+buffers), random interleavings - the simulated result is the definition
 of the collective and the schedule has no unsynchronised hazard."""
 import numpy as np
 from hypothesis import HealthCheck, given, settings, strategies as st
@@ -19,19 +20,22 @@ def cases(draw):
     n = draw(st.integers(1, 7))
     op = draw(st.sampled_from(["sum", "max", "min"]))
     seed = draw(st.integers(0, 2 ** 31))
-    return coll, algo, P, k, b, n, op, seed
+    lowering = draw(st.sampled_from(["private", "symmetric", "in_symmetric", "out_symmetric", "in_place"]))
+    return coll, algo, P, k, b, n, op, seed, lowering
 
 
 @settings(max_examples=500, deadline=None, suppress_health_check=list(HealthCheck))
 @given(cases())
 def test_random_shapes(case):
-    coll, algo, P, k, b, n, op, seed = case
+    coll, algo, P, k, b, n, op, seed, lowering = case
+    flags = dict(in_symmetric=lowering in ("symmetric", "in_symmetric"), out_symmetric=lowering in ("symmetric", "out_symmetric"),
+                 in_place=lowering == "in_place")
     count = n * P if coll == "allreduce" else n
     aux = 0
     if algo == "inter_reduce_exchange_bcast":
         aux = b                                     # ranks per node
     try:
-        p = Program(coll, algo, P, count, k=k, b=b, aux=aux)
+        p = Program(coll, algo, P, count, k=k, b=b, aux=aux, **flags)
     except ProgramError as e:
         # a documented precondition (power-of-two ranks for recursive doubling allgather, ...), never a crash
         assert any(w in str(e) for w in ("power", "divide", "multiple", "must", "needs", "radix", "ranks")), str(e)

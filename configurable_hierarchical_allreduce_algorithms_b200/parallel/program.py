@@ -142,24 +142,32 @@ class Program:
             raise AssertionError(f"{self.name}: {bad} unsynchronised hazards: {err.value.decode()}")
         return 0
 
-    def simulate(self, inputs: list[np.ndarray], op: str = "sum", seed: int = 0) -> list[np.ndarray]:
-        """Run all P ranks on host arrays; returns the P output arrays."""
+    def simulate(self, inputs: list[np.ndarray], op: str = "sum", seed: int = 0, alias: bool = False) -> list[np.ndarray]:
+        """Run all P ranks on host arrays; returns the P output arrays.  ``alias=True`` hands every rank ONE
+        buffer as both input and output (the in-place form; the program must have been created with
+        ``in_place=True``)."""
         assert len(inputs) == self.P
         dt = inputs[0].dtype
         code = _DT_FROM_NP[np.dtype(dt)]
         ins = [np.ascontiguousarray(x, dtype=dt) for x in inputs]
         for x in ins:
             assert x.size == self.in_elems, (x.size, self.in_elems)
-        # outputs start poisoned so that positions the program never writes stand out
-        outs = [np.full(self.out_elems, -17, dtype=dt) for _ in range(self.P)]
+        if alias:
+            assert self.in_place, "aliased buffers need a program lowered with in_place=True"
+            bufs = [np.full(max(self.in_elems, self.out_elems), -17, dtype=dt) for _ in range(self.P)]
+            for b_, x in zip(bufs, ins):
+                b_[:x.size] = x
+            ins, outs = bufs, bufs
+        else:
+            # outputs start poisoned so that positions the program never writes stand out
+            outs = [np.full(self.out_elems, -17, dtype=dt) for _ in range(self.P)]
         ip = (C.c_void_p * self.P)(*[x.ctypes.data for x in ins])
         opp = (C.c_void_p * self.P)(*[x.ctypes.data for x in outs])
         err = C.create_string_buffer(512)
         rc = N.lib().chb_program_simulate(self._h, code, _OPS[op], ip, opp, seed, err, len(err))
         if rc:
             raise RuntimeError(f"simulate({self.name}) failed: {err.value.decode()}")
-        return outs
-
+        return [o[:self.out_elems] for o in outs]
 
     def run_threads(self, inputs: list[np.ndarray], op: str = "sum", iters: int = 1):
         """Run all P ranks as concurrent host threads; returns (outputs, mean seconds per repetition)."""

@@ -11,6 +11,7 @@
 // (testing/custom_implementations/work_dir/all_gather/all_gather_radix_batch_1_0.cpp:148-163)
 // in its flat (b = 1) form: every rank fetches every block from its owner.
 #include <cstdio>
+#include <mutex>
 
 #include "../api/chb.h"
 #include "../symm/comm.h"
@@ -176,6 +177,8 @@ int chb_ag_bulk(chb_comm* c, const void* const* in, void* const* out, long long 
   const int max_pair_ctas = (kSigSlots - kSigNvlsBase) / kMaxRanks;
   int budget = c->max_ctas / c->nlocal;           // 128 KiB of shared memory: one CTA per SM
   static bool attr_set[64] = {};
+  static std::mutex attr_mu;                      // several host threads may make their first call at once
+  std::lock_guard<std::mutex> attr_lock(attr_mu);
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {

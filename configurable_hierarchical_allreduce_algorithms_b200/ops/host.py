@@ -150,7 +150,7 @@ def all_reduce_host(comm: Communicator, hx: torch.Tensor, hy: torch.Tensor | Non
                     scale: float = 1.0, chunk_elems: int = 16 << 20, depth: int = 3, **kw) -> torch.Tensor:
     """One-off form of :class:`HostAllReduce`; the pipeline is cached on the communicator per
     (dtype, chunk, depth) so repeated calls reuse its device buffers."""
-    cache = comm.__dict__.setdefault("_host_pipelines", {})
+    cache = comm._host_pipelines
     key = (hx.dtype, int(chunk_elems), int(depth))
     pipe = cache.get(key)
     if pipe is None:

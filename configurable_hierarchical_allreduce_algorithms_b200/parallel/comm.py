@@ -106,6 +106,7 @@ class Communicator:
         self._programs = {}
         self._choices = {}       # (collective, bytes, dtype, symmetric) -> autotune.Choice
         self._user_ranges = []
+        self._host_pipelines = {}  # (dtype, chunk, depth) -> ops.host.HostAllReduce
         self.group = None
         return self
 
@@ -282,6 +283,7 @@ class Communicator:
         if self._h:
             L = N.lib()
             torch.cuda.synchronize()
+            self._host_pipelines = {}                    # their buffers live in the heap that goes away below
             if getattr(self, "_boot", None):
                 L.chb_bootstrap_barrier(self._boot)      # nobody frees a heap that a peer may still read
             L.chb_comm_destroy(self._h)

@@ -30,9 +30,14 @@ except ImportError:  # pragma: no cover - depends on the image
     plt = None
 
 
-def _need_plt():
-    if plt is None:
-        raise RuntimeError("matplotlib is not installed; only median_best (as a markdown table) is available")
+def _md_table(path: str, header: list[str], rows: list[list]) -> str:
+    """Without matplotlib every analysis is written as a markdown table instead of a figure."""
+    with open(path, "w") as f:
+        f.write("| " + " | ".join(header) + " |\n|" + "---|" * len(header) + "\n")
+        for r in rows:
+            f.write("| " + " | ".join(f"{v:.3e}" if isinstance(v, float) else str(v) for v in r) + " |\n")
+    return path
+
 
 VENDOR_NAMES = {"MPICH_allreduce", "allgather_standard", "reduce_scatter_standard"}
 
@@ -106,10 +111,14 @@ def median_best(path: str, outdir: str = ".", stat: str = "median") -> str:
 
 
 def per_algo(path: str, outdir: str = ".", stat: str = "median") -> list[str]:
-    _need_plt()
     m = cell_stat(load(path), stat)
     outs = []
     for p, g in m.groupby("nprocs"):
+        if plt is None:
+            best = g.groupby(["send_count", "algorithm_name"])["time"].min().unstack("algorithm_name")
+            rows = [[int(n)] + [float(v) if v == v else "" for v in best.loc[n].values] for n in best.index]
+            outs.append(_md_table(os.path.join(outdir, f"{stat}_per_algo_np{p}.md"), ["send_count"] + list(best.columns), rows))
+            continue
         fig, ax = plt.subplots(figsize=(7, 4.5))
         for name, h in g.groupby("algorithm_name"):
             best = h.groupby("send_count")["time"].min()
@@ -129,9 +138,19 @@ def per_algo(path: str, outdir: str = ".", stat: str = "median") -> list[str]:
 
 def radix(path: str, outdir: str = ".", stat: str = "median") -> str:
     """Median time against k for every send_count; best / second / worst k marked, library as a dashed line."""
-    _need_plt()
     df = load(path)
     ns = sorted(df["send_count"].unique())
+    if plt is None:
+        rows = []
+        for n in ns:
+            g = df[(df["send_count"] == n) & (df["k"] > 0)]
+            order = getattr(g.groupby("k")["time"], stat)().sort_values()
+            v = df[(df["send_count"] == n) & df["algorithm_name"].isin(VENDOR_NAMES)]["time"]
+            rows.append([int(n), int(order.index[0]) if len(order) else "", float(order.iloc[0]) if len(order) else "",
+                         int(order.index[1]) if len(order) > 1 else "", int(order.index[-1]) if len(order) > 1 else "",
+                         float(getattr(v, stat)()) if len(v) else ""])
+        return _md_table(os.path.join(outdir, "radix_" + os.path.splitext(os.path.basename(path))[0] + ".md"),
+                         ["send_count", "best k", "its time (s)", "second k", "worst k", "library (s)"], rows)
     fig, axes = plt.subplots(1, len(ns), figsize=(3.2 * len(ns), 3), squeeze=False)
     for ax, n in zip(axes[0], ns):
         g = df[(df["send_count"] == n) & (df["k"] > 0)]
@@ -156,9 +175,13 @@ def radix(path: str, outdir: str = ".", stat: str = "median") -> str:
 
 
 def winners(path: str, outdir: str = ".", stat: str = "median") -> str:
-    _need_plt()
     df = load(path)
     w = winners_table(df, stat)
+    if plt is None:
+        rows = [[int(r["nprocs"]), int(r["send_count"]), r["winner"], float(r["time"]), float(r["vendor_time"])]
+                for _, r in w.sort_values(["nprocs", "send_count"]).iterrows()]
+        return _md_table(os.path.join(outdir, "winners_" + os.path.splitext(os.path.basename(path))[0] + ".md"),
+                         ["nprocs", "send_count", "winner", "time (s)", "library (s)"], rows)
     fig, ax = plt.subplots(figsize=(7, 4.5))
     for p, g in w.groupby("nprocs"):
         g = g.sort_values("send_count")

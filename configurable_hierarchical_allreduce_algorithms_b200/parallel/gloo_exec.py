@@ -100,6 +100,9 @@ class GlooExecutor:
         return out
 
 
+_EXECUTORS: dict = {}     # (program, group) -> executor with its per-round send / receive lists already built
+
+
 def run_collective(coll: str, algo: str, x: torch.Tensor, count: int, k: int = 2, b: int = 1, aux: int = 0,
                    op: str = "sum", group=None) -> torch.Tensor:
     """Compile (cached per process) and execute one collective on CPU tensors."""
@@ -107,4 +110,10 @@ def run_collective(coll: str, algo: str, x: torch.Tensor, count: int, k: int = 2
 
     P = dist.get_world_size(group if group is not None else dist.group.WORLD)
     prog = cached_program(coll, algo, P, count, k, b, aux, False, False)
-    return GlooExecutor(prog, group).run(x, op=op)
+    key = (id(prog), id(group))         # both objects stay alive (program cache / caller's group), so ids are stable
+    ex = _EXECUTORS.get(key)
+    if ex is None:
+        if len(_EXECUTORS) > 256:
+            _EXECUTORS.clear()
+        ex = _EXECUTORS[key] = GlooExecutor(prog, group)
+    return ex.run(x, op=op)

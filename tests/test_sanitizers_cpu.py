@@ -49,3 +49,25 @@ def test_threaded_executor_under_tsan(tmp_path):
     r = subprocess.run([str(exe), "threads-only"], capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, (r.stdout[-2000:], r.stderr[-4000:])
     assert "0 failures" in r.stdout and "ThreadSanitizer" not in r.stderr
+
+
+@pytest.mark.skipif(CXX is None, reason="no g++")
+def test_bootstrap_under_asan_ubsan(tmp_path):
+    """The shared-memory rendezvous (forked ranks, barriers, blob exchange, a rank that never arrives) with
+    AddressSanitizer + UndefinedBehaviorSanitizer in every process."""
+    flags = ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"]
+    probe = tmp_path / "probe.cc"
+    probe.write_text("int main(){return 0;}\n")
+    if subprocess.run([CXX, *flags, str(probe), "-o", str(tmp_path / "probe")], capture_output=True).returncode != 0:
+        pytest.skip("sanitizers are not available with this compiler")
+    obj = tmp_path / "bootstrap_test.o"
+    r = subprocess.run([shutil.which("gcc") or "gcc", "-O1", "-g", *flags, "-I", str(CSRC / "boot"), "-c",
+                        str(ROOT / "tests" / "native" / "bootstrap_test.c"), "-o", str(obj)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
+    exe = tmp_path / "bootstrap_san"
+    r = subprocess.run([CXX, "-std=c++17", "-O1", "-g", *flags, "-I", str(CSRC), str(obj), str(CSRC / "boot" / "bootstrap.cc"),
+                        "-o", str(exe), "-lpthread", "-lrt"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-3000:]
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "BOOTSTRAP OK" in r.stdout, (r.stdout[-1000:], r.stderr[-3000:])
+    assert "Sanitizer" not in r.stderr

@@ -43,7 +43,8 @@ class ClockSampler:
         self._t = None
 
     def _loop(self):
-        # NVML (read-only queries) samples every 10 ms; nvidia-smi is the fallback
+        # NVML (read-only queries) samples every 2 ms, so that a timed region of a few ms still holds samples;
+        # nvidia-smi is the fallback
         try:
             import pynvml
             pynvml.nvmlInit()
@@ -74,7 +75,7 @@ class ClockSampler:
                 row += ["Active" if rs & bits[n] else "Not Active"
                         for n in ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")]
                 self.rows.append(row + [ts])
-                self._stop.wait(0.01)
+                self._stop.wait(0.002)
             return
         except Exception:  # noqa: BLE001
             pass

@@ -41,7 +41,7 @@ def test_sampler_reads_clocks_and_reasons(monkeypatch):
     s = cs.summary()
     assert s["sm_mhz"] == 1342 and s["sm_max_mhz"] == 1965
     assert s["reasons"] == ["sw_power_cap", "sw_thermal_slowdown"]
-    assert s["sampled_during"] == "timed region" and 3 <= s["samples"] <= 20
+    assert s["sampled_during"] == "timed region" and 10 <= s["samples"] <= 80      # 120 ms at one sample per 2 ms (plus query time)
     # a window shorter than the sampling period: the samples right before it are used, and the summary says so
     cs.mark(t1 - 0.0001, t1 - 0.00005)
     s2 = cs.summary()

@@ -44,3 +44,31 @@ def test_native_bootstrap_rendezvous(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0 and "BOOTSTRAP OK" in r.stdout, r.stdout + r.stderr
+
+
+def _build_ranks_example(tmp_path):
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    exe = tmp_path / "native_ranks_example"
+    cmd = [nvcc, "-x", "c", str(ROOT / "tests" / "native" / "native_ranks_example.c"), "-I", str(PKG / "csrc" / "api"),
+           "-I", str(PKG / "csrc" / "boot"), "-L", str(PKG), "-lchb", "-Xlinker", f"-rpath={PKG}", "-o", str(exe)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr[-2000:]
+    return exe
+
+
+def test_native_ranks_example_compiles(tmp_path):
+    """Launcher + bootstrap + cudaIpc communicator + reference-signature call from plain C: the headers fit together."""
+    from configurable_hierarchical_allreduce_algorithms_b200 import _native
+    _native.lib()
+    _build_ranks_example(tmp_path)
+
+
+@pytest.mark.multigpu
+def test_native_ranks_example_runs(tmp_path):
+    import torch
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    exe = _build_ranks_example(tmp_path)
+    r = subprocess.run([str(exe), str(min(n, 4))], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "NATIVE RANKS OK" in r.stdout, r.stdout + r.stderr

@@ -3,6 +3,7 @@
 //   ref_driver time  <ar|rs|ag> P k b bytes_per_rank steps warmup
 //   ref_driver check <ar|rs|ag|semi> P k b elems_per_rank seed (int32 pattern, prints every rank's result;
 //                    semi = all_reduce_semi_radix_batch)
+//   ref_driver checkf <ar|rs|semi> P k b elems_per_rank seed   (float32 values that do not add exactly; prints bit patterns)
 // Timing follows the reference's drivers: Barrier; t0; call; Barrier; t1
 // (testing/custom_implementations/work_dir/all_reduce/main.cpp:56-66), here
 // taken as the maximum over ranks.
@@ -27,6 +28,32 @@ int main(int argc, char** argv) {
   const std::string mode = argv[1], coll = argv[2];
   const int P = std::atoi(argv[3]), k = std::atoi(argv[4]), b = std::atoi(argv[5]);
   shim_init(P);
+  if (mode == "checkf") {
+    // the same on float32 values that do not add exactly: the printed bit patterns depend on the order of the additions
+    const long n = std::atol(argv[6]);
+    const int seed = std::atoi(argv[7]);
+    std::vector<std::vector<float>> out(P);
+    std::vector<std::thread> th;
+    auto fpat = [&](int r, long i) { return (float)pattern(seed, r, i) / 7.0f + (float)r * 0.37f; };
+    for (int r = 0; r < P; ++r) th.emplace_back([&, r] {
+      shim_set_rank(r);
+      if (coll == "rs") {
+        std::vector<float> s(n * P); out[r].assign(n, -1.f);
+        for (long i = 0; i < n * P; ++i) s[i] = fpat(r, i);
+        reduce_scatter_radix_batch(s.data(), out[r].data(), n, MPI_FLOAT, MPI_SUM, 0, k, b);
+      } else {
+        std::vector<float> s(n * P); out[r].assign(n * P, -1.f);
+        for (long i = 0; i < n * P; ++i) s[i] = fpat(r, i);
+        if (coll == "semi") all_reduce_semi_radix_batch((char*)s.data(), (char*)out[r].data(), (int)(n * P), MPI_FLOAT, MPI_SUM, 0, k, b);
+        else all_reduce_radix_batch((char*)s.data(), (char*)out[r].data(), (int)(n * P), MPI_FLOAT, MPI_SUM, 0, k, b);
+      }
+    });
+    for (auto& t : th) t.join();
+    std::printf("%d", shim_failed());
+    for (int r = 0; r < P; ++r) for (float v : out[r]) { unsigned u; std::memcpy(&u, &v, 4); std::printf(" %u", u); }
+    std::printf("\n");
+    return shim_failed();
+  }
   if (mode == "check") {
     const long n = std::atol(argv[6]);
     const int seed = std::atoi(argv[7]);

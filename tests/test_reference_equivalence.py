@@ -218,3 +218,38 @@ def test_semi_custom_and_custom_allreduce_match_the_reference(ref_driver, P, b):
             for r in range(P):
                 np.testing.assert_array_equal(ours[r], np.array(vals[1 + r * n * P:1 + (r + 1) * n * P], dtype=np.int32),
                                               err_msg=f"custom P={P} r={k} b={b} rank {r}")
+
+
+@pytest.mark.parametrize("P,b", [(4, 1), (4, 2), (8, 2), (8, 4), (8, 8), (12, 3), (16, 4), (18, 3), (6, 6), (9, 3), (10, 2), (12, 2)])
+def test_float_results_are_bit_identical_to_the_reference(ref_driver, P, b):
+    """float32 inputs that do not add exactly: the bits of a sum depend on the order of the additions.  The pull
+    programs combine their sources in the order in which the reference receives and reduces them, so the results
+    agree bit for bit (reduce-scatter, allreduce and the semi-custom allreduce)."""
+    seed, n = 5, 3
+    pat = lambda q: (((seed * 31 + q * 1009 + np.arange(n * P)) % 97).astype(np.float32) / np.float32(7.0)
+                     + np.float32(q) * np.float32(0.37)).astype(np.float32)
+    ins = [pat(q) for q in range(P)]
+    exact = np.sum(np.stack(ins).astype(np.float64), axis=0)
+    for k in (2, 3, 4):
+        for short, coll, algo in (("rs", "reduce_scatter", "radix_batch"), ("ar", "allreduce", "radix_batch"),
+                                  ("semi", "allreduce", "semi_radix_batch")):
+            r = subprocess.run([str(ref_driver), "checkf", short, str(P), str(k), str(b), str(n), str(seed)],
+                               capture_output=True, text=True, timeout=120)
+            vals = [int(v) for v in r.stdout.split()]
+            assert vals and vals[0] == 0
+            per = n if short == "rs" else n * P
+            ours = Program(coll, algo, P, per, k, b).simulate(ins)
+            for q in range(P):
+                ref = np.array(vals[1 + q * per:1 + (q + 1) * per], dtype=np.uint32)
+                np.testing.assert_array_equal(ours[q].view(np.uint32), ref, err_msg=f"{coll}/{algo} P={P} k={k} b={b} rank {q}")
+    # the test has teeth: another order of the same additions changes bits for these inputs
+    flipped = np.sum(np.stack(ins[::-1]), axis=0, dtype=np.float32)
+    forward = ins[0].copy()
+    for x in ins[1:]:
+        forward = forward + x
+    backward = ins[-1].copy()
+    for x in ins[-2::-1]:
+        backward = backward + x
+    assert np.allclose(forward, exact, rtol=1e-5) and flipped.shape == forward.shape
+    if P >= 8:
+        assert not np.array_equal(forward.view(np.uint32), backward.view(np.uint32))

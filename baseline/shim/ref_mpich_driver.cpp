@@ -11,6 +11,7 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <string>
 #include <thread>
 #include <vector>
@@ -43,7 +44,8 @@ int main(int argc, char** argv) {
   const long n = std::atol(argv[4]);
   const int seed = std::atoi(argv[5]);
   const bool inplace = argc > 6 && std::string(argv[6]) == "inplace";
-  const int batch = (argc > 6 && !inplace) ? std::atoi(argv[6]) : 1;
+  const bool as_float = argc > 6 && std::string(argv[6]) == "float";   // float32 values that do not add exactly; bit patterns are printed
+  const int batch = (argc > 6 && !inplace && !as_float) ? std::atoi(argv[6]) : 1;
   const bool ar = name.rfind("ar_", 0) == 0;
   long nin = n * P, nout = ar ? n * P : n;
   if (name == "ag_k_brucks" || name == "gather_k_nomial") { nin = n; nout = n * P; }
@@ -60,22 +62,25 @@ int main(int argc, char** argv) {
     shim_set_rank(r);
     std::vector<int> s(nin);
     for (long i = 0; i < nin; ++i) s[i] = pattern(seed, r, i);
+    if (as_float)
+      for (long i = 0; i < nin; ++i) { float f = (float)pattern(seed, r, i) / 7.0f + (float)r * 0.37f; std::memcpy(&s[i], &f, 4); }
+    const MPI_Datatype T = as_float ? MPI_FLOAT : MPI_INT;
     out[r].assign(inplace ? nin : nout, -17);
     if (inplace) out[r] = s;
     const char* sb = inplace ? (const char*)MPI_IN_PLACE : (const char*)s.data();
     char* rb = (char*)out[r].data();
     const int cnt = (int)(ar ? nin : n);
-    if (name == "ar_recursive_doubling") rcs[r] = MPICH_Allreduce_recursive_doubling(sb, rb, cnt, MPI_INT, MPI_SUM, 0);
-    else if (name == "ar_ring") rcs[r] = MPICH_Allreduce_ring(sb, rb, cnt, MPI_INT, MPI_SUM, 0);
-    else if (name == "ar_reduce_scatter_allgather") rcs[r] = MPICH_Allreduce_reduce_scatter_allgather(sb, rb, cnt, MPI_INT, MPI_SUM, 0);
-    else if (name == "ar_recursive_multiplying") rcs[r] = MPICH_Allreduce_recursive_multiplying(sb, rb, cnt, MPI_INT, MPI_SUM, 0, k);
-    else if (name == "ar_k_reduce_scatter_allgather") rcs[r] = MPICH_Allreduce_k_reduce_scatter_allgather(sb, rb, cnt, MPI_INT, MPI_SUM, 0, k, 1);
-    else if (name == "ar_recursive_exchange") rcs[r] = MPICH_Allreduce_recursive_exchange(sb, rb, cnt, MPI_INT, MPI_SUM, 0, k, 1);
-    else if (name == "rs_rec_halving") rcs[r] = MPICH_reduce_scatter_rec_halving(sb, rb, cnt, MPI_INT, MPI_SUM, 0);
-    else if (name == "rs_pairwise") rcs[r] = MPICH_reduce_scatter_pairwise(sb, rb, n, MPI_INT, MPI_SUM, 0);
-    else if (name == "rs_radix") rcs[r] = MPICH_reduce_scatter_radix(sb, rb, n, MPI_INT, MPI_SUM, 0, k);
-    else if (name == "rs_rec_doubling") rcs[r] = MPICH_reduce_scatter_rec_doubling(sb, rb, n, MPI_INT, MPI_SUM, 0);
-    else if (name == "ar_smp") rcs[r] = MPICH_Allreduce_inter_reduce_exchange_bcast(sb, rb, cnt, MPI_INT, MPI_SUM, 0);
+    if (name == "ar_recursive_doubling") rcs[r] = MPICH_Allreduce_recursive_doubling(sb, rb, cnt, T, MPI_SUM, 0);
+    else if (name == "ar_ring") rcs[r] = MPICH_Allreduce_ring(sb, rb, cnt, T, MPI_SUM, 0);
+    else if (name == "ar_reduce_scatter_allgather") rcs[r] = MPICH_Allreduce_reduce_scatter_allgather(sb, rb, cnt, T, MPI_SUM, 0);
+    else if (name == "ar_recursive_multiplying") rcs[r] = MPICH_Allreduce_recursive_multiplying(sb, rb, cnt, T, MPI_SUM, 0, k);
+    else if (name == "ar_k_reduce_scatter_allgather") rcs[r] = MPICH_Allreduce_k_reduce_scatter_allgather(sb, rb, cnt, T, MPI_SUM, 0, k, 1);
+    else if (name == "ar_recursive_exchange") rcs[r] = MPICH_Allreduce_recursive_exchange(sb, rb, cnt, T, MPI_SUM, 0, k, 1);
+    else if (name == "rs_rec_halving") rcs[r] = MPICH_reduce_scatter_rec_halving(sb, rb, cnt, T, MPI_SUM, 0);
+    else if (name == "rs_pairwise") rcs[r] = MPICH_reduce_scatter_pairwise(sb, rb, n, T, MPI_SUM, 0);
+    else if (name == "rs_radix") rcs[r] = MPICH_reduce_scatter_radix(sb, rb, n, T, MPI_SUM, 0, k);
+    else if (name == "rs_rec_doubling") rcs[r] = MPICH_reduce_scatter_rec_doubling(sb, rb, n, T, MPI_SUM, 0);
+    else if (name == "ar_smp") rcs[r] = MPICH_Allreduce_inter_reduce_exchange_bcast(sb, rb, cnt, T, MPI_SUM, 0);
     else if (name == "rs_radix_block") rcs[r] = reduce_scatter_radix_block((char*)s.data(), rb, (int)n, MPI_INT, MPI_SUM, 0, k, batch);
     else if (name == "rs_k_nomial") rcs[r] = MPICH_reduce_scatter_k_nomial(sb, rb, (int)n, MPI_INT, MPI_SUM, 0, k);
     else if (name == "ag_k_brucks") rcs[r] = allgather_k_brucks((char*)s.data(), (int)n, MPI_INT, rb, 0, k);

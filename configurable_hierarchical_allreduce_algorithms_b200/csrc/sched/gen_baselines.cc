@@ -207,54 +207,67 @@ Builder gen_ar_rabenseifner(int P, int64_t N) {
 }
 
 // ============================ allreduce: radix-k RS + AG =============================
+// Radix-k recursive exchange: reduce-scatter with the nearest neighbours first, so that a rank ends up with
+// the block whose index is its digit-reversed rank, then the allgather in the opposite order.  Phases,
+// block sizes (count / k^log each, the last block takes the remainder) and the order in which a rank adds its
+// neighbours' contributions follow the reference
+// (testing/mpich_implementations/all_reduce/allreduce_k_reduce_scatter_allgather.cpp:330-470), which makes
+// float results identical to its results bit for bit.
 Builder gen_ar_k_rsag(int P, int64_t N, int k) {
   Builder B(P, N, N, "allreduce_k_reduce_scatter_allgather");
   if (P == 1) { B.copy(0, L_OUT, 0, 0, L_IN, 0, N); return B; }
   Recexch rx(P, k);
-  std::vector<int64_t> off, cnt;
-  split_blocks(N, rx.p_of_k, off, cnt);
+  const int K = rx.k, L = rx.log, pk = rx.p_of_k;
+  std::vector<int64_t> off(pk + 1);
+  for (int i = 0; i < pk; ++i) off[i] = (int64_t)i * (N / pk);
+  off[pk] = N;
   int ACC = B.tmp(N);
   std::vector<int> cur(P, L_IN);
   for (int r = 0; r < P; ++r) {
     std::vector<int> fl = rx.folded_into(r);
     if (fl.empty()) continue;
-    std::vector<Src> s{Src{r, L_IN, 0}};
+    std::vector<Src> s{Src{r, L_IN, 0}};                 // own data first, then the folded ranks in receive order
     for (int q : fl) s.push_back(Src{q, L_IN, 0});
-    B.reduce(r, ACC, 0, sorted_sources(s), N, false);
+    B.reduce(r, ACC, 0, s, N, false);
     cur[r] = ACC;
   }
-  auto srange = [&](int r, int phase, int* lo, int* hi) {
-    int s = rx.step2rank(r);
-    int64_t pw = ipow(rx.k, phase);
-    *lo = (int)(s / pw * pw);
+  auto reversed = [&](int v) {                           // digit 0 becomes the most significant digit
+    int out = 0;
+    for (int i = 0; i < L; ++i) { out = out * K + v % K; v /= K; }
+    return out;
+  };
+  // blocks owned by rank r once the phases of digits 0 .. L-1-level are done
+  auto owned = [&](int r, int level, int* lo, int* hi) {
+    int64_t pw = ipow(K, level);
+    *lo = (int)(reversed(rx.step2rank(r)) / pw * pw);
     *hi = (int)(*lo + pw);
   };
-  for (int p = rx.log - 1; p >= 0; --p) {
+  for (int ph = 0; ph < L; ++ph) {
     std::vector<int> nxt = cur;
+    const bool last = ph == L - 1;
     for (int r = 0; r < P; ++r) {
       if (!rx.participates(r)) continue;
       int lo, hi;
-      srange(r, p, &lo, &hi);
-      bool last = (p == 0);
+      owned(r, L - 1 - ph, &lo, &hi);
       int d = last ? (int)L_OUT : ACC;
       std::vector<Src> s;
       bool acc = (cur[r] == ACC && d == ACC);
       if (!acc) s.push_back(Src{r, cur[r], off[lo]});
-      for (int q : rx.neighbours(r, p)) s.push_back(Src{q, cur[q], off[lo]});
+      for (int q : rx.neighbours(r, ph)) s.push_back(Src{q, cur[q], off[lo]});
       B.reduce(r, d, off[lo], s, off[hi] - off[lo], acc, last ? OPF_FINAL : 0);
       nxt[r] = d;
     }
     cur = nxt;
   }
-  if (rx.log == 0)
+  if (L == 0)
     for (int r = 0; r < P; ++r)
       if (rx.participates(r)) B.copy(r, L_OUT, 0, r, cur[r], 0, N);
-  for (int p = 0; p < rx.log; ++p)
+  for (int ph = L - 1; ph >= 0; --ph)
     for (int r = 0; r < P; ++r) {
       if (!rx.participates(r)) continue;
-      for (int q : rx.neighbours(r, p)) {
+      for (int q : rx.neighbours(r, ph)) {
         int lo, hi;
-        srange(q, p, &lo, &hi);
+        owned(q, L - 1 - ph, &lo, &hi);
         B.copy(r, L_OUT, off[lo], q, L_OUT, off[lo], off[hi] - off[lo]);
       }
     }
@@ -274,6 +287,14 @@ static Builder gen_ar_fullvec(int P, int64_t N, int k, int fold_mode, const char
   Cur cur(P, TA, TB);
   Recexch rx(P, k);
   int keff = rx.k, pofk = rx.p_of_k, log = rx.log;
+  if (fold_mode == 0) {
+    // recursive multiplying keeps the radix it is given, also beyond the number of ranks (everything then folds
+    // onto the ranks below k^log), allreduce_recursive_multiplying.cpp:9-12
+    keff = k;
+    pofk = 1;
+    log = 0;
+    while ((int64_t)pofk * k <= P) { pofk *= k; ++log; }
+  }
   auto participates = [&](int r) { return fold_mode == 0 ? r < pofk : rx.participates(r); };
   auto folded = [&](int r) {
     std::vector<int> v;
@@ -295,9 +316,14 @@ static Builder gen_ar_fullvec(int P, int64_t N, int k, int fold_mode, const char
     if (!participates(r)) continue;
     std::vector<int> fl = folded(r);
     if (fl.empty()) continue;
-    std::vector<Src> s{Src{r, L_IN, 0}};
+    // the reference adds the folded ranks' data in the order it receives them: recursive exchange starts from its
+    // own data (allreduce_recexch.cpp:283-296), recursive multiplying chains the senders in rank order and adds
+    // its own data last (allreduce_recursive_multiplying.cpp:57-76)
+    std::vector<Src> s;
+    if (fold_mode == 1) s.push_back(Src{r, L_IN, 0});
     for (int q : fl) s.push_back(Src{q, L_IN, 0});
-    B.reduce(r, TA, 0, sorted_sources(s), N, false);
+    if (fold_mode == 0) s.push_back(Src{r, L_IN, 0});
+    B.reduce(r, TA, 0, s, N, false);
     cur.buf[r] = TA;
   }
   for (int p = 0; p < log; ++p) {

@@ -253,3 +253,25 @@ def test_float_results_are_bit_identical_to_the_reference(ref_driver, P, b):
     assert np.allclose(forward, exact, rtol=1e-5) and flipped.shape == forward.shape
     if P >= 8:
         assert not np.array_equal(forward.view(np.uint32), backward.view(np.uint32))
+
+
+@pytest.mark.parametrize("name", sorted(n for n in MPICH if n != "ar_smp"))
+def test_mpich_style_baselines_are_bit_identical_on_floats(ref_mpich_driver, name):
+    """float32 inputs that do not add exactly: every MPICH-style baseline adds in the reference's order (phases,
+    neighbour order, fold order, block boundaries), so the sums agree bit for bit.  The SMP allreduce is left out:
+    its order is that of the MPI library's own MPI_Reduce / MPI_Allreduce, which MPI does not define."""
+    coll, algo, has_k = MPICH[name]
+    seed, n = 3, 3
+    for P in (2, 3, 4, 5, 6, 7, 8, 12):
+        nout = n * P if coll == "allreduce" else n
+        ins = [(((seed * 31 + q * 1009 + np.arange(n * P) * 7) % 97).astype(np.float32) / np.float32(7.0)
+                + np.float32(q) * np.float32(0.37)).astype(np.float32) for q in range(P)]
+        for k in ((2, 3, 4) if has_k else (2,)):
+            r = subprocess.run([str(ref_mpich_driver), name, str(P), str(k), str(n), str(seed), "float"],
+                               capture_output=True, text=True, timeout=120)
+            vals = [int(v) for v in r.stdout.split()]
+            assert vals and vals[0] == 0
+            ours = Program(coll, algo, P, n * P if coll == "allreduce" else n, k, 1).simulate(ins)
+            for q in range(P):
+                np.testing.assert_array_equal(ours[q].view(np.uint32), np.array(vals[1 + q * nout:1 + (q + 1) * nout], dtype=np.uint32),
+                                              err_msg=f"{name} P={P} k={k} rank {q}")

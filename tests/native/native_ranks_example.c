@@ -13,7 +13,7 @@
 #include "chb_compat.h"
 
 static int rank_main(const char* name, int rank, int world) {
-  const int n = 1 << 16;                      /* elements of the allreduce vector (a multiple of the ranks) */
+  const int n = (1 << 16) / world * world;    /* elements of the allreduce vector: a multiple of the ranks */
   if (cudaSetDevice(rank) != cudaSuccess) return 10;
   struct chb_bootstrap* boot = NULL;
   if (chb_bootstrap_create(name, rank, world, 60000, &boot)) return 11;

@@ -34,16 +34,19 @@ def test_sampler_reads_clocks_and_reasons(monkeypatch):
     with bench.ClockSampler(0) as cs:
         _first_sample(cs)
         t0 = time.perf_counter()
-        time.sleep(0.12)
+        n0 = len(cs.rows)
+        while len(cs.rows) < n0 + 3 and time.perf_counter() - t0 < 30:       # until samples fall into the window, however busy the machine
+            time.sleep(0.01)
         t1 = time.perf_counter()
         time.sleep(0.03)
     cs.mark(t0, t1)
     s = cs.summary()
     assert s["sm_mhz"] == 1342 and s["sm_max_mhz"] == 1965
     assert s["reasons"] == ["sw_power_cap", "sw_thermal_slowdown"]
-    assert s["sampled_during"] == "timed region" and 10 <= s["samples"] <= 80      # 120 ms at one sample per 2 ms (plus query time)
+    assert s["sampled_during"] == "timed region" and s["samples"] >= 1           # about 60 at one sample per 2 ms; no bound: the machine may be busy
     # a window shorter than the sampling period: the samples right before it are used, and the summary says so
-    cs.mark(t1 - 0.0001, t1 - 0.00005)
+    first = cs.rows[0][-1]
+    cs.mark(first - 1.0, first - 0.9)          # a window that cannot hold a sample
     s2 = cs.summary()
     assert s2["samples"] >= 1 and "warm-up" in s2["sampled_during"]
 

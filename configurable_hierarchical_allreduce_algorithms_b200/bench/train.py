@@ -16,6 +16,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import sys
 import time
 
 import torch
@@ -146,3 +147,7 @@ def main(argv=None):
 
 if __name__ == "__main__":
     main()
+    # results are written: skip the interpreter's teardown (see bench/driver.py)
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)

@@ -44,7 +44,9 @@ def _worker(rank, P, port, q):
     opt.step()
     if rank == 0:
         q.put((grads, {n: p.detach().clone().numpy() for n, p in model.named_parameters()}))   # plain arrays: no shared-memory handles
+    dist.barrier()                    # nobody tears its transport down while a peer is still communicating
     dist.destroy_process_group()
+    os._exit(0)                       # skip the interpreter's teardown: helper threads of the transport may still be alive
 
 
 def test_two_ranks_match_single_process():

@@ -56,6 +56,7 @@ def _worker(rank, P, port, cases, q):
             q.put(int(flag.item()))
     finally:
         dist.destroy_process_group()
+    os._exit(0)                       # skip the interpreter's teardown: helper threads of the transport may still be alive
 
 
 def _launch(P, cases):

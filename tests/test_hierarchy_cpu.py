@@ -65,6 +65,7 @@ def _worker(rank, P, L, port, q):
             q.put(int(flag.item()))
     finally:
         dist.destroy_process_group()
+    os._exit(0)                       # skip the interpreter's teardown: helper threads of the transport may still be alive
 
 
 @pytest.mark.parametrize("P,L", [(4, 2), (6, 3), (6, 2), (4, 1), (4, 4)])

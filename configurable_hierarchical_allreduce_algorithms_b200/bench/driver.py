@@ -253,8 +253,10 @@ def main(argv=None):
 
 if __name__ == "__main__":
     main()
-    # leave without the interpreter's teardown: on a busy machine the transport's helper threads can still be
-    # alive when static destructors run, which ends a rank that has already written everything with SIGABRT
-    sys.stdout.flush()
-    sys.stderr.flush()
-    os._exit(0)
+    if not torch.cuda.is_available():
+        # CPU ranks leave without the interpreter's teardown: on a busy machine gloo's helper threads can still be
+        # alive when static destructors run, which ends a rank that has already written everything with SIGABRT.
+        # GPU ranks take the normal way out, so that mapped peer memory is released in order.
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)

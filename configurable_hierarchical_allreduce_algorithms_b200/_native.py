@@ -49,6 +49,8 @@ def _declare(L: C.CDLL) -> None:
     L.chb_program_simulate.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(vp), u64, cp, i32]
     L.chb_program_run_threads.restype = i32
     L.chb_program_run_threads.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(vp), i32, C.POINTER(C.c_double)]
+    L.chb_program_run_threads_late.restype = i32
+    L.chb_program_run_threads_late.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(vp), i32, i32]
     L.chb_program_export.restype = i32
     L.chb_program_export.argtypes = [vp, vp, vp, vp, vp, vp]
     L.chb_list_algorithms.restype = i32

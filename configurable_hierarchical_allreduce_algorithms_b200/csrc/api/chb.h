@@ -65,6 +65,10 @@ int chb_program_simulate(const chb_program_t* p, int dtype, int op, void* const*
 /* run all ranks as host threads (real concurrency); mean wall seconds per repetition in *seconds */
 int chb_program_run_threads(const chb_program_t* p, int dtype, int op, void* const* in, void* const* out,
                             int iters, double* seconds);
+/* the same, once, with rank late_rank entering delay_ms late; until it enters, its input holds poison
+ * (checks that no peer reads a directly pulled input before its owner has entered the collective) */
+int chb_program_run_threads_late(const chb_program_t* p, int dtype, int op, void* const* in, void* const* out,
+                                 int late_rank, int delay_ms);
 /* Flat export (all int64):
  *   ops        [NOPS][8]        rank, round, dst_buf, dst_off, count, acc, src_begin, nsrc
  *   srcs       [NSRCS][3]       peer, buf, off

@@ -1,6 +1,7 @@
 // One-call collectives on a communicator (program cache + dispatch to the
 // interpreter, flagged-line or multimem kernels) and the reference-compatible
 // entry points declared in chb_compat.h.
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -18,6 +19,9 @@ extern "C" {
 void chb_program_release(chb_comm* c, const chb_program* p);
 int chb_run_program(chb_comm* c, const chb_program* p, int dtype, int op, const void* const* in,
                     void* const* out, float scale, int nctas, cudaStream_t stream);
+int chb_run_program_ll(chb_comm* c, const chb_program* p, int dtype, int op, const void* const* in,
+                       void* const* out, float scale, int nctas, cudaStream_t stream);
+long long chb_program_ll_lines(const chb_program* p, int esz);
 int chb_ll_collective(chb_comm* c, int mode, int dtype, int op, const void* const* in, void* const* out,
                       long long count, float scale, int nctas, cudaStream_t stream);
 long long chb_ll_max_bytes(const chb_comm* c);
@@ -146,6 +150,24 @@ int chb_collective(chb_comm* c, int coll, const char* algo, int k, int b, int au
     if (mode < 0) return CHB_ERR_UNSUPPORTED;
     return chb_nvls_collective(c, mode, dtype, in[0], out[0], count, scale, nctas, stream);
   }
+  // "<name>:ll" / "<name>:pull" pin the way a step program is executed; without a suffix, collectives in
+  // which every rank depends on every rank run with flagged lines up to CHB_LL_PROGRAM_MAX bytes
+  // (default 512 KiB of payload, if the messages fit the inbox) and with the pull interpreter above that.
+  std::string name(algo);
+  int mode = 0;                                   // 0 auto, 1 flagged lines, 2 pull
+  {
+    const size_t colon = name.find(':');
+    if (colon != std::string::npos) {
+      const std::string m = name.substr(colon + 1);
+      name.resize(colon);
+      if (m == "ll") mode = 1;
+      else if (m == "pull") mode = 2;
+      else { c->last_error = "unknown execution mode '" + m + "' (ll | pull)"; return CHB_ERR_ARG; }
+    }
+  }
+  algo = name.c_str();
+  const bool ll_kind = coll == CHB_ALLREDUCE || coll == CHB_REDUCE_SCATTER || coll == CHB_ALLGATHER;
+  if (mode == 1 && !ll_kind) { c->last_error = "flagged-line execution covers allreduce, reduce-scatter and allgather"; return CHB_ERR_UNSUPPORTED; }
   // In place means in == out, except for the allgather, whose in-place form is
   // "my block already sits at its slot of the output" (in == out + rank * block):
   // that needs no staging, the self copy is a no-op.
@@ -164,6 +186,24 @@ int chb_collective(chb_comm* c, int coll, const char* algo, int k, int b, int au
   // peers cannot address them as "my input pointer, your heap": stage them
   if (ag_alias) flags &= ~1;
   chb_program* p = nullptr;
+  if (mode != 2 && ll_kind && c->P > 1) {
+    static const long long ll_max = [] {
+      const char* e = std::getenv("CHB_LL_PROGRAM_MAX");
+      return e ? std::atoll(e) : (512ll << 10);
+    }();
+    const int esz = chb_dtype_size(dtype);
+    const long long payload = (long long)count * esz * (coll == CHB_ALLREDUCE ? 1 : c->P);
+    if (mode == 1 || payload <= ll_max) {
+      // owners push, nobody reads a peer's buffers: lowered without staging whatever the buffers are
+      const int ll_flags = 3 | (in_place ? 4 : 0);
+      int rc = get_program(c, coll, algo, k, b, aux, count, ll_flags, &p);
+      if (rc) return rc;
+      const long long need = chb_program_ll_lines(p, esz);
+      if (need <= (long long)c->P * (long long)c->ll_lines_per_src)
+        return chb_run_program_ll(c, p, dtype, op, in, out, scale, nctas, stream);
+      if (mode == 1) { c->last_error = "messages of this program exceed the flagged-line inbox"; return CHB_ERR_COUNT; }
+    }
+  }
   int rc = get_program(c, coll, algo, k, b, aux, count, flags, &p);
   if (rc) return rc;
   return chb_run_program(c, p, dtype, op, in, out, scale, nctas, stream);

@@ -121,6 +121,13 @@ int chb_program_run_threads(const chb_program_t* p, int dtype, int op, void* con
   return rc == 0 ? CHB_SUCCESS : (rc == -1 ? CHB_ERR_TIMEOUT : CHB_ERR_ARG);
 }
 
+int chb_program_run_threads_late(const chb_program_t* p, int dtype, int op, void* const* in, void* const* out,
+                                 int late_rank, int delay_ms) {
+  if (!p || !in || !out || late_rank < 0 || late_rank >= p->prog.P) return CHB_ERR_ARG;
+  int rc = chb::run_threads(p->prog, dtype, op, in, out, 1, nullptr, late_rank, delay_ms);
+  return rc == 0 ? CHB_SUCCESS : (rc == -1 ? CHB_ERR_TIMEOUT : CHB_ERR_ARG);
+}
+
 int chb_program_export(const chb_program_t* p, int64_t* ops, int64_t* srcs, int64_t* waits,
                        int64_t* exit_waits, int64_t* signals) {
   if (!p) return CHB_ERR_ARG;

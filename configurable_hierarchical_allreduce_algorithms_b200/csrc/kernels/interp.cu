@@ -129,13 +129,21 @@ static std::vector<char> make_blob(const Program& p) {
   return blob;
 }
 
-// ------------------------------------------------------------------ one step
+// ------------------------------------------------------------------ one step (or one tile of it)
+// Elements [e0, e0 + cnt) of step `st`, strided over `nparts` CTAs of which this one is `part`.
+// Sources are combined left to right (the order in which the reference receives and reduces), but
+// their loads are issued kSrcGroup sources at a time, so that a step with k-1 or P-1 remote sources
+// keeps that many NVLink round trips in flight per thread instead of one.
+constexpr int kSrcGroup = 4;
+
 template <typename T>
 __device__ __forceinline__ void run_step(const DevStep& st, const DevSrc* __restrict__ srcs, const World& w,
-                                         const IoTable& io, int rank, unsigned part, unsigned nparts,
+                                         const IoTable& io, int rank, long long e0, long long cnt,
+                                         unsigned part, unsigned nparts,
                                          int op, float scale, const char** s_ptr, int* s_meta, const long long* limit) {
   using Acc = typename Elem<T>::Acc;
   constexpr int VE = Elem<T>::kPerVec;
+  constexpr int G = kSrcGroup;
   const int tid = threadIdx.x;
   const bool acc = (st.flags & 0x100u) != 0;
   const int nsrc = st.nsrc + (acc ? 1 : 0);
@@ -143,20 +151,20 @@ __device__ __forceinline__ void run_step(const DevStep& st, const DevSrc* __rest
   if (tid < nsrc || tid == kMaxSrc) {
     if (tid == kMaxSrc) {
       char* base = st.dst_buf == 0 ? const_cast<char*>(io.in[rank]) : (st.dst_buf == 1 ? io.out[rank] : w.work[rank]);
-      s_ptr[kMaxSrc] = base + st.dst_off * (long long)sizeof(T);
+      s_ptr[kMaxSrc] = base + (st.dst_off + e0) * (long long)sizeof(T);
     } else if (acc && tid == 0) {
       char* base = st.dst_buf == 1 ? io.out[rank] : w.work[rank];
-      s_ptr[0] = base + st.dst_off * (long long)sizeof(T);
+      s_ptr[0] = base + (st.dst_off + e0) * (long long)sizeof(T);
     } else {
       const DevSrc s = srcs[st.src_begin + tid - (acc ? 1 : 0)];
       const char* base = s.buf == 0 ? io.in[s.peer] : (s.buf == 1 ? io.out[s.peer] : w.work[s.peer]);
-      s_ptr[tid] = base + s.off * (long long)sizeof(T);
+      s_ptr[tid] = base + (s.off + e0) * (long long)sizeof(T);
     }
   }
 #ifdef CHB_CHECK_BOUNDS
   // checked build: the same range test as on the host, on the values the kernel actually uses
   if (tid == 0) {
-    bool ok = st.dst_off >= 0 && st.dst_off + st.count <= limit[st.dst_buf];
+    bool ok = e0 >= 0 && cnt >= 0 && e0 + cnt <= st.count && st.dst_off >= 0 && st.dst_off + st.count <= limit[st.dst_buf];
     for (int j = 0; j < st.nsrc; ++j) {
       const DevSrc s = srcs[st.src_begin + j];
       ok = ok && s.off >= 0 && s.off + st.count <= limit[s.buf] && s.peer >= 0 && s.peer < w.P;
@@ -178,11 +186,11 @@ __device__ __forceinline__ void run_step(const DevStep& st, const DevSrc* __rest
   const bool aligned = align_level != 0;
   char* dst = const_cast<char*>(s_ptr[kMaxSrc]);
   const bool do_scale = (st.flags & OPF_FINAL) && scale != 1.0f;
-  const long long count = st.count;
+  const long long count = cnt;
   const long long nvec = aligned ? count / VE : 0;
   const long long TT = (long long)nparts * blockDim.x;
   const long long g = (long long)part * blockDim.x + tid;
-  constexpr int U = 4;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
   long long i0 = g;
   if (align_level == 2) {
     // 256-bit accesses on pairs of vectors; a last odd vector is left to the 128-bit loop
@@ -204,65 +212,75 @@ __device__ __forceinline__ void run_step(const DevStep& st, const DevSrc* __rest
         d += UC * stride;
       }
     }
-    constexpr int UW = U / 2;
+    constexpr int UW = 1;
     for (; j0 < nw; j0 += TT * UW) {
-      Acc a[U][VE];
-      {
-        uint4 v[U];
+      Acc a[UW][2][VE];
+      for (int s = 0; s < nsrc; s += G) {
+        uint4 x[G][UW][2];
 #pragma unroll
-        for (int u = 0; u < UW; ++u) {
-          const long long j = j0 + (long long)u * TT;
-          if (j < nw) ld32_cg(s_ptr[0] + j * 32, v[2 * u], v[2 * u + 1]);
-          else v[2 * u] = v[2 * u + 1] = make_uint4(0u, 0u, 0u, 0u);
+        for (int gi = 0; gi < G; ++gi) {
+          if (s + gi < nsrc) {
+            const char* p0 = s_ptr[s + gi];
+#pragma unroll
+            for (int u = 0; u < UW; ++u) {
+              const long long j = j0 + (long long)u * TT;
+              if (j < nw) ld32_cg(p0 + j * 32, x[gi][u][0], x[gi][u][1]);
+              else x[gi][u][0] = x[gi][u][1] = zero;
+            }
+          }
         }
 #pragma unroll
-        for (int u = 0; u < U; ++u) vec_to_acc<T>(v[u], a[u]);
-      }
-      for (int s = 1; s < nsrc; ++s) {
-        uint4 x[U];
-        const char* p0 = s_ptr[s];
+        for (int gi = 0; gi < G; ++gi) {
+          if (s + gi < nsrc) {
+            if (gi == 0 && s == 0) {
 #pragma unroll
-        for (int u = 0; u < UW; ++u) {
-          const long long j = j0 + (long long)u * TT;
-          if (j < nw) ld32_cg(p0 + j * 32, x[2 * u], x[2 * u + 1]);
-          else x[2 * u] = x[2 * u + 1] = make_uint4(0u, 0u, 0u, 0u);
+              for (int u = 0; u < UW; ++u) { vec_to_acc<T>(x[0][u][0], a[u][0]); vec_to_acc<T>(x[0][u][1], a[u][1]); }
+            } else {
+#pragma unroll
+              for (int u = 0; u < UW; ++u) { vec_combine<T>(op, x[gi][u][0], a[u][0]); vec_combine<T>(op, x[gi][u][1], a[u][1]); }
+            }
+          }
         }
-#pragma unroll
-        for (int u = 0; u < U; ++u) vec_combine<T>(op, x[u], a[u]);
       }
 #pragma unroll
       for (int u = 0; u < UW; ++u) {
         const long long j = j0 + (long long)u * TT;
         if (j < nw) {
-          if (do_scale) { acc_scale<T>(a[2 * u], scale); acc_scale<T>(a[2 * u + 1], scale); }
-          st32(dst + j * 32, acc_to_vec<T>(a[2 * u]), acc_to_vec<T>(a[2 * u + 1]));
+          if (do_scale) { acc_scale<T>(a[u][0], scale); acc_scale<T>(a[u][1], scale); }
+          st32(dst + j * 32, acc_to_vec<T>(a[u][0]), acc_to_vec<T>(a[u][1]));
         }
       }
     }
     i0 = nw * 2 + g;
   }
+  constexpr int U = 2;
   for (; i0 < nvec; i0 += TT * U) {
     Acc a[U][VE];
-    {
-      uint4 v[U];
+    for (int s = 0; s < nsrc; s += G) {
+      uint4 x[G][U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const long long i = i0 + (long long)u * TT;
-        v[u] = (i < nvec) ? ld16_cg(s_ptr[0] + i * 16) : make_uint4(0u, 0u, 0u, 0u);
+      for (int gi = 0; gi < G; ++gi) {
+        if (s + gi < nsrc) {
+          const char* p0 = s_ptr[s + gi];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const long long i = i0 + (long long)u * TT;
+            x[gi][u] = (i < nvec) ? ld16_cg(p0 + i * 16) : zero;
+          }
+        }
       }
 #pragma unroll
-      for (int u = 0; u < U; ++u) vec_to_acc<T>(v[u], a[u]);
-    }
-    for (int s = 1; s < nsrc; ++s) {
-      uint4 x[U];
-      const char* p0 = s_ptr[s];
+      for (int gi = 0; gi < G; ++gi) {
+        if (s + gi < nsrc) {
+          if (gi == 0 && s == 0) {
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const long long i = i0 + (long long)u * TT;
-        x[u] = (i < nvec) ? ld16_cg(p0 + i * 16) : make_uint4(0u, 0u, 0u, 0u);
+            for (int u = 0; u < U; ++u) vec_to_acc<T>(x[0][u], a[u]);
+          } else {
+#pragma unroll
+            for (int u = 0; u < U; ++u) vec_combine<T>(op, x[gi][u], a[u]);
+          }
+        }
       }
-#pragma unroll
-      for (int u = 0; u < U; ++u) vec_combine<T>(op, x[u], a[u]);
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -284,6 +302,17 @@ __device__ __forceinline__ void run_step(const DevStep& st, const DevSrc* __rest
 }
 
 // ------------------------------------------------------------------ the kernel
+// Large steps of one round are independent of each other.  They are cut into tiles and the tiles are
+// dealt to the CTAs row by row: tile j of every large step, then tile j + 1 of every large step, with
+// the step order rotated by the rank.  All sources of a round are therefore pulled at the same time
+// (the k-1 neighbour exchanges and the lanes of one round run concurrently, where the reference posts
+// them one after the other: testing/custom_implementations/work_dir/all_reduce/all_reduce_radix_batch.cpp:343-364),
+// and at any moment the P readers of one round are spread over P different owners instead of all
+// reading from the owner that comes first in the schedule.
+constexpr int kMaxBig = 64;                       // large steps per round handled by the tile scheduler
+constexpr long long kTileGrain = 16 << 10;        // tiles are multiples of this (keeps 32-byte alignment for every type)
+constexpr long long kTileMin = 64 << 10, kTileMax = 512 << 10;
+
 template <typename T>
 __global__ void __launch_bounds__(kInterpThreads, 1)
 interp_kernel(World w, const char* __restrict__ blob, IoTable io, int op, float scale) {
@@ -303,7 +332,9 @@ interp_kernel(World w, const char* __restrict__ blob, IoTable io, int op, float 
   __shared__ unsigned long long s_base;
   __shared__ int s_ok;
   __shared__ const char* s_ptr[kMaxSrc + 1];
-  __shared__ int s_meta[2];
+  __shared__ int s_meta[4];
+  __shared__ int s_big[kMaxBig];
+  __shared__ long long s_tile;
   if (tid == 0) {
     s_base = ld_volatile_u64(&c->epoch);
     s_ok = ld_volatile_u32(&c->abort) ? 0 : 1;
@@ -330,52 +361,63 @@ interp_kernel(World w, const char* __restrict__ blob, IoTable io, int op, float 
     if (!ok) break;
     unsigned long long* tr = w.trace[rank];
     if (tr && cta == 0 && tid == 0 && t < w.trace_rounds) tr[2 * t] = globaltimer_ns();   // waits of round t satisfied
-    // Large steps of one round are independent of each other.  When a round has
-    // both steps that pull from peers (NVLink bound) and steps that only touch
-    // local memory (HBM bound, e.g. the copy of the own block), the CTAs split
-    // into two groups sized by cost, one per kind, so the two overlap; inside a
-    // group the steps still run one after the other on all of the group's CTAs,
-    // which keeps the load balanced.
-    if (tid == 0) {
-      float wr = 0.f, wl = 0.f;
-      for (int s = R.step_begin; s < R.step_end; ++s) {
-        const DevStep st = steps[s];
-        if (st.count * (long long)sizeof(T) < kSmallStepBytes) continue;
-        bool remote = false;
-        float wgt = 1.f;                                    // the store
-        for (int j = 0; j < st.nsrc; ++j) {
-          const bool rj = srcs[st.src_begin + j].peer != rank;
-          remote |= rj;
-          wgt += rj ? 8.f : 1.f;
+    const int nst = R.step_end - R.step_begin;
+    if (nst > 0) {
+      if (tid == 0) {
+        int nb = 0;
+        long long maxc = 0, tot = 0;
+        for (int s = R.step_begin; s < R.step_end; ++s) {
+          const long long cnt = steps[s].count;
+          if (cnt * (long long)sizeof(T) < kSmallStepBytes) continue;
+          if (nb < kMaxBig) s_big[nb] = s;
+          ++nb;
+          maxc = cnt > maxc ? cnt : maxc;
+          tot += cnt;
         }
-        (remote ? wr : wl) += wgt * (float)st.count;
+        // about four tiles per CTA and round: enough for balance, few enough to keep the set-up cost per tile small
+        long long tb = tot * (long long)sizeof(T) / ((long long)nct * 4);
+        tb = tb < kTileMin ? kTileMin : (tb > kTileMax ? kTileMax : tb);
+        tb = tb / kTileGrain * kTileGrain;
+        const long long te = tb / (long long)sizeof(T);
+        s_tile = te;
+        s_meta[1] = nb;
+        s_meta[2] = (int)((maxc + te - 1) / te);
       }
-      int na = 0;                                           // CTAs of the remote group; 0 = no split
-      if (wr > 0.f && wl > 0.f && nct >= 2) {
-        na = (int)(wr / (wr + wl) * (float)nct + 0.5f);
-        na = na < 1 ? 1 : (na > (int)nct - 1 ? (int)nct - 1 : na);
+      __syncthreads();
+      const int nb = s_meta[1], nsmall = nst - nb;
+      const long long te = s_tile;
+      const long long nitems = (long long)nsmall + (long long)s_meta[2] * nb;
+      // work items of this round: the small steps (one CTA each), then the tiles of the large steps
+      for (long long v = cta; v < nitems; v += nct) {
+        int sidx = -1;
+        long long e0 = 0;
+        if (v < nsmall) {
+          long long seen = 0;
+          for (int s = R.step_begin; s < R.step_end; ++s)
+            if (steps[s].count * (long long)sizeof(T) < kSmallStepBytes && seen++ == v) { sidx = s; break; }
+        } else {
+          const long long u = v - nsmall;
+          const int bi = (int)((u % nb + rank) % nb);
+          e0 = (u / nb) * te;
+          if (nb <= kMaxBig) {
+            sidx = s_big[bi];
+          } else {   // more large steps than the table holds: find the bi-th one by walking the round
+            int seen = 0;
+            for (int s = R.step_begin; s < R.step_end; ++s)
+              if (steps[s].count * (long long)sizeof(T) >= kSmallStepBytes && seen++ == bi) { sidx = s; break; }
+          }
+        }
+        if (sidx < 0) continue;
+        const DevStep st = steps[sidx];
+        if (e0 >= st.count) continue;
+        long long cnt = st.count - e0;
+        if (v >= nsmall && cnt > te) cnt = te;
+        run_step<T>(st, srcs, w, io, rank, e0, cnt, 0u, 1u, op, scale, s_ptr, s_meta, h->limit);
       }
-      s_meta[1] = na;
+      ok = rank_barrier(c, nct, gen, w.timeout_ns, rank, t);
+      if (!ok) break;
     }
-    __syncthreads();
-    const unsigned na = (unsigned)s_meta[1];
-    for (int s = R.step_begin; s < R.step_end; ++s) {
-      const DevStep st = steps[s];
-      const bool small = st.count * (long long)sizeof(T) < kSmallStepBytes;
-      if (small) {
-        if ((unsigned)(s - R.step_begin) % nct == cta)
-          run_step<T>(st, srcs, w, io, rank, 0u, 1u, op, scale, s_ptr, s_meta, h->limit);
-      } else if (na == 0) {
-        run_step<T>(st, srcs, w, io, rank, cta, nct, op, scale, s_ptr, s_meta, h->limit);
-      } else {
-        bool remote = false;
-        for (int j = 0; j < st.nsrc; ++j) remote |= (srcs[st.src_begin + j].peer != rank);
-        if (remote && cta < na) run_step<T>(st, srcs, w, io, rank, cta, na, op, scale, s_ptr, s_meta, h->limit);
-        if (!remote && cta >= na) run_step<T>(st, srcs, w, io, rank, cta - na, nct - na, op, scale, s_ptr, s_meta, h->limit);
-      }
-    }
-    ok = rank_barrier(c, nct, gen, w.timeout_ns, rank, t);
-    if (!ok) break;
+    // (a round without steps only announces that this rank has entered: nothing to wait for)
     if (tr && cta == 0 && tid == 0 && t < w.trace_rounds) tr[2 * t + 1] = globaltimer_ns();  // round t complete on this rank
     if (cta == 0) {
       const int n = R.sig_end - R.sig_begin;
@@ -478,6 +520,10 @@ void chb_program_release(chb_comm* c, const chb_program* p) {
   if (!p) return;
   auto it = c->blobs.find(p->uid);
   if (it != c->blobs.end()) { cudaFree(it->second); c->blobs.erase(it); }
+  for (auto jt = c->ll_blobs.lower_bound(p->uid * 16u); jt != c->ll_blobs.end() && jt->first < (p->uid + 1) * 16u;) {
+    cudaFree(jt->second.first);
+    jt = c->ll_blobs.erase(jt);
+  }
 }
 
 // Launch a compiled program.  in / out hold one pointer per local rank

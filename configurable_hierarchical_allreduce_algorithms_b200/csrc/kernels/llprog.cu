@@ -1,0 +1,334 @@
+// Step programs executed with flagged lines: the latency-bound way to run ANY schedule.
+//
+// The pull interpreter (interp.cu) pays, per round, a grid barrier, a release
+// store, an acquire poll and a load round trip over NVLink.  Here every remote
+// source of a step becomes a message that its OWNER pushes, as 16-byte lines
+// {data, flag, data, flag}, into a slot of the reader's inbox reserved for that
+// (step, source) pair; the reader polls its own memory until the line carries
+// the flag of this launch.  A round then costs one NVLink traversal and no
+// cross-GPU barrier, whatever the algorithm: the radix-k / group-b shapes, the
+// recursive-doubling and Rabenseifner baselines and the rest can be compared in
+// the regime where the number of rounds decides (the regime of the reference's
+// published wins, testing/plots/all_reduce/results_custom_polaris.csv).
+//
+// Level t of a rank (t = round of the lowered program):
+//   1. push: every region of mine that a peer's step of level t reads goes to
+//      that peer's inbox.  It was written by my own steps of levels < t.
+//   2. execute my steps of level t: local sources are loaded, remote ones are
+//      polled in the inbox, combined left to right, stored once.
+// Steps of one level never conflict (the lowering guarantees it), so 1 and 2 of
+// the same level need no ordering; levels are separated by a rank-local barrier.
+// Owners push from inside their own launch, so an input is never read before
+// its owner's stream has produced it, and nobody reads a peer's buffers: no
+// entry handshake, no exit waits, no staging of caller buffers.
+//
+// Flags are launch sequence numbers shared with the one-shot kernels (ll.cu);
+// the two inbox halves alternate by launch parity.  That is sound for
+// collectives in which every rank's result depends on every rank's input
+// (allreduce, reduce-scatter, allgather): a rank can finish launch n only after
+// every peer has entered launch n, so nobody is ever two launches ahead.
+#include <algorithm>
+#include <cstring>
+#include <vector>
+
+#include "../api/chb.h"
+#include "../api/program_handle.h"
+#include "../symm/comm.h"
+#include "common.cuh"
+#include "ll_lines.cuh"
+
+namespace chb {
+
+constexpr int kLPThreads = 512;
+
+struct LPLevel { int step_begin, step_end, send_begin, send_end; long long step_lines, send_lines; };
+struct LPStep { long long dst_off, count, line_prefix; int dst_buf, nsrc, src_begin; unsigned flags; };
+struct LPSrc { long long off, inbox_line; int peer, buf; };          // inbox_line < 0: local source
+struct LPSend { long long src_off, count, inbox_line, line_prefix; int dst_rank, src_buf; };
+struct LPHeader {
+  int P, nlevels, nsteps, nsrcs, nsends, esz;
+  long long off_levels, off_steps, off_srcs, off_sends;
+  long long max_level_lines;     // busiest (rank, level): lines pushed + lines executed
+  long long inbox_lines;         // lines needed in the fullest inbox
+};
+
+struct LPIo {
+  const char* in[kMaxRanks];
+  char* out[kMaxRanks];
+};
+
+static long long lines_of(long long count, int esz) { return (count * esz + 7) / 8; }
+
+// Flatten a lowered program into the level tables above for elements of `esz` bytes.
+static std::vector<char> make_ll_blob(const Program& p, int esz, LPHeader* hout) {
+  const int P = p.P, T = p.nrounds;
+  std::vector<LPLevel> levels((size_t)P * T);
+  std::vector<LPStep> steps;
+  std::vector<LPSrc> srcs;
+  std::vector<std::vector<LPSend>> sends_of((size_t)P * T);
+  std::vector<long long> inbox(P, 0);
+  LPHeader h{};
+  // steps in (rank, level) order; every remote source gets its inbox slot and its owner a send
+  for (int r = 0; r < P; ++r)
+    for (int t = 0; t < T; ++t) {
+      LPLevel& lv = levels[(size_t)r * T + t];
+      lv.step_begin = (int)steps.size();
+      long long pre = 0;
+      for (int oi : p.rr[r][t].ops) {
+        const Op& o = p.ops[oi];
+        LPStep s{};
+        s.dst_off = o.dst_off;
+        s.count = o.count;
+        s.dst_buf = o.dst_buf;
+        s.flags = o.flags | (o.acc ? 0x100u : 0u);
+        s.src_begin = (int)srcs.size();
+        s.nsrc = (int)o.srcs.size();
+        s.line_prefix = pre;
+        const long long nl = lines_of(o.count, esz);
+        pre += nl;
+        for (const Src& x : o.srcs) {
+          LPSrc d{x.off, -1, x.peer, x.buf};
+          if (x.peer != r) {
+            d.inbox_line = inbox[r];
+            inbox[r] += nl;
+            sends_of[(size_t)x.peer * T + t].push_back(LPSend{x.off, o.count, d.inbox_line, 0, r, x.buf});
+          }
+          srcs.push_back(d);
+        }
+        steps.push_back(s);
+      }
+      lv.step_end = (int)steps.size();
+      lv.step_lines = pre;
+    }
+  std::vector<LPSend> sends;
+  for (int r = 0; r < P; ++r)
+    for (int t = 0; t < T; ++t) {
+      LPLevel& lv = levels[(size_t)r * T + t];
+      lv.send_begin = (int)sends.size();
+      long long pre = 0;
+      for (LPSend s : sends_of[(size_t)r * T + t]) {
+        s.line_prefix = pre;
+        pre += lines_of(s.count, esz);
+        sends.push_back(s);
+      }
+      lv.send_end = (int)sends.size();
+      lv.send_lines = pre;
+      h.max_level_lines = std::max(h.max_level_lines, lv.send_lines + lv.step_lines);
+    }
+  h.P = P;
+  h.nlevels = T;
+  h.nsteps = (int)steps.size();
+  h.nsrcs = (int)srcs.size();
+  h.nsends = (int)sends.size();
+  h.esz = esz;
+  for (int r = 0; r < P; ++r) h.inbox_lines = std::max(h.inbox_lines, inbox[r]);
+  auto al = [](size_t x) { return (x + 15) / 16 * 16; };
+  size_t off = al(sizeof(LPHeader));
+  h.off_levels = (long long)off; off = al(off + levels.size() * sizeof(LPLevel));
+  h.off_steps = (long long)off;  off = al(off + steps.size() * sizeof(LPStep));
+  h.off_srcs = (long long)off;   off = al(off + srcs.size() * sizeof(LPSrc));
+  h.off_sends = (long long)off;  off = al(off + sends.size() * sizeof(LPSend));
+  std::vector<char> blob(off, 0);
+  std::memcpy(blob.data(), &h, sizeof(h));
+  auto put = [&](long long o, const void* src, size_t n) { if (n) std::memcpy(blob.data() + o, src, n); };
+  put(h.off_levels, levels.data(), levels.size() * sizeof(LPLevel));
+  put(h.off_steps, steps.data(), steps.size() * sizeof(LPStep));
+  put(h.off_srcs, srcs.data(), srcs.size() * sizeof(LPSrc));
+  put(h.off_sends, sends.data(), sends.size() * sizeof(LPSend));
+  *hout = h;
+  return blob;
+}
+
+// Index of the item in [begin, end) whose line range holds global line gl (prefixes ascend from 0).
+template <typename Item>
+__device__ __forceinline__ int find_item(const Item* items, int begin, int end, long long gl) {
+  int lo = begin, hi = end - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (items[mid].line_prefix <= gl) lo = mid;
+    else hi = mid - 1;
+  }
+  return lo;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kLPThreads, 1)
+llprog_kernel(World w, const char* __restrict__ blob, LPIo io, int op, float scale, long long lines_per_src) {
+  using Acc = typename Elem<T>::Acc;
+  constexpr int PE = (int)(8 / sizeof(T));     // elements per line
+  const int rank = w.rank0 + (int)blockIdx.y;
+  const unsigned nct = gridDim.x;
+  Ctrl* c = w.ctrl[rank];
+  const LPHeader* h = reinterpret_cast<const LPHeader*>(blob);
+  const int nlevels = h->nlevels;
+  const LPLevel* levels = reinterpret_cast<const LPLevel*>(blob + h->off_levels) + (size_t)rank * nlevels;
+  const LPStep* steps = reinterpret_cast<const LPStep*>(blob + h->off_steps);
+  const LPSrc* srcs = reinterpret_cast<const LPSrc*>(blob + h->off_srcs);
+  const LPSend* sends = reinterpret_cast<const LPSend*>(blob + h->off_sends);
+  __shared__ unsigned long long s_seq;
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) { s_seq = ld_volatile_u64(&c->ll_seq); s_abort = ld_volatile_u32(&c->abort); }
+  __syncthreads();
+  const unsigned long long seq = s_seq;
+  bool ok = s_abort == 0;
+  const unsigned flag = (unsigned)(seq % 0xFFFFFFFFull) + 1u;
+  const long long half = (long long)(seq & 1ull) * w.P * lines_per_src;
+  const long long TT = (long long)nct * blockDim.x;
+  const long long gtid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool do_scale = scale != 1.0f;
+  const char* my_in = io.in[rank];
+  char* my_out = io.out[rank];
+  char* my_work = w.work[rank];
+  const char* inbox = w.ll[rank] + half * 16;
+  unsigned gen = 0;
+
+  for (int t = 0; t < nlevels && ok; ++t) {
+    const LPLevel L = levels[t];
+    // ---- 1. push what peers' steps of this level read from me
+    for (long long gl = gtid; gl < L.send_lines; gl += TT) {
+      const LPSend S = sends[find_item(sends, L.send_begin, L.send_end, gl)];
+      const long long l = gl - S.line_prefix;
+      const char* base = (S.src_buf == 0 ? my_in : (S.src_buf == 1 ? my_out : my_work)) + S.src_off * (long long)sizeof(T);
+      const uint2 v = load_payload(base, l * 8, S.count * (long long)sizeof(T));
+      st_line(w.ll[S.dst_rank] + (half + S.inbox_line + l) * 16, v.x, v.y, flag);
+    }
+    // ---- 2. my steps of this level
+    bool failed = false;
+    for (long long gl = gtid; gl < L.step_lines && !failed; gl += TT) {
+      const LPStep st = steps[find_item(steps, L.step_begin, L.step_end, gl)];
+      const long long l = gl - st.line_prefix;
+      const long long nbytes = st.count * (long long)sizeof(T);
+      char* dst = (st.dst_buf == 1 ? my_out : my_work) + st.dst_off * (long long)sizeof(T);
+      const bool acc = (st.flags & 0x100u) != 0;
+      Acc a[PE];
+      uint2 v = make_uint2(0u, 0u);
+      bool have = false;
+      if (acc) { payload_to_acc<T>(load_payload(dst, l * 8, nbytes), a); have = true; }
+      for (int j = 0; j < st.nsrc; ++j) {
+        const LPSrc s = srcs[st.src_begin + j];
+        if (s.inbox_line < 0) {
+          const char* base = (s.buf == 0 ? my_in : (s.buf == 1 ? my_out : my_work)) + s.off * (long long)sizeof(T);
+          v = load_payload(base, l * 8, nbytes);
+        } else if (!poll_line(inbox + (s.inbox_line + l) * 16, flag, v, c, w.timeout_ns, rank, l, s.peer)) {
+          failed = true;
+          break;
+        }
+        if (!have) { payload_to_acc<T>(v, a); have = true; }
+        else payload_combine<T>(op, v, a);
+      }
+      if (failed) break;
+      // a plain copy keeps the payload's bits; everything else goes through the accumulator type
+      if (acc || st.nsrc > 1 || (do_scale && (st.flags & OPF_FINAL)))
+        v = acc_to_payload<T>(a, scale, do_scale && (st.flags & OPF_FINAL));
+      store_payload(dst, l * 8, nbytes, v);
+    }
+    // ---- levels are ordered on this rank; a failed wait ends the launch for all its CTAs
+    if (t + 1 < nlevels) ok = rank_barrier(c, nct, gen, w.timeout_ns, rank, t);
+  }
+  rank_exit(c, nct, [&](Ctrl* cc) { cc->ll_seq = seq + 1ull; });
+}
+
+typedef void (*LPFn)(World, const char*, LPIo, int, float, long long);
+static LPFn pick_lp(int dtype) {
+  switch (dtype) {
+    case DT_F32: return llprog_kernel<float>;
+    case DT_BF16: return llprog_kernel<__nv_bfloat16>;
+    case DT_F16: return llprog_kernel<__half>;
+    case DT_I32: return llprog_kernel<int32_t>;
+    case DT_F64: return llprog_kernel<double>;
+    case DT_I64: return llprog_kernel<int64_t>;
+    case DT_U8: return llprog_kernel<uint8_t>;
+  }
+  return nullptr;
+}
+
+}  // namespace chb
+
+using namespace chb;
+
+extern "C" {
+
+// Lines the fullest inbox needs when program p runs with flagged lines on elements of esz bytes,
+// or -1 if the program is not eligible (see chb_run_program_ll).
+long long chb_program_ll_lines(const chb_program* p, int esz) {
+  if (!p || esz < 1) return -1;
+  long long worst = 0;
+  std::vector<long long> inbox(p->prog.P, 0);
+  for (const Op& o : p->prog.ops)
+    for (const Src& x : o.srcs)
+      if (x.peer != o.rank) inbox[o.rank] += lines_of(o.count, esz);
+  for (long long v : inbox) worst = std::max(worst, v);
+  return worst;
+}
+
+// Run a compiled program with flagged lines (see the head of this file).  The program must have been
+// lowered with in_symmetric and out_symmetric set (no staging copies are wanted: nobody reads a peer's
+// buffers here, so the caller's buffers may live anywhere), for a collective in which every rank's
+// result depends on every rank's input.  in / out: one pointer per local rank.
+// Returns CHB_ERR_COUNT when the messages do not fit the inbox.
+int chb_run_program_ll(chb_comm* c, const chb_program* p, int dtype, int op, const void* const* in,
+                       void* const* out, float scale, int nctas, cudaStream_t stream) {
+  if (!c || !p || !in || !out) return CHB_ERR_ARG;
+  const Program& g = p->prog;
+  if (g.P != c->P) { c->last_error = "program was compiled for a different number of ranks"; return CHB_ERR_ARG; }
+  LPFn fn = pick_lp(dtype);
+  if (!fn) return CHB_ERR_ARG;
+  const int esz = dtype_size(dtype);
+  if (op == OP_PROD && dtype == DT_U8) return CHB_ERR_OP;
+  if ((g.reads_peer_in && !g.in_symmetric) || (g.reads_peer_out && !g.out_symmetric)) {
+    c->last_error = "flagged-line execution wants a program lowered without staging copies";
+    return CHB_ERR_ARG;
+  }
+  if ((size_t)g.work_elems * (size_t)esz > c->scratch_bytes) {
+    c->last_error = "program needs more scratch than the communicator has";
+    return CHB_ERR_NO_MEM;
+  }
+  const uint64_t key = p->uid * 16u + (uint64_t)esz;
+  void* blob = nullptr;
+  LPHeader hd{};
+  auto it = c->ll_blobs.find(key);
+  if (it != c->ll_blobs.end()) {
+    blob = it->second.first;
+    hd.max_level_lines = it->second.second;
+  } else {
+    std::vector<char> host = make_ll_blob(g, esz, &hd);
+    if (hd.inbox_lines > (long long)c->P * (long long)c->ll_lines_per_src) {
+      c->last_error = "messages of this program exceed the flagged-line inbox";
+      return CHB_ERR_COUNT;
+    }
+    if (cudaMalloc(&blob, host.size()) != cudaSuccess) { c->last_error = "cudaMalloc(program lines) failed"; return CHB_ERR_NO_MEM; }
+    if (cudaMemcpy(blob, host.data(), host.size(), cudaMemcpyHostToDevice) != cudaSuccess) {
+      cudaFree(blob);
+      c->last_error = "cudaMemcpy(program lines) failed";
+      return CHB_ERR_CUDA;
+    }
+    c->ll_blobs[key] = {blob, hd.max_level_lines};
+  }
+  LPIo io{};
+  for (int l = 0; l < c->nlocal; ++l) {
+    io.in[c->rank + l] = (const char*)in[l];
+    io.out[c->rank + l] = (char*)out[l];
+  }
+  int budget = c->max_ctas / (c->nlocal > 0 ? c->nlocal : 1);
+  if (budget < 1) budget = 1;
+  if (nctas <= 0) {
+    // about four lines per thread in the busiest level
+    nctas = (int)((hd.max_level_lines + kLPThreads * 4 - 1) / (kLPThreads * 4));
+    if (nctas > 32) nctas = 32;
+  }
+  if (nctas > 64) nctas = 64;
+  if (nctas > budget) nctas = budget;
+  if (nctas < 1) nctas = 1;
+  dim3 grid((unsigned)nctas, (unsigned)c->nlocal, 1), block(kLPThreads, 1, 1);
+  World w = c->world;
+  const char* bp = (const char*)blob;
+  long long lps = (long long)c->ll_lines_per_src;
+  void* args[] = {&w, &bp, &io, &op, &scale, &lps};
+  cudaError_t e;
+  if (c->nlocal > 1 || nctas > 1) e = cudaLaunchCooperativeKernel((const void*)fn, grid, block, args, 0, stream);
+  else e = cudaLaunchKernel((const void*)fn, grid, block, args, 0, stream);
+  if (e != cudaSuccess) { c->last_error = std::string("flagged-line program launch failed: ") + cudaGetErrorString(e); return CHB_ERR_CUDA; }
+  return CHB_SUCCESS;
+}
+
+}  // extern "C"

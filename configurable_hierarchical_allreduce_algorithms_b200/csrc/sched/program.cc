@@ -101,6 +101,7 @@ struct Access {
   int32_t level;
   int32_t exec_rank;
   bool write;
+  bool arrival = false;   // the owner's "my input is final" point, not a step (see lower(), part 4)
 };
 
 inline bool overlap(int64_t a, int64_t an, int64_t b, int64_t bn) {
@@ -218,6 +219,21 @@ Program Builder::lower(const LowerOpts& o) const {
   auto H = [&](int rank, int buf) -> std::vector<Access>& { return hist[(size_t)rank * 3 + buf]; };
   struct XDep { int32_t waiter, round, peer, need; };
   std::vector<XDep> xdeps;
+  // Entry handshake.  A caller input that peers pull directly (in_symmetric, not staged) is produced by
+  // whatever the owner's stream ran before this collective, so a reader must not touch it before the
+  // owner has entered the collective.  The owner's entry is modelled as a write of the input by the
+  // owner in round 0: every peer that reads it lands in round >= 1 with a wait on (owner, 0), and the
+  // owner's round 0 (possibly without steps) signals those readers.  The owner's own reads are not
+  // delayed.  Staged inputs need none of this: the staging copy is a step of the owner.
+  // (In the two-sided original a message cannot leave before the sender's call began:
+  //  testing/custom_implementations/work_dir/all_reduce/all_reduce_radix_batch.cpp:353-364.)
+  if (rin && !stage_in)
+    for (int r = 0; r < P_; ++r)
+      if (in_hi[r] >= 0) {
+        Access a{in_lo[r], in_hi[r] - in_lo[r], 0, r, true};
+        a.arrival = true;
+        H(r, P_IN).push_back(a);
+      }
   int32_t cur_fence = INT32_MIN, fence_floor = 0, max_level = -1;
   for (Op& op : ops) {
     if (op.fence != cur_fence) {
@@ -230,6 +246,7 @@ Program Builder::lower(const LowerOpts& o) const {
       for (const Access& a : H(owner, buf)) {
         if (!overlap(a.off, a.cnt, off, cnt)) continue;
         if (!i_write && !a.write) continue;  // read after read
+        if (a.arrival && a.exec_rank == op.rank) continue;  // the owner itself is past its own entry
         lvl = std::max(lvl, a.level + 1);
         if (a.exec_rank != op.rank) deps.emplace_back(a.exec_rank, a.level);
       }
@@ -349,6 +366,17 @@ int simulate_t(const Program& p, int rop, void* const* in, void* const* out, uin
       default: return work[rank].data() + off;
     }
   };
+  // Inputs that peers pull directly are only final once their owner has entered the collective: until a
+  // rank starts its round 0 its input holds poison here, so a schedule that lets a peer read too early
+  // produces a wrong result instead of passing by luck.
+  bool late_inputs = false;
+  for (const Op& op : p.ops)
+    for (const Src& s : op.srcs) late_inputs |= (s.peer != op.rank && s.buf == P_IN);
+  std::vector<std::vector<T>> held(late_inputs ? P : 0);
+  for (int r = 0; r < (int)held.size(); ++r) {
+    held[r].assign((T*)in[r], (T*)in[r] + p.in_elems);
+    std::memset(in[r], 0xEE, (size_t)p.in_elems * sizeof(T));
+  }
   std::vector<int> next(P, 0);  // next round to execute; completed = next-1
   std::mt19937_64 rng(seed);
   std::vector<T> tmp;
@@ -363,10 +391,13 @@ int simulate_t(const Program& p, int rop, void* const* in, void* const* out, uin
       if (ok) ready.push_back(r);
     }
     if (ready.empty()) {
+      for (int q = 0; q < (int)held.size(); ++q)
+        if (next[q] == 0) std::memcpy(in[q], held[q].data(), (size_t)p.in_elems * sizeof(T));
       if (err) *err = "deadlock: no rank can start its next round";
       return -1;
     }
     int r = ready[rng() % ready.size()];
+    if (late_inputs && next[r] == 0) std::memcpy(in[r], held[r].data(), (size_t)p.in_elems * sizeof(T));
     std::vector<int32_t> order = p.rr[r][next[r]].ops;
     std::shuffle(order.begin(), order.end(), rng);
     for (int32_t oi : order) {
@@ -459,6 +490,12 @@ int verify(const Program& p, std::string* err) {
     for (const Src& s : op.srcs)
       if (s.peer != op.rank) {
         if (s.buf == P_IN && !p.in_symmetric) { ++bad; msg << "op " << i << " reads a private input; "; }
+        // a peer's input is only final once that peer has entered the collective (completed its round 0)
+        if (s.buf == P_IN && p.in_symmetric && vc[op.rank][op.level][s.peer] < 0) {
+          ++bad;
+          msg << "op " << i << " (rank " << op.rank << ", round " << op.level << ") reads the input of rank " << s.peer
+              << " before that rank is known to have entered; ";
+        }
         if (s.buf == P_OUT && !p.out_symmetric) { ++bad; msg << "op " << i << " reads a private output; "; }
       }
   }
@@ -483,7 +520,12 @@ namespace {
 
 template <typename T>
 void run_rank(const Program& p, int rank, int rop, void* const* in, void* const* out, std::vector<T>* work,
-              std::atomic<int>* done, std::atomic<bool>* failed) {
+              std::atomic<int>* done, std::atomic<bool>* failed, const std::vector<T>* late_input, int delay_ms) {
+  if (late_input) {
+    // this rank enters late, and its input only becomes final when it enters
+    std::this_thread::sleep_for(std::chrono::milliseconds(delay_ms));
+    std::memcpy(in[rank], late_input->data(), late_input->size() * sizeof(T));
+  }
   auto ptr = [&](int r, int buf, int64_t off) -> T* {
     switch (buf) {
       case P_IN: return (T*)in[r] + off;
@@ -532,8 +574,11 @@ void run_rank(const Program& p, int rank, int rop, void* const* in, void* const*
 }
 
 template <typename T>
-int run_threads_t(const Program& p, int rop, void* const* in, void* const* out, int iters, double* seconds) {
+int run_threads_t(const Program& p, int rop, void* const* in, void* const* out, int iters, double* seconds,
+                  int late_rank, int delay_ms) {
   const int P = p.P;
+  std::vector<T> held;
+  if (late_rank >= 0 && late_rank < P) held.assign((T*)in[late_rank], (T*)in[late_rank] + p.in_elems);
   std::vector<std::vector<T>> work(P);
   for (auto& w : work) w.resize((size_t)std::max<int64_t>(p.work_elems, 1));
   std::atomic<bool> failed{false};
@@ -543,8 +588,10 @@ int run_threads_t(const Program& p, int rop, void* const* in, void* const* out, 
     for (auto& d : done) d.store(-1);
     auto t0 = std::chrono::steady_clock::now();
     std::vector<std::thread> th;
+    if (!held.empty()) std::memset(in[late_rank], 0xEE, held.size() * sizeof(T));
     for (int r = 0; r < P; ++r)
-      th.emplace_back(run_rank<T>, std::cref(p), r, rop, in, out, work.data(), done.data(), &failed);
+      th.emplace_back(run_rank<T>, std::cref(p), r, rop, in, out, work.data(), done.data(), &failed,
+                      (!held.empty() && r == late_rank) ? &held : nullptr, delay_ms);
     for (auto& t : th) t.join();
     total += std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
     if (failed.load()) return -1;
@@ -557,12 +604,13 @@ int run_threads_t(const Program& p, int rop, void* const* in, void* const* out, 
 
 // Note on reduction order: a non-accumulating step combines into dst starting
 // from its first source, i.e. ((s0 op s1) op s2) ..., like the simulator.
-int run_threads(const Program& p, int dtype, int op, void* const* in, void* const* out, int iters, double* seconds) {
+int run_threads(const Program& p, int dtype, int op, void* const* in, void* const* out, int iters, double* seconds,
+                int late_rank, int delay_ms) {
   switch (dtype) {
-    case DT_F32: return run_threads_t<float>(p, op, in, out, iters, seconds);
-    case DT_F64: return run_threads_t<double>(p, op, in, out, iters, seconds);
-    case DT_I32: return run_threads_t<int32_t>(p, op, in, out, iters, seconds);
-    case DT_I64: return run_threads_t<int64_t>(p, op, in, out, iters, seconds);
+    case DT_F32: return run_threads_t<float>(p, op, in, out, iters, seconds, late_rank, delay_ms);
+    case DT_F64: return run_threads_t<double>(p, op, in, out, iters, seconds, late_rank, delay_ms);
+    case DT_I32: return run_threads_t<int32_t>(p, op, in, out, iters, seconds, late_rank, delay_ms);
+    case DT_I64: return run_threads_t<int64_t>(p, op, in, out, iters, seconds, late_rank, delay_ms);
   }
   return -2;
 }

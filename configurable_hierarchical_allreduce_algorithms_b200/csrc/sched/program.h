@@ -145,8 +145,10 @@ int simulate(const Program& p, int dtype, int op, void* const* in, void* const* 
 // seconds per repetition in *seconds.  Returns 0, -1 on a wait that expired, -2
 // for an unsupported dtype.  A step whose first source aliases its destination
 // is handled (in-place copies are skipped).
+// late_rank >= 0: that rank's thread starts delay_ms late and its input holds poison until it does (an
+// input that peers pull directly is only final once its owner has entered the collective).
 int run_threads(const Program& p, int dtype, int op, void* const* in, void* const* out, int iters,
-                double* seconds);
+                double* seconds, int late_rank = -1, int delay_ms = 0);
 
 // Static check: within one round no region is written by one step and read
 // or written by another (on any rank); and every cross-round cross-rank

@@ -123,6 +123,7 @@ void chb_comm_destroy(chb_comm* c) {
   if (!c) return;
   chb_collective_cache_clear(c);
   for (auto& kv : c->blobs) cudaFree(kv.second);
+  for (auto& kv : c->ll_blobs) cudaFree(kv.second.first);
   if (c->ctrl) cudaFree(c->ctrl);
   if (c->trace) cudaFree(c->trace);
   for (void* q : c->ipc_opened) cudaIpcCloseMemHandle(q);

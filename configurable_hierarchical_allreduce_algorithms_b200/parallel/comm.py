@@ -48,6 +48,8 @@ N.optional("chb_dev_free", i32, [vp])
 N.optional("chb_program_prepare", i32, [vp, vp])
 N.optional("chb_program_release", None, [vp, vp])
 N.optional("chb_run_program", i32, [vp, vp, i32, i32, C.POINTER(vp), C.POINTER(vp), f32, i32, vp])
+N.optional("chb_run_program_ll", i32, [vp, vp, i32, i32, C.POINTER(vp), C.POINTER(vp), f32, i32, vp])
+N.optional("chb_program_ll_lines", C.c_longlong, [vp, i32])
 N.optional("chb_ll_max_bytes", C.c_longlong, [vp])
 N.optional("chb_ll_collective", i32, [vp, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), C.c_longlong, f32, i32, vp])
 N.optional("chb_collective", i32, [vp, i32, C.c_char_p, i32, i32, i32, i32, i32, C.POINTER(vp), C.POINTER(vp), i64, f32, i32, vp])
@@ -402,15 +404,20 @@ class Communicator:
                 in_symmetric: bool = False, out_symmetric: bool = False, in_place: bool = False) -> Program:
         return cached_program(coll, algo, self.P, count, k, b, aux, in_symmetric, out_symmetric, in_place)
 
-    def run_program(self, prog: Program, ins, outs, op: str = "sum", scale: float = 1.0, nctas: int = 0, stream=None):
+    def run_program(self, prog: Program, ins, outs, op: str = "sum", scale: float = 1.0, nctas: int = 0, stream=None,
+                    mode: str = "pull"):
+        """Launch a compiled program.  ``mode="pull"``: the persistent interpreter (readers pull over
+        NVLink, rounds separated by flags); ``mode="ll"``: owners push flagged lines into the readers'
+        inboxes (one traversal per round; the program must be lowered with ``in_symmetric`` and
+        ``out_symmetric``, and fit the inbox)."""
         ins, outs = self._lists(ins), self._lists(outs)
         dt = DTYPES[ins[0].dtype]
         for t in ins:
             assert t.is_contiguous() and t.numel() >= prog.in_elems and t.dtype == ins[0].dtype
         for t in outs:
             assert t.is_contiguous() and t.numel() >= prog.out_elems and t.dtype == ins[0].dtype
-        rc = N.lib().chb_run_program(self._h, prog.handle, dt, OPS[op], self._ptrs(ins), self._ptrs(outs),
-                                     scale, nctas, _stream_ptr(stream))
+        fn = N.lib().chb_run_program_ll if mode == "ll" else N.lib().chb_run_program
+        rc = fn(self._h, prog.handle, dt, OPS[op], self._ptrs(ins), self._ptrs(outs), scale, nctas, _stream_ptr(stream))
         self._err(rc)
         self.launches += 1
 

@@ -169,8 +169,13 @@ class Program:
             raise RuntimeError(f"simulate({self.name}) failed: {err.value.decode()}")
         return [o[:self.out_elems] for o in outs]
 
-    def run_threads(self, inputs: list[np.ndarray], op: str = "sum", iters: int = 1):
-        """Run all P ranks as concurrent host threads; returns (outputs, mean seconds per repetition)."""
+    def run_threads(self, inputs: list[np.ndarray], op: str = "sum", iters: int = 1,
+                    late_rank: int | None = None, delay_ms: int = 20):
+        """Run all P ranks as concurrent host threads; returns (outputs, mean seconds per repetition).
+
+        With ``late_rank`` the run is done once, that rank's thread starts ``delay_ms`` late and its input
+        holds poison until then: a schedule that lets a peer pull an input before its owner has entered
+        the collective returns poisoned sums."""
         dt = inputs[0].dtype
         code = _DT_FROM_NP[np.dtype(dt)]
         ins = [np.ascontiguousarray(x, dtype=dt) for x in inputs]
@@ -178,7 +183,10 @@ class Program:
         ip = (C.c_void_p * self.P)(*[x.ctypes.data for x in ins])
         opp = (C.c_void_p * self.P)(*[x.ctypes.data for x in outs])
         sec = C.c_double(0.0)
-        rc = N.lib().chb_program_run_threads(self._h, code, _OPS[op], ip, opp, iters, C.byref(sec))
+        if late_rank is not None:
+            rc = N.lib().chb_program_run_threads_late(self._h, code, _OPS[op], ip, opp, late_rank, delay_ms)
+        else:
+            rc = N.lib().chb_program_run_threads(self._h, code, _OPS[op], ip, opp, iters, C.byref(sec))
         if rc:
             raise RuntimeError(f"run_threads({self.name}) failed with code {rc}")
         return outs, sec.value

@@ -459,3 +459,105 @@ def test_alltoallv_c_entry_point_in_a_world_of_one(cuda):
     assert L.tuna2_algorithm(2, 1, x.data_ptr(), one, zero, NN.I32, y.data_ptr(), wrong, zero, NN.I32, comm.handle) == NN.ERR_COUNT
     comm.check()
     comm.close()
+
+
+# ---------------------------------------------------------------- execution modes of step programs
+MODE_CASES = [("radix_batch", 2, 1), ("radix_batch", 2, 2), ("radix_batch", 4, 4), ("radix_batch", 8, 8),
+              ("radix_batch", 3, 4), ("recursive_doubling", 2, 1), ("reduce_scatter_allgather", 2, 1),
+              ("ring", 2, 1), ("recursive_multiplying", 3, 1), ("semi_radix_batch", 2, 2)]
+
+
+@pytest.mark.parametrize("mode", ["ll", "pull"])
+@pytest.mark.parametrize("algo,k,b", MODE_CASES)
+def test_allreduce_program_modes(comms, algo, k, b, mode):
+    """Every schedule gives the same sums whether readers pull or owners push flagged lines."""
+    P = 8
+    comm = comms(P)
+    for dtype, n in ((torch.float32, 8 * 1024), (torch.bfloat16, 8 * 33), (torch.int32, 8 * 3), (torch.float32, 8),
+                     (torch.float64, 8 * 5), (torch.float16, 8 * 129)):
+        ins = make_inputs(P, n, dtype, seed=n)
+        exp = ref_reduce(ins, "sum")
+        outs = chb.all_reduce(comm, ins, algo=f"{algo}:{mode}", k=k, b=b)
+        for r in range(P):
+            check(outs[r], exp, dtype, P)
+    # scale is applied exactly once, in place works, back-to-back launches alternate the inbox halves
+    ins = make_inputs(P, 8 * 100, torch.float32, seed=5)
+    exp = ref_reduce(ins, "sum")
+    for _ in range(5):
+        outs = chb.all_reduce(comm, ins, algo=f"{algo}:{mode}", k=k, b=b, scale=0.5)
+    for r in range(P):
+        check(outs[r], exp * 0.5, torch.float32, P)
+    bufs = [x.clone() for x in ins]
+    chb.all_reduce(comm, bufs, out=bufs, algo=f"{algo}:{mode}", k=k, b=b)
+    for r in range(P):
+        check(bufs[r], exp, torch.float32, P)
+    comm.check()
+
+
+@pytest.mark.parametrize("mode", ["ll", "pull"])
+@pytest.mark.parametrize("P", [2, 3, 4, 6, 8])
+def test_rs_ag_program_modes(comms, P, mode):
+    comm = comms(P)
+    for b in [d for d in (1, 2, 3, 4, 8) if P % d == 0]:
+        for k in (2, 3):
+            for dtype, n in ((torch.float32, 1), (torch.float32, 31), (torch.bfloat16, 127), (torch.int64, 5), (torch.float32, 2048)):
+                ins = make_inputs(P, n * P, dtype, seed=n + b)
+                exp = ref_reduce(ins, "sum")
+                outs = chb.reduce_scatter(comm, ins, algo=f"radix_batch:{mode}", k=k, b=b)
+                for r in range(P):
+                    check(outs[r], exp[r * n:(r + 1) * n], dtype, P)
+                blocks = [x[:n].contiguous() for x in ins]
+                outs = chb.all_gather(comm, blocks, algo=f"radix_batch:{mode}", k=k, b=b)
+                cat = torch.cat(blocks)
+                for r in range(P):
+                    assert torch.equal(outs[r], cat)
+    # max / min through the flagged lines as well
+    ins = make_inputs(P, 64 * P, torch.float32, seed=9)
+    for op in ("max", "min"):
+        outs = chb.all_reduce(comm, ins, op=op, algo=f"radix_batch:{mode}", k=2, b=1)
+        for r in range(P):
+            check(outs[r], ref_reduce(ins, op), torch.float32, P)
+    comm.check()
+
+
+def test_ll_mode_refuses_what_does_not_fit(comms):
+    P = 4
+    comm = comms(P)
+    n = (comm.ll_max_bytes * P) // 4 * 2           # twice what the inbox holds
+    ins = make_inputs(P, n, torch.float32)
+    with pytest.raises(chb.CollectiveError):
+        chb.all_reduce(comm, ins, algo="radix_batch:ll", k=2, b=1)
+    # without a pinned mode the same call falls back to the pull interpreter
+    outs = chb.all_reduce(comm, ins, algo="radix_batch", k=2, b=1)
+    check(outs[0], ref_reduce(ins, "sum"), torch.float32, P)
+    comm.check()
+
+
+@pytest.mark.parametrize("k,b", [(2, 1), (2, 2), (4, 4), (2, 8)])
+def test_tile_scheduler_large_steps(comms, k, b):
+    """Steps of several MiB are cut into tiles dealt over the CTAs; odd lengths leave ragged last tiles
+    and unaligned tails, a sliced view shifts every pointer off the 32-byte grid."""
+    P = 8
+    comm = comms(P)
+    for dtype, n in ((torch.float32, (1 << 19) + 24), (torch.bfloat16, (1 << 20) + 8 * 5)):
+        n = n // P * P
+        ins = make_inputs(P, n, dtype, seed=k + b)
+        exp = ref_reduce(ins, "sum")
+        for nctas in (3, 16):
+            outs = chb.all_reduce(comm, ins, algo="radix_batch:pull", k=k, b=b, nctas=nctas)
+            for r in range(P):
+                check(outs[r], exp, dtype, P)
+        m = n // P
+        outs = chb.reduce_scatter(comm, ins, algo="radix_batch:pull", k=k, b=b, nctas=8)
+        for r in range(P):
+            check(outs[r], exp[r * m:(r + 1) * m], dtype, P)
+        blocks = [x[:m + 0].contiguous() for x in ins]
+        outs = chb.all_gather(comm, blocks, algo="radix_batch:pull", k=k, b=b, nctas=8)
+        for r in range(P):
+            assert torch.equal(outs[r], torch.cat(blocks))
+    # pointers 4 bytes off the vector grid: the scalar path of the same tiles
+    big = make_inputs(P, (1 << 18) + P, torch.float32, seed=3)
+    ins = [x[1:1 + (1 << 18)] for x in big]
+    outs = chb.all_reduce(comm, [x.contiguous() for x in ins], algo="radix_batch:pull", k=k, b=b, nctas=4)
+    check(outs[P - 1], ref_reduce(ins, "sum"), torch.float32, P)
+    comm.check()

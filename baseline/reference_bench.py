@@ -1,9 +1,18 @@
 """Reference arm of bench.py: the reference's own ``all_reduce_radix_batch``
 (unmodified source, ``baseline/_ref/src``) on the host CPUs, N ranks as
-threads over the MPI shim in ``baseline/shim`` — the image has no MPI.  Same
-metric and configuration as the main arm: sum allreduce of ``--bytes`` fp32
-per rank, ``k = 2, b = 1`` (the flat setting, which is the reference's best
-large-message shape), value = N * bytes / time.
+threads over the MPI stand-in of ``baseline/shim`` (the image has no MPI).  Same
+metric, configuration, step and warm-up counts as the main arm: sum allreduce
+of ``--bytes`` fp32 per rank, ``k = 2, b = 1`` (the flat setting, the
+reference's best large-message shape), value = N * bytes / time.
+
+The reference's buffers are host arrays, so its timed call
+(testing/custom_implementations/work_dir/all_reduce/main.cpp:55-66: Barrier; t0;
+call; Barrier; t1) already is an end-to-end number: host buffer in, host buffer
+out, no device on the path.  It is therefore reported both as ``value`` and as
+``e2e`` (with zero bytes over PCIe).
+
+Nothing of this repository's library is imported or loaded here: the process
+runs ``baseline/_ref/ref_driver`` and parses its one line of output.
 """
 from __future__ import annotations
 
@@ -20,7 +29,7 @@ def _unavailable(why: str) -> dict:
     return {"impl": "reference", "unavailable": why}
 
 
-def run(args) -> dict | None:
+def run(args, config: dict, metric: str) -> dict | None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return None   # the N ranks are threads of rank 0's process
@@ -39,8 +48,7 @@ def run(args) -> dict | None:
             return _unavailable(f"host memory: {need >> 30} GiB needed for {N} thread ranks of {S >> 20} MiB")
     except ImportError:
         pass
-    # the CPU code needs seconds per GiB-sized step: a handful of steps is enough for a stable mean
-    K, W = max(1, min(int(args.steps), 5)), 1
+    K, W = max(1, int(args.steps)), max(int(args.warmup), 3)      # the same counts as the main arm
     try:
         r = subprocess.run([str(EXE), "time", "ar", str(N), "2", "1", str(S), str(K), str(W)],
                            capture_output=True, text=True, timeout=3000)
@@ -51,31 +59,20 @@ def run(args) -> dict | None:
         return _unavailable(f"reference driver failed rc={r.returncode}: {r.stderr[-150:]}")
     d = json.loads(line[-1])
     ms = d["ms_per_step"]
-    # the same collective with this library's schedule on host threads (one thread per rank, same machine):
-    # a CPU-to-CPU comparison that does not involve the GPUs at all
-    host_ms = None
-    try:
-        import numpy as np
-        import sys
-        sys.path.insert(0, str(HERE.parent))
-        from configurable_hierarchical_allreduce_algorithms_b200.parallel.program import Program
-        n = S // 4 // N * N
-        prog = Program("allreduce", "radix_batch", N, n, 2, 1)
-        ins = [np.full(n, float(r), np.float32) for r in range(N)]
-        _, sec = prog.run_threads(ins, iters=2)
-        host_ms = sec * 1e3
-    except Exception:  # noqa: BLE001 - optional extra
-        host_ms = None
     algbw = S / (ms * 1e-3) / 1e9
     return {
-        "impl": "reference", "metric": "allreduce_sum_fp32_aggregate_algbw_GBps", "value": algbw * N, "unit": "GB/s",
+        "impl": "reference", "metric": metric, "value": algbw * N, "unit": "GB/s",
         "n_gpus": N, "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "fp32", "data": "synthetic", "is_correct": bool(d["is_correct"]),
         "algbw_GBps": algbw, "busbw_GBps": algbw * 2 * (N - 1) / N,
-        "config": {"model": "allreduce sum fp32", "bytes_per_gpu": S, "parallelism": f"{N} CPU thread ranks",
-                   "algorithm": "all_reduce_radix_batch k=2 b=1",
-                   "transport": "thread-per-rank MPI shim on the host CPUs (no MPI installation on the image)",
-                   "timing": "host clock, Barrier; t0; call; Barrier; t1 as in the reference's drivers"},
+        "config": config,
+        "arm": {"algorithm": "all_reduce_radix_batch k=2 b=1 (unmodified reference source)",
+                "ranks": f"{N} CPU thread ranks",
+                "transport": "thread-per-rank MPI stand-in on the host CPUs (no MPI installation on the image); "
+                             "large messages are copied once, by the receiver",
+                "timing": "host clock, Barrier; t0; call; Barrier; t1 as in the reference's drivers"},
         "gpu_launches": 0,
-        "this_library_same_schedule_on_host_threads_ms": host_ms,
+        "e2e": {"value": algbw * N, "unit": "GB/s", "ms_per_step": ms, "steps": K,
+                "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                "note": "the reference's buffers are host buffers: its timed call is host in, host out"},
     }

@@ -1,8 +1,10 @@
 // Minimal single-process stand-in for <mpi.h>: every MPI rank is a thread of
 // one process.  Only what the reference's collectives and stand-alone phases call is provided
 // (rank / size / type size, Isend / Irecv / Wait / Waitall, Reduce_local,
-// Barrier, Wtime).  Sends are eager (the payload is copied into the
-// destination's mailbox), receives match on (source, tag) in arrival order.
+// Barrier, Wtime).  Small sends are eager (the payload is copied into the
+// destination's mailbox), large non-blocking sends are copied once, by the
+// receiver, straight from the sender's buffer; receives match on (source, tag)
+// in arrival order.
 // This exists so that the reference's own sources can be compiled unmodified
 // and timed on a machine without an MPI installation.
 #pragma once

@@ -1,8 +1,13 @@
 // Thread-per-rank implementation of the calls declared in mpi.h (see there).
 //
-// Ranks are threads of one process.  Point-to-point sends are eager (the payload
-// is packed into the destination's mailbox), receives match on (communicator,
-// source, tag) in arrival order.  Communicators are rank lists created by
+// Ranks are threads of one process.  Small point-to-point sends are eager (the
+// payload is packed into the destination's mailbox); a non-blocking send of 64 KiB
+// or more of a basic type is a rendezvous: the mailbox entry only points at the
+// sender's buffer, the receiver copies from it once (what a shared-memory MPI does
+// for large messages) and the send request completes when that copy is done.
+// Receives match on (communicator, source, tag) in arrival order.  A rank that
+// waits, for a send or a receive, keeps completing all the receives it has posted,
+// as an MPI progress engine would.  Communicators are rank lists created by
 // MPI_Comm_split; the few collectives the reference's sources call are done by
 // publishing buffer pointers and meeting at the communicator's barrier.
 // Derived datatypes are lists of (byte displacement, byte length) segments.
@@ -18,9 +23,20 @@
 #include <mutex>
 #include <vector>
 
-struct ShimRequest { bool recv; void* buf; int count; MPI_Datatype type; int peer, tag; MPI_Comm comm; };
+namespace { struct Rdv { bool done = false; }; }   // guarded by the SENDER's mailbox mutex
+struct ShimRequest {
+  bool recv; void* buf; int count; MPI_Datatype type; int peer, tag; MPI_Comm comm;
+  bool done = false;                 // receive completed (by whichever wait of this rank made progress)
+  std::shared_ptr<Rdv> rdv;          // rendezvous send: completes when the receiver has copied
+};
 namespace {
-struct Message { int comm, src, tag; std::unique_ptr<char[]> data; size_t bytes; };
+constexpr size_t kRendezvousBytes = 64 << 10;
+struct Message {
+  int comm, src, tag; std::unique_ptr<char[]> data; size_t bytes;
+  const void* ref = nullptr;         // rendezvous: the sender's buffer (data is empty)
+  std::shared_ptr<Rdv> rdv;
+  int gsrc = -1;                     // global rank of the sender (whose mailbox guards rdv)
+};
 struct Mailbox { std::mutex m; std::condition_variable cv; std::deque<Message> q; };
 struct Comm {
   std::vector<int> ranks;                 // global ranks, in communicator order
@@ -41,6 +57,8 @@ std::mutex g_reg_m;                               // guards growth of g_comms / 
 std::vector<Segments> g_types;                    // derived datatypes, id = kTypeBase + index
 constexpr int kTypeBase = 1000;
 thread_local int t_rank = -1;
+thread_local bool g_rendezvous_ok = true;
+thread_local std::vector<ShimRequest*> t_posted;  // receives this rank has posted and not yet waited for
 bool g_fail = false;
 
 size_t basic_bytes(MPI_Datatype d) { return d == MPI_FLOAT ? 4 : (size_t)d; }
@@ -146,36 +164,68 @@ int MPI_Isend(const void* buf, int count, MPI_Datatype d, int dst, int tag, MPI_
   if (dst < 0 || dst >= (int)cm.ranks.size()) { g_fail = true; return MPI_ERR_ARG; }
   const int gdst = cm.ranks[(size_t)dst];
   size_t n = (size_t)count * type_bytes(d);
-  Message m{c, comm_rank(cm), tag, std::unique_ptr<char[]>(new char[n ? n : 1]), n};
-  pack(buf, count, d, m.data.get());
+  Message m{c, comm_rank(cm), tag, nullptr, n};
+  if (g_rendezvous_ok && !derived(d) && n >= kRendezvousBytes) {
+    m.ref = buf;
+    m.rdv = std::make_shared<Rdv>();
+    m.gsrc = t_rank;
+    (*r)->rdv = m.rdv;
+  } else {
+    m.data.reset(new char[n ? n : 1]);
+    pack(buf, count, d, m.data.get());
+  }
   { std::lock_guard<std::mutex> l(g_box[gdst]->m); g_box[gdst]->q.push_back(std::move(m)); }
   g_box[gdst]->cv.notify_all();
   return MPI_SUCCESS;
 }
 int MPI_Irecv(void* buf, int count, MPI_Datatype d, int src, int tag, MPI_Comm c, MPI_Request* r) {
   *r = new ShimRequest{true, buf, count, d, src, tag, c};
+  t_posted.push_back(*r);
   return MPI_SUCCESS;
 }
+
+namespace {
+// Complete, in posting order, every posted receive of this rank whose message has arrived.  Called with this
+// rank's mailbox locked; the lock is dropped while a payload is copied.
+void progress(Mailbox& b, std::unique_lock<std::mutex>& l) {
+  for (size_t i = 0; i < t_posted.size(); ++i) {
+    ShimRequest* r = t_posted[i];
+    if (r->done) continue;
+    for (auto it = b.q.begin(); it != b.q.end(); ++it) {
+      if (!(it->comm == r->comm && it->src == r->peer && it->tag == r->tag)) continue;
+      Message m = std::move(*it);
+      b.q.erase(it);
+      l.unlock();
+      const size_t cap = (size_t)r->count * type_bytes(r->type);
+      if (m.bytes > cap) g_fail = true;  // truncation
+      unpack(m.ref ? (const char*)m.ref : m.data.get(), std::min(m.bytes, cap), r->buf, r->count, r->type);
+      if (m.rdv) {
+        Mailbox& sb = *g_box[(size_t)m.gsrc];
+        { std::lock_guard<std::mutex> g(sb.m); m.rdv->done = true; }
+        sb.cv.notify_all();
+      }
+      l.lock();
+      r->done = true;
+      break;
+    }
+  }
+}
+}  // namespace
+
 int MPI_Wait(MPI_Request* rp, MPI_Status*) {
   ShimRequest* r = *rp;
   if (!r) return MPI_SUCCESS;
-  if (r->recv) {
-    const size_t cap = (size_t)r->count * type_bytes(r->type);
+  if (r->recv || r->rdv) {
     Mailbox& b = *g_box[t_rank];
     std::unique_lock<std::mutex> l(b.m);
+    const auto t0 = std::chrono::steady_clock::now();
     for (;;) {
-      bool found = false;
-      for (auto it = b.q.begin(); it != b.q.end(); ++it)
-        if (it->comm == r->comm && it->src == r->peer && it->tag == r->tag) {
-          if (it->bytes > cap) g_fail = true;  // truncation
-          unpack(it->data.get(), std::min(it->bytes, cap), r->buf, r->count, r->type);
-          b.q.erase(it);
-          found = true;
-          break;
-        }
-      if (found) break;
-      if (b.cv.wait_for(l, std::chrono::seconds(60)) == std::cv_status::timeout) { g_fail = true; break; }
+      progress(b, l);
+      if (r->recv ? r->done : r->rdv->done) break;
+      b.cv.wait_for(l, std::chrono::milliseconds(200));
+      if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(120)) { g_fail = true; break; }
     }
+    if (r->recv) t_posted.erase(std::find(t_posted.begin(), t_posted.end(), r));
   }
   delete r;
   *rp = nullptr;
@@ -186,8 +236,11 @@ int MPI_Waitall(int n, MPI_Request* r, MPI_Status*) {
   return MPI_SUCCESS;
 }
 int MPI_Send(const void* buf, int count, MPI_Datatype d, int dst, int tag, MPI_Comm c) {
+  // always eager: a blocking send returns at once, as it does for the sizes the phase sources were tested with
   MPI_Request r;
+  g_rendezvous_ok = false;
   int rc = MPI_Isend(buf, count, d, dst, tag, c, &r);
+  g_rendezvous_ok = true;
   MPI_Wait(&r, nullptr);
   return rc;
 }
@@ -200,9 +253,9 @@ int MPI_Sendrecv(const void* sb, int sc, MPI_Datatype sd, int dst, int stag, voi
                  int rtag, MPI_Comm c, MPI_Status*) {
   MPI_Request rs, rr;
   MPI_Irecv(rb, rc, rd, src, rtag, c, &rr);
-  int e = MPI_Isend(sb, sc, sd, dst, stag, c, &rs);   // eager: the payload is copied before the receive unpacks
-  MPI_Wait(&rs, nullptr);
+  int e = MPI_Isend(sb, sc, sd, dst, stag, c, &rs);
   MPI_Wait(&rr, nullptr);
+  MPI_Wait(&rs, nullptr);
   return e;
 }
 

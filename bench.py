@@ -165,12 +165,42 @@ def per_call_ms(fn, iters, flush, barrier):
     return out
 
 
+METRIC = "allreduce_sum_fp32_aggregate_algbw_GBps"
+
+
+def headline_config(N: int, S: int) -> dict:
+    """What is measured, identical for both arms (what differs between them goes under "arm")."""
+    return {"model": "allreduce sum fp32 (config 2 of the sweep: 8 B - 1 GiB)", "bytes_per_gpu": S,
+            "global_batch": None, "seq_len": None, "parallelism": f"{N} ranks",
+            "l2": "inputs larger than L2 for the headline; explicit 256 MiB L2 flush before every timed call in the sweep"}
+
+
 def reference_arm(args):
     from baseline import reference_bench
 
-    out = reference_bench.run(args)
+    N = max(1, int(os.environ.get("WORLD_SIZE", args.gpus)))
+    out = reference_bench.run(args, headline_config(N, int(args.bytes)), METRIC)
     if out is not None:
         print(json.dumps(out), flush=True)
+
+
+def roofline(N: int, S: int, kernel: str, ms_per_step: float, peaks: dict) -> dict:
+    """Bytes one GPU must put on NVLink for an allreduce of S bytes, over the link rate.
+    Pull / push two-shot: 2 (N-1)/N S per direction.  In-switch (multimem) two-shot: the switch reads every
+    GPU's copy of a slice and writes the result to every GPU, S (1 + 1/N) per direction per GPU.
+    N = 1: a local copy, 2 S at the measured HBM copy bandwidth."""
+    if N == 1:
+        bw = peaks.get("hbm_gbs", 6650.0) * 1e9
+        ideal = 2 * S / bw * 1e3
+        return {"model": "local copy, 2 S bytes at the measured HBM copy bandwidth", "ideal_ms": ideal,
+                "frac_of_measured": ideal / ms_per_step}
+    if kernel.startswith("nvls"):
+        nbytes, model = S * (1 + 1 / N), "in-switch two-shot: S (1 + 1/N) bytes per direction per GPU"
+    else:
+        nbytes, model = 2 * (N - 1) / N * S, "peer two-shot: 2 (N-1)/N S bytes per direction per GPU"
+    i900, i770 = nbytes / 900e9 * 1e3, nbytes / 770e9 * 1e3
+    return {"model": model, "bytes_per_direction": nbytes, "ideal_ms_at_900_nominal": i900, "frac_of_900_nominal": i900 / ms_per_step,
+            "ideal_ms_at_770_measured": i770, "frac_of_770_measured": i770 / ms_per_step}
 
 
 def main():
@@ -180,9 +210,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--bytes", type=int, default=1 << 30, help="allreduce vector bytes per GPU (headline)")
-    ap.add_argument("--sweep", default="8,512,32768,1048576,33554432,268435456",
-                    help="comma separated message sizes in bytes for the latency / bandwidth table ('' = none)")
-    ap.add_argument("--sweep-iters", type=int, default=10)
+    ap.add_argument("--sweep", default=",".join(str(8 * 4 ** i) for i in range(14)) + ",1073741824",
+                    help="comma separated message sizes in bytes for the latency / bandwidth table ('' = none); "
+                         "default 8 B ... 512 MiB in powers of 4, and 1 GiB")
+    ap.add_argument("--sweep-iters", type=int, default=7)
+    ap.add_argument("--grid", default="32768,1048576,16777216,1073741824",
+                    help="sizes of the (k, b) grid / NCCL ring, tree / reference-algorithm table ('' = none)")
+    ap.add_argument("--rows-out", default="", help="also write sweep and grid rows to this JSON file")
     ap.add_argument("--no-nccl", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
@@ -193,13 +227,17 @@ def main():
     import torch
     import torch.distributed as dist
 
-    import configurable_hierarchical_allreduce_algorithms_b200 as chb
-    from configurable_hierarchical_allreduce_algorithms_b200.parallel.comm import Communicator
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
+    # cores and memory node nearest this rank's GPU, before any pinned buffer is allocated
+    from configurable_hierarchical_allreduce_algorithms_b200.utils import affinity, autotune
+    host_binding = affinity.bind_to_gpu(local_rank)
+
+    import configurable_hierarchical_allreduce_algorithms_b200 as chb
+    from configurable_hierarchical_allreduce_algorithms_b200.parallel.comm import CollectiveError, Communicator
+
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -220,10 +258,17 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    heap_user = 2 * S + (64 << 20) + (0 if args.no_e2e else (6 * (64 << 20) + (1 << 20)))   # + the host pipeline's chunks
+    def all_ranks_ok(ok: bool) -> bool:
+        if world == 1:
+            return bool(ok)
+        t = torch.tensor([1 if ok else 0], device="cuda", dtype=torch.int32)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item())
+
+    heap_user = 2 * S + (64 << 20) + (0 if args.no_e2e else (8 * (32 << 20) + (1 << 20)))   # + the host pipeline's chunks
     if world > 1:
-        comm = Communicator.from_process_group(scratch_bytes=max(64 << 20, S + (16 << 20)) if N > 1 else 1 << 20,
-                                               user_bytes=heap_user)
+        # scratch: the hierarchical shapes (b > 1) and the full-vector baselines keep up to two vectors of temporaries
+        comm = Communicator.from_process_group(scratch_bytes=2 * S + (32 << 20), user_bytes=heap_user)
     else:
         comm = Communicator.emulated(1, scratch_bytes=1 << 20, user_bytes=heap_user)
 
@@ -234,24 +279,21 @@ def main():
     y = unl(comm.empty(nelem, torch.float32))
     g = torch.Generator(device="cuda").manual_seed(1234 + rank)
     x.copy_(torch.rand(nelem, generator=g, device="cuda") * 2 - 1)
-    wrap = lambda t: t  # one local rank per process: tensors, not lists
 
     def step():
-        chb.all_reduce(comm, wrap(x), out=wrap(y))
+        chb.all_reduce(comm, x, out=y)
 
     # ---- correctness of the timed call (against NCCL when there are peers, else identity)
     step()
     torch.cuda.synchronize()
     comm.check()
+    ref = x.clone()
     if world > 1:
-        ref = x.clone()
         dist.all_reduce(ref)
-        err = float((y - ref).abs().max())
-        tol = 1e-4 * N
-    else:
-        err = float((y - x).abs().max())
-        tol = 0.0
-    correct = err <= tol
+    err = float((y - ref).abs().max())
+    tol = 1e-4 * N if world > 1 else 0.0
+    correct = all_ranks_ok(err <= tol)
+    headline_kernel = autotune.choose(comm, "allreduce", S, torch.float32, True)
 
     with ClockSampler(local_rank) as cs:
         for _ in range(W):
@@ -275,8 +317,9 @@ def main():
     busbw = algbw * (2 * (N - 1) / N)
     clocks = cs.summary()
 
-    # ---- NCCL on the same buffers
+    # ---- NCCL on the same buffers: its default choice, and ring / tree pinned through NCCL_ALGO on groups of their own
     nccl = None
+    nccl_groups = {}
     if world > 1 and not args.no_nccl:
         z = x.clone()
         for _ in range(W):
@@ -284,6 +327,20 @@ def main():
         t = max_over_ranks(device_time_ms(lambda: dist.all_reduce(z), K, None, barrier)) / K
         nccl = {"ms_per_step": t, "algbw_GBps": S / (t * 1e-3) / 1e9, "busbw_GBps": S / (t * 1e-3) / 1e9 * 2 * (N - 1) / N}
         del z
+        for name in ("Ring", "Tree"):
+            try:
+                os.environ["NCCL_ALGO"] = name          # read when the group's communicator is set up
+                grp = dist.new_group(ranks=list(range(world)), backend="nccl")
+                w1 = torch.ones(8, device="cuda")
+                dist.all_reduce(w1, group=grp)           # the communicator exists before the variable goes away
+                torch.cuda.synchronize()
+                nccl_groups[name.lower()] = grp
+            except Exception as e:  # noqa: BLE001 - an optional comparison row
+                nccl_groups[name.lower()] = None
+                if rank == 0:
+                    print(f"# NCCL_ALGO={name}: {e!r}"[:200], file=sys.stderr)
+            finally:
+                os.environ.pop("NCCL_ALGO", None)
 
     # ---- end to end through the public API: pinned host -> device, allreduce, device -> host
     e2e = None
@@ -302,33 +359,83 @@ def main():
             pipe(hx, hy)
             torch.cuda.current_stream().synchronize()
 
+        def timed(fn, reps):
+            barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            barrier()
+            return max_over_ranks(e0.elapsed_time(e1)) / reps, (time.perf_counter() - t0) * 1e3 / reps
+
         ke = max(3, min(K, 10))
         for _ in range(3):
             e2e_step()
-        barrier()
+        tms, wall = timed(e2e_step, ke)
+        e2e_ok = all_ranks_ok(bool(torch.equal(hy, y.cpu())))       # the whole vector against the device result
+        # what the host side of this box allows with every rank copying at once: upload alone, download alone, both
+        # together (no collective), and the chunked collective alone; the pipeline cannot beat the slowest of them
+        s_up, s_dn = torch.cuda.Stream(), torch.cuda.Stream()
+        ch = 8 << 20
+
+        def copies(up: bool, down: bool):
+            cur = torch.cuda.current_stream()
+            s_up.wait_stream(cur)
+            s_dn.wait_stream(cur)
+            for a in range(0, nelem, ch):
+                e = min(nelem, a + ch)
+                if up:
+                    with torch.cuda.stream(s_up):
+                        x[a:e].copy_(hx[a:e], non_blocking=True)
+                if down:
+                    with torch.cuda.stream(s_dn):
+                        hy[a:e].copy_(y[a:e], non_blocking=True)
+            cur.wait_stream(s_up)
+            cur.wait_stream(s_dn)
+            cur.synchronize()
+
+        def coll_only():
+            for a in range(0, nelem, ch):
+                e = min(nelem, a + ch)
+                chb.all_reduce(comm, x[a:e], out=y[a:e])
+            torch.cuda.current_stream().synchronize()
+
+        x_keep = x.clone()
+        stages = {}
+        for name, fn in (("upload_only", lambda: copies(True, False)), ("download_only", lambda: copies(False, True)),
+                         ("upload_and_download", lambda: copies(True, True)), ("collective_only", coll_only)):
+            fn()
+            stages[name + "_ms"] = timed(fn, 3)[0]
+        x.copy_(x_keep)
+        step()                                                   # y holds the reduced vector again
         torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(ke):
-            e2e_step()
-        e1.record()
-        torch.cuda.synchronize()
-        barrier()
-        tms = max_over_ranks(e0.elapsed_time(e1)) / ke
-        wall = (time.perf_counter() - t0) * 1e3 / ke
-        probe = slice(nelem - (1 << 20), nelem)      # the last chunk's tail: wrong only if the pipeline lost a chunk
-        e2e_ok = bool(torch.equal(hy[probe], y[probe].cpu()))
+        del x_keep
+        floor_ms = max(stages["upload_and_download_ms"], stages["collective_only_ms"])
         e2e = {"value": N * S / (tms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": tms, "steps": ke,
                "h2d_bytes_per_step": S, "d2h_bytes_per_step": S, "wall_ms_per_step": wall, "is_correct": e2e_ok,
-               "api": "HostAllReduce: 32 MiB chunks, upload / allreduce / download pipelined on three streams"}
+               "checked": "whole output vector against the device-side result, all ranks",
+               "api": "HostAllReduce: 32 MiB chunks, upload / allreduce / download pipelined on three streams",
+               "stages": stages, "host_binding": host_binding,
+               "host_ceiling_GBps": N * S / (floor_ms * 1e-3) / 1e9,
+               "frac_of_host_ceiling": floor_ms / tms,
+               "ceiling_note": "ceiling = N * bytes / max(all ranks uploading and downloading at once, chunked collective alone)"}
         del hx, hy
 
-    # ---- latency / bandwidth table
+    # ---- latency / bandwidth table: algo="auto" against NCCL's default, three collectives, fp32 and bf16
     sweep = []
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    flush = lambda: flush_buf.fill_(1)
+
+    def close_enough(a, b, dtype):
+        tol_ = (1e-5 if dtype == torch.float32 else 2e-2) * max(N, 1)
+        return bool(torch.allclose(a.float(), b.float(), rtol=tol_, atol=tol_))
+
     if args.sweep:
-        flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-        flush = lambda: flush_buf.fill_(1)
+        scratch_ref = torch.empty(min(nelem, 1 << 26), dtype=torch.float32, device="cuda")   # NCCL's output for the checks
         for sz in [int(s) for s in args.sweep.split(",") if s]:
             if sz > S:
                 continue
@@ -339,25 +446,36 @@ def main():
                 xf, yf = x.view(dtype), y.view(dtype)     # slices below may be longer than ne for tiny sizes
                 xv, yv = xf[:ne], yf[:ne]
                 row = {"bytes": ne * esz, "dtype": dname}
+                rf = scratch_ref.view(dtype)
                 cases = {
-                    "allreduce": (lambda: chb.all_reduce(comm, wrap(xv), out=wrap(yv)),
-                                  (lambda: dist.all_reduce(yv)) if world > 1 else None, 2 * (N - 1) / N, ne * esz),
-                    "reduce_scatter": (lambda: chb.reduce_scatter(comm, wrap(xf[:ne_rs * N]), out=wrap(yf[:ne_rs])),
+                    "allreduce": (lambda: chb.all_reduce(comm, xv, out=yv),
+                                  (lambda: dist.all_reduce(yv)) if world > 1 else None, 2 * (N - 1) / N, ne * esz,
+                                  (lambda: (rf[:ne].copy_(xv), dist.all_reduce(rf[:ne]) if world > 1 else None, (yv, rf[:ne]))[-1])),
+                    "reduce_scatter": (lambda: chb.reduce_scatter(comm, xf[:ne_rs * N], out=yf[:ne_rs]),
                                        (lambda: dist.reduce_scatter_tensor(yf[:ne_rs], xf[:ne_rs * N])) if world > 1 else None,
-                                       (N - 1) / N, ne_rs * N * esz),
-                    "allgather": (lambda: chb.all_gather(comm, wrap(xf[:ne_rs]), out=wrap(yf[:ne_rs * N])),
+                                       (N - 1) / N, ne_rs * N * esz,
+                                       (lambda: (dist.reduce_scatter_tensor(rf[:ne_rs], xf[:ne_rs * N]) if world > 1
+                                                 else rf[:ne_rs].copy_(xf[:ne_rs]), (yf[:ne_rs], rf[:ne_rs]))[-1])),
+                    "allgather": (lambda: chb.all_gather(comm, xf[:ne_rs], out=yf[:ne_rs * N]),
                                   (lambda: dist.all_gather_into_tensor(yf[:ne_rs * N], xf[:ne_rs])) if world > 1 else None,
-                                  (N - 1) / N, ne_rs * N * esz),
+                                  (N - 1) / N, ne_rs * N * esz,
+                                  (lambda: (dist.all_gather_into_tensor(rf[:ne_rs * N], xf[:ne_rs]) if world > 1
+                                            else rf[:ne_rs].copy_(xf[:ne_rs]), (yf[:ne_rs * N], rf[:ne_rs * N]))[-1])),
                 }
-                for name, (ours, theirs, factor, total_bytes) in cases.items():
-                    # about 30 ms of back-to-back calls first (the same count on every rank): after the small
+                for name, (ours, theirs, factor, total_bytes, checker) in cases.items():
+                    # about 20 ms of back-to-back calls first (the same count on every rank): after the small
                     # sizes of the sweep the links and clocks need more than three calls to be back at speed
-                    n_warm = min(200, max(3, int(30e-3 / (20e-6 + total_bytes / 2e11))))
+                    n_warm = min(100, max(3, int(20e-3 / (20e-6 + total_bytes / 2e11))))
                     for _ in range(n_warm):
                         ours()
                     t = [max_over_ranks(v) for v in per_call_ms(ours, args.sweep_iters, flush, barrier)]
                     p50 = statistics.median(t)
                     row[name] = {"p50_us": p50 * 1e3, "busbw_GBps": total_bytes / (p50 * 1e-3) / 1e9 * factor}
+                    if total_bytes <= scratch_ref.numel() * 4:
+                        ours()
+                        got, want = checker()
+                        torch.cuda.synchronize()
+                        row[name]["is_correct"] = all_ranks_ok(close_enough(got, want, dtype))
                     if theirs is not None and not args.no_nccl:
                         for _ in range(n_warm):
                             theirs()
@@ -365,7 +483,56 @@ def main():
                         p50n = statistics.median(t)
                         row[name]["nccl_p50_us"] = p50n * 1e3
                         row[name]["nccl_busbw_GBps"] = total_bytes / (p50n * 1e-3) / 1e9 * factor
+                        row[name]["vs_nccl"] = p50n / p50
                 sweep.append(row)
+        del scratch_ref
+        comm.check()
+
+    # ---- the (k, b) grid of the hierarchical allreduce, the MPICH-style reference algorithms as programs on the
+    # GPU, and NCCL pinned to ring / tree: fp32 sum allreduce, p50 of individually timed calls, checked against NCCL
+    grid = []
+    if args.grid and world > 1:
+        refbuf = torch.empty(nelem, dtype=torch.float32, device="cuda")
+        for sz in [int(s) for s in args.grid.split(",") if s]:
+            if sz > S:
+                continue
+            ne = max(N, sz // 4 // N * N)
+            xv, yv = x[:ne], y[:ne]
+            refbuf[:ne].copy_(xv)
+            dist.all_reduce(refbuf[:ne])
+            iters = 5 if sz >= (256 << 20) else args.sweep_iters
+            cands = [("radix_batch", k, b) for b in (1, 2, 4) if N % b == 0 and b <= N for k in (2, 4, 8)]
+            cands += [("recursive_doubling", 2, 1), ("reduce_scatter_allgather", 2, 1), ("ring", 2, 1)]
+            for algo, k, b in cands:
+                rec = {"bytes": ne * 4, "algo": algo, "k": k, "b": b}
+                try:
+                    fn = lambda: chb.all_reduce(comm, xv, out=yv, algo=algo, k=k, b=b)
+                    yv.zero_()
+                    for _ in range(3):
+                        fn()
+                    torch.cuda.synchronize()
+                    comm.check()
+                    rec["is_correct"] = all_ranks_ok(close_enough(yv, refbuf[:ne], torch.float32))
+                    t = [max_over_ranks(v) for v in per_call_ms(fn, iters, flush, barrier)]
+                    p50 = statistics.median(t)
+                    rec.update(p50_us=p50 * 1e3, busbw_GBps=ne * 4 / (p50 * 1e-3) / 1e9 * 2 * (N - 1) / N)
+                except CollectiveError as e:
+                    rec["skipped"] = str(e)[:120]
+                    comm.clear_error()
+                grid.append(rec)
+            if not args.no_nccl:
+                for name, grp in [("nccl_default", None)] + [("nccl_" + n_, g_) for n_, g_ in nccl_groups.items()]:
+                    if name != "nccl_default" and grp is None:
+                        grid.append({"bytes": ne * 4, "algo": name, "skipped": "group could not be created"})
+                        continue
+                    fn = (lambda: dist.all_reduce(yv, group=grp)) if grp is not None else (lambda: dist.all_reduce(yv))
+                    for _ in range(3):
+                        fn()
+                    t = [max_over_ranks(v) for v in per_call_ms(fn, iters, flush, barrier)]
+                    p50 = statistics.median(t)
+                    grid.append({"bytes": ne * 4, "algo": name, "p50_us": p50 * 1e3,
+                                 "busbw_GBps": ne * 4 / (p50 * 1e-3) / 1e9 * 2 * (N - 1) / N})
+        del refbuf
         comm.check()
 
     # ---- launch-free latency: 20 back-to-back allreduces captured in one CUDA graph (small sizes only)
@@ -408,33 +575,33 @@ def main():
         except Exception as e:  # noqa: BLE001 - an optional table must not cost the headline
             graph_lat = [{"error": repr(e)[:200]}]
 
-
     if rank == 0:
         peaks = {}
         try:
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
         except (OSError, ValueError):
             pass
-        # roofline: bytes that must cross NVLink per GPU / measured peer bandwidth (770 GB/s per direction),
-        # or for one GPU the local copy at the measured HBM copy bandwidth
-        if N > 1:
-            ideal_ms = (2 * (N - 1) / N * S) / 770e9 * 1e3
-        else:
-            ideal_ms = (2 * S) / (peaks.get("hbm_gbs", 6650.0) * 1e9) * 1e3
+        rf = roofline(N, S, headline_kernel.algo, ms_per_step, peaks)
+        if args.rows_out:
+            try:
+                with open(args.rows_out, "w") as f:
+                    json.dump({"n_gpus": N, "sweep": sweep, "grid": grid, "graph_replay_latency": graph_lat}, f)
+            except OSError:
+                pass
         out = {
-            "metric": "allreduce_sum_fp32_aggregate_algbw_GBps",
+            "metric": METRIC,
             "value": value, "unit": "GB/s", "n_gpus": N, "steps": K, "warmup": W, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
             "impl": "ours",
-            "config": {"model": "allreduce sum fp32 (config 2 of the sweep: 8 B - 1 GiB)", "bytes_per_gpu": S,
-                       "global_batch": None, "seq_len": None, "parallelism": f"{N} ranks, one per GPU",
-                       "backend": comm.backend, "nvls": comm.has_multicast,
-                       "l2": "inputs larger than L2 for the headline; explicit 256 MiB L2 flush before every timed call in the sweep"},
-            "algbw_GBps": algbw, "busbw_GBps": busbw, "roofline_frac": ideal_ms / ms_per_step,
-            "roofline_note": "of measured (770 GB/s NVLink per direction; HBM copy from MEASURED_PEAKS.json at N=1)",
+            "busbw_GBps": busbw, "algbw_GBps": algbw,
+            "config": headline_config(N, S),
+            "arm": {"ranks": f"{N} ranks, one per GPU", "backend": comm.backend, "nvls": comm.has_multicast,
+                    "headline_kernel": f"{headline_kernel.algo} k={headline_kernel.k} b={headline_kernel.b}"},
+            "roofline": rf,
+            "roofline_frac": rf.get("frac_of_770_measured", rf.get("frac_of_measured")),
             "is_correct": bool(correct), "max_abs_err": err,
-            "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "nccl": nccl, "sweep": sweep,
-            "graph_replay_latency": graph_lat,
+            "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "nccl": nccl,
+            "grid": grid, "sweep": sweep, "graph_replay_latency": graph_lat,
         }
         print(json.dumps(out), flush=True)
     comm.close()

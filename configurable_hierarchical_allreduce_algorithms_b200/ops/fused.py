@@ -17,6 +17,27 @@ N.optional("chb_rs_adam", i32, [vp, C.POINTER(vp), C.POINTER(vp), C.POINTER(vp),
 
 
 N.optional("chb_adam_flat", i32, [vp, vp, vp, vp, vp, C.c_longlong, C.POINTER(f32), vp])
+N.optional("chb_bucket_fill", i32, [vp, i32, C.POINTER(vp), C.POINTER(C.c_longlong), C.POINTER(C.c_longlong),
+                                    C.POINTER(i32), C.POINTER(C.c_ubyte), vp])
+
+
+def bucket_fill(bucket: torch.Tensor, items, stream=None):
+    """One kernel for a whole gradient bucket: ``items`` = (gradient tensor, element offset in the flat fp32
+    ``bucket``, overwrite?) per parameter; bf16 / fp16 / fp32 gradients are cast and either replace their
+    slot or are added to it (``csrc/kernels/bucket.cu``)."""
+    k = len(items)
+    if k == 0:
+        return
+    assert bucket.dtype == torch.float32 and bucket.is_cuda
+    grads = [g if g.is_contiguous() else g.contiguous() for g, _, _ in items]
+    src = (vp * k)(*[g.data_ptr() for g in grads])
+    off = (C.c_longlong * k)(*[int(o) for _, o, _ in items])
+    n = (C.c_longlong * k)(*[g.numel() for g in grads])
+    dt = (i32 * k)(*[DTYPES[g.dtype] for g in grads])
+    ow = (C.c_ubyte * k)(*[1 if w else 0 for _, _, w in items])
+    rc = N.lib().chb_bucket_fill(bucket.data_ptr(), k, src, off, n, dt, ow, _stream_ptr(stream))
+    if rc:
+        raise RuntimeError(f"chb_bucket_fill failed with code {rc}")
 
 
 def adam_flat(grad, master, exp_avg, exp_avg_sq, param_bf16, *, lr, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,

@@ -26,7 +26,8 @@ class _Bucket:
         self.params = []
         self.pending = 0
         self.ready_event = None
-        self.fresh = False                   # True: the next gradient of each parameter overwrites
+        self.fresh = set()                   # parameters whose next gradient overwrites their slot (after zero_grad)
+        self.queued = []                     # (parameter, gradient) pairs not yet moved into the bucket
 
 
 class DataParallel:
@@ -76,14 +77,33 @@ class DataParallel:
     # ------------------------------------------------------------------ hooks
     def _hook(self, p):
         bk, _ = self._where[p]
-        if bk.fresh:
-            p.main_grad.copy_(p.grad)       # first micro-batch: cast only, the bucket needs no zero fill
-        else:
-            p.main_grad.add_(p.grad)        # bf16 (or fp32) gradient accumulated in fp32
+        # the gradient is only queued here; the whole bucket is filled by ONE kernel when its last
+        # gradient has arrived (bf16 / fp16 / fp32 -> fp32, overwrite or accumulate per parameter)
+        bk.queued.append((p, p.grad))
         p.grad = None
         bk.pending -= 1
-        if bk.pending == 0 and self.require_sync:
-            self._reduce(bk)
+        if bk.pending == 0:
+            self._fill(bk)
+            if self.require_sync:
+                self._reduce(bk)
+
+    def _fill(self, bk: _Bucket):
+        """Move the queued gradients into the bucket: fresh slots are overwritten (first micro-batch after
+        ``zero_grad``, so the bucket needs no zero fill), the others accumulate in fp32."""
+        if not bk.queued:
+            return
+        if self.cuda:
+            from ..ops import fused
+            fused.bucket_fill(bk.acc, [(g, self._where[p][1], p in bk.fresh) for p, g in bk.queued])
+        else:
+            for p, g in bk.queued:
+                if p in bk.fresh:
+                    p.main_grad.copy_(g)
+                else:
+                    p.main_grad.add_(g)
+        for p, _ in bk.queued:
+            bk.fresh.discard(p)
+        bk.queued = []
 
     def _reduce(self, bk: _Bucket):
         scale = 1.0 / self.world
@@ -113,9 +133,15 @@ class DataParallel:
     def finish(self):
         """Call after backward: waits for the bucket reductions and re-arms the hooks."""
         for bk in self.buckets:
-            if bk.pending != 0 and self.require_sync:
-                # parameters that received no gradient: reduce what is there
-                self._reduce(bk)
+            if bk.pending != 0:
+                # some parameters received no gradient in this pass: take what arrived, and a slot that
+                # is still fresh holds the previous step's values, so it counts as zero
+                self._fill(bk)
+                if self.require_sync:
+                    for p in list(bk.fresh):
+                        p.main_grad.zero_()
+                    bk.fresh.clear()
+                    self._reduce(bk)
         if self.cuda:
             self._ev_bwd_end = torch.cuda.Event(enable_timing=True)
             self._ev_bwd_end.record()
@@ -125,7 +151,6 @@ class DataParallel:
                 torch.cuda.current_stream().wait_stream(self.side)
         for bk in self.buckets:
             bk.pending = len(bk.params)
-            bk.fresh = False
 
     def exposed_comm_ms(self) -> float:
         """Communication time not hidden behind backward in the last step (after a synchronize)."""
@@ -136,10 +161,11 @@ class DataParallel:
     def zero_grad(self):
         """Start a new accumulation: the first gradient written to a slot replaces its content."""
         for bk in self.buckets:
-            bk.fresh = True
+            bk.fresh = set(bk.params)
 
     def no_sync(self):
-        """Context manager for gradient accumulation: bucket reductions are skipped."""
+        """Context manager for gradient accumulation: bucket reductions are skipped; every backward pass
+        inside still accumulates into the buckets (any number of micro-batches per context)."""
         ddp = self
 
         class _Ctx:
@@ -149,8 +175,8 @@ class DataParallel:
             def __exit__(self, *a):
                 ddp.require_sync = True
                 for bk in ddp.buckets:
+                    ddp._fill(bk)                  # a pass that left some parameters without a gradient
                     bk.pending = len(bk.params)
-                    bk.fresh = False
 
         return _Ctx()
 

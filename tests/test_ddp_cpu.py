@@ -71,3 +71,64 @@ def test_two_ranks_match_single_process():
     opt.step()
     for n, p in ref.named_parameters():
         torch.testing.assert_close(torch.from_numpy(params[n]), p.detach(), rtol=1e-4, atol=1e-5)
+
+
+class _TwoHeads(torch.nn.Module):
+    """A layer that only gets a gradient when ``use_b`` is set."""
+
+    def __init__(self):
+        super().__init__()
+        self.a = torch.nn.Linear(8, 8)
+        self.b = torch.nn.Linear(8, 8)
+
+    def forward(self, x, use_b):
+        y = self.a(x)
+        return (y + self.b(x)).sum() if use_b else y.sum()
+
+
+def test_several_micro_batches_inside_one_no_sync_block_all_count():
+    # single process, world of one: the wrapper's accumulation must equal plain autograd accumulation
+    torch.manual_seed(3)
+    m, ref = _TwoHeads(), _TwoHeads()
+    ref.load_state_dict(m.state_dict())
+    ddp = DataParallel(m, comm=None, bucket_bytes=1 << 8)
+    xs = [torch.randn(2, 8) for _ in range(4)]
+    ddp.zero_grad()
+    with ddp.no_sync():
+        for x in xs[:3]:                      # three backward passes in ONE context
+            ddp(x, True).backward()
+    ddp(xs[3], True).backward()
+    ddp.finish()
+    for x in xs:
+        ref(x, True).backward()
+    for (n, p), (_, q) in zip(m.named_parameters(), ref.named_parameters()):
+        torch.testing.assert_close(p.reduced_grad, q.grad, rtol=1e-5, atol=1e-6, msg=n)
+
+
+def test_parameter_without_gradient_contributes_zero_not_last_steps_values():
+    torch.manual_seed(4)
+    m, ref = _TwoHeads(), _TwoHeads()
+    ref.load_state_dict(m.state_dict())
+    ddp = DataParallel(m, comm=None, bucket_bytes=1 << 8)
+    x = torch.randn(2, 8)
+    ddp.zero_grad()
+    ddp(x, True).backward()                   # step 1: every parameter gets a gradient
+    ddp.finish()
+    ddp.zero_grad()
+    ddp(x, False).backward()                  # step 2: head b is unused
+    ddp.finish()
+    ref(x, False).backward()
+    for (n, p), (_, q) in zip(m.named_parameters(), ref.named_parameters()):
+        exp = q.grad if q.grad is not None else torch.zeros_like(q)
+        torch.testing.assert_close(p.reduced_grad, exp, rtol=1e-5, atol=1e-6, msg=n)
+    # and accumulation across a pass in which b is unused keeps b's earlier contribution
+    ddp.zero_grad()
+    with ddp.no_sync():
+        ddp(x, True).backward()
+        ddp(x, False).backward()
+    ddp(x, False).backward()
+    ddp.finish()
+    ref.zero_grad()
+    ref(x, True).backward(); ref(x, False).backward(); ref(x, False).backward()
+    for (n, p), (_, q) in zip(m.named_parameters(), ref.named_parameters()):
+        torch.testing.assert_close(p.reduced_grad, q.grad, rtol=1e-5, atol=1e-6, msg=n)

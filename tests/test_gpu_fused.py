@@ -80,3 +80,33 @@ def test_adam_flat_matches_torch(cuda):
         opt.step()
         torch.testing.assert_close(master, ref.detach(), rtol=2e-5, atol=2e-6)
         torch.testing.assert_close(pb.float(), ref.detach().bfloat16().float(), rtol=1e-2, atol=1e-2)
+
+
+def test_bucket_fill_casts_overwrites_and_accumulates(cuda):
+    """One launch moves a whole bucket's gradients (mixed dtypes, odd lengths, unaligned offsets) into the
+    flat fp32 buffer; compared with plain PyTorch fp32 arithmetic."""
+    import torch
+
+    from configurable_hierarchical_allreduce_algorithms_b200.ops import fused
+
+    g = torch.Generator(device="cuda").manual_seed(5)
+    sizes = [1, 3, 4, 127, 4096, 100003] + [64] * 60          # more tensors than one launch's table holds
+    dts = [torch.bfloat16, torch.float32, torch.float16]
+    grads = [(torch.rand(n, generator=g, device="cuda") * 2 - 1).to(dts[i % 3]) for i, n in enumerate(sizes)]
+    offs, off = [], 0
+    for n in sizes:
+        offs.append(off)
+        off += (n + 3) // 4 * 4 if n != 3 else 3               # one odd offset: the next slot is not 16-byte aligned
+    bucket = torch.full((off + 8,), 7.0, device="cuda")
+    ref = bucket.clone()
+    ow = [i % 2 == 0 for i in range(len(sizes))]
+    fused.bucket_fill(bucket, [(gr, o, w) for gr, o, w in zip(grads, offs, ow)])
+    for gr, o, w in zip(grads, offs, ow):
+        ref[o:o + gr.numel()] = gr.float() if w else ref[o:o + gr.numel()] + gr.float()
+    torch.cuda.synchronize()
+    assert torch.equal(bucket, ref)
+    # a view of a larger gradient (non-zero storage offset) accumulates as well
+    big = torch.arange(64, device="cuda", dtype=torch.bfloat16)
+    fused.bucket_fill(bucket, [(big[1:33], 0, False)])
+    ref[0:32] += big[1:33].float()
+    assert torch.equal(bucket, ref)

@@ -12,8 +12,10 @@ message sizes double ``n_iter`` times starting from ``base`` elements per rank, 
 ``k = 2 .. b-1`` in steps of ``radix_increment`` for the hierarchical algorithm, every repetition is
 checked against the library collective (``MPI_Allreduce`` there, NCCL / gloo here) and written as one
 CSV row ``algorithm_name,k,b,nprocs,send_count,time,is_correct`` (the same columns, followed by
-``dtype,op,bytes,algbw_GBs,busbw_GBs,ngpus``).  An existing file is appended to unless ``--overwrite``
-is given, and rows are flushed one by one, so an interrupted sweep resumes where it stopped.
+``dtype,op,bytes,algbw_GBs,busbw_GBs,ngpus,p50_us,roofline_frac``: the last two are per configuration, the
+median over its repetitions and the share of the NVLink roofline that median reaches).  An existing file
+is appended to unless ``--overwrite`` is given, and rows are flushed configuration by configuration, so an
+interrupted sweep resumes where it stopped.
 Correctness is AND-reduced and time MAX-reduced over ranks, as in the reference's reduce-scatter
 driver (main.cpp:79-83).  ``symmetric=1`` places input and output in the peer-visible heap (registered
 buffers: nothing is staged, and the kernel-level algorithms ``ll``, ``ll2``, ``nvls``, ``bulk`` can be
@@ -32,7 +34,7 @@ import torch
 import torch.distributed as dist
 
 DT = {"int32": torch.int32, "fp32": torch.float32, "bf16": torch.bfloat16, "fp64": torch.float64, "fp16": torch.float16}
-HEADER = "algorithm_name,k,b,nprocs,send_count,time,is_correct,dtype,op,bytes,algbw_GBs,busbw_GBs,ngpus"
+HEADER = "algorithm_name,k,b,nprocs,send_count,time,is_correct,dtype,op,bytes,algbw_GBs,busbw_GBs,ngpus,p50_us,roofline_frac"
 BASELINES = {
     "allreduce": ["recursive_doubling", "ring", "reduce_scatter_allgather", "k_reduce_scatter_allgather",
                   "recursive_multiplying", "recursive_exchange"],
@@ -142,6 +144,7 @@ def main(argv=None):
         """`reps` timed, checked repetitions of one configuration."""
         send_count = n
         kk, gb = (k or 2), (bb or 1)       # the CSV keeps 0 for "not applicable", the generators need valid values
+        rows = []                          # one row per repetition; written together once their median is known
         for _ in range(o["reps"]):
             if backend == "gpu":
                 dist.barrier()
@@ -202,9 +205,18 @@ def main(argv=None):
                 t = float(tt.item())
                 total = n * P * esz
                 factor = 2 * (P - 1) / P if coll == "allreduce" else (P - 1) / P
-                csv.write(f"{name},{k},{bb},{P},{send_count},{t:.9f},{int(flag[0].item())},{o['dtype']},{op},{total},"
-                          f"{total / t / 1e9:.4f},{total / t / 1e9 * factor:.4f},{P if backend == 'gpu' else 0}\n")
-                csv.flush()
+                rows.append((t, f"{name},{k},{bb},{P},{send_count},{t:.9f},{int(flag[0].item())},{o['dtype']},{op},{total},"
+                                f"{total / t / 1e9:.4f},{total / t / 1e9 * factor:.4f},{P if backend == 'gpu' else 0}"))
+        if rank == 0 and rows:
+            # p50 of the configuration, and the share of the NVLink roofline it reaches: the bytes one GPU must
+            # move per direction (bus-bandwidth factor times the vector) over the measured 770 GB/s peer rate
+            p50 = sorted(t for t, _ in rows)[len(rows) // 2]
+            total = n * P * esz
+            factor = 2 * (P - 1) / P if coll == "allreduce" else (P - 1) / P
+            frac = (total * factor / 770e9) / p50 if backend == "gpu" and P > 1 else 0.0
+            for _, line in rows:
+                csv.write(f"{line},{p50 * 1e6:.3f},{frac:.4f}\n")
+            csv.flush()
 
     def vendor(x):
         if coll == "allreduce":

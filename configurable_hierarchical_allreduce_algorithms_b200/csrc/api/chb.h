@@ -104,6 +104,12 @@ struct chb_comm* chb_comm_create_emulated(int P, size_t ll_payload_bytes, size_t
                                           char* err, int errlen);
 struct chb_comm* chb_comm_create_ipc(struct chb_bootstrap* boot, size_t ll_payload_bytes, size_t scratch_bytes,
                                      size_t user_bytes, char* err, int errlen);
+/* the same with heaps from CUDA's virtual-memory allocator and, if want_multicast and every device supports it, an
+ * NVLink multicast alias (the multimem kernels then work without Python); *code = CHB_ERR_UNSUPPORTED when the
+ * platform has no shareable allocation handles: fall back to chb_comm_create_ipc.  Destroying such a communicator
+ * is collective (the ranks meet before memory is unbound and unmapped). */
+struct chb_comm* chb_comm_create_vmm(struct chb_bootstrap* boot, size_t ll_payload_bytes, size_t scratch_bytes,
+                                     size_t user_bytes, int want_multicast, int* code, char* err, int errlen);
 void chb_comm_destroy(struct chb_comm* c);
 const char* chb_comm_last_error(const struct chb_comm* c);
 int chb_comm_set_timeout_us(struct chb_comm* c, unsigned long long us);

@@ -12,7 +12,14 @@
  * and the call is enqueued on the stream set with chb_set_stream (default
  * stream if never set).  Return value: 0 or a CHB_ERR_* code, like
  * MPI_SUCCESS / MPI_ERR_*.  CHB_IN_PLACE as sendbuf is honoured by
- * reduce-scatter and allreduce.  Counts are 64-bit where the reference's are
+ * reduce-scatter and allreduce (input taken from recvbuf) and by the
+ * allgathers (the rank's block already sits at its slot of recvbuf, as in
+ * MPI); gather and the stand-alone phases answer CHB_ERR_ARG.  All ranks of
+ * one call must pass buffers of the same kind (all inside the communicator's
+ * peer-visible region or all outside it, all in place or none): the schedule
+ * is chosen from the local pointers without cross-rank agreement, and ranks
+ * that disagree would run different schedules and end in a wait that expires.
+ * Counts are 64-bit where the reference's are
  * MPI_Aint and int where the reference's are int (values beyond 2^31 go
  * through chb_collective).
  */

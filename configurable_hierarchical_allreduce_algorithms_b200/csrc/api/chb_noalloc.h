@@ -28,7 +28,10 @@
  *     threads) race on that array and give wrong results: order them;
  *   - the first call on a device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current) and remembers it.  Make
- *     that first call outside of any stream capture;
+ *     that first call outside of any stream capture.  The per-device table of
+ *     remembered addresses is written without a lock: two host threads that
+ *     make the first call on one device at the same time both store the same
+ *     value, which is harmless;
  *   - no cudaMalloc / cudaFree / allocating library routine is called, on the
  *     first call or later.
  *

@@ -217,7 +217,14 @@ static int one(CHB_Comm comm, int coll, const char* algo, const void* sendbuf, v
                CHB_Datatype dt, CHB_Op op, int k, int b, int aux) {
   if (!comm) return CHB_ERR_ARG;
   if (comm->nlocal != 1) { comm->last_error = "reference-compatible calls need one rank per process"; return CHB_ERR_ARG; }
-  const void* in = (sendbuf == CHB_IN_PLACE) ? recvbuf : sendbuf;
+  const void* in = sendbuf;
+  if (sendbuf == CHB_IN_PLACE) {
+    // MPI's meaning: reductions take their input from recvbuf; an allgather finds each rank's block already at
+    // its slot of recvbuf.  A gather or a stand-alone phase has no in-place form.
+    if (coll == CHB_ALLREDUCE || coll == CHB_REDUCE_SCATTER) in = recvbuf;
+    else if (coll == CHB_ALLGATHER) in = (const char*)recvbuf + (int64_t)comm->rank * count * chb_dtype_size(dt);
+    else { comm->last_error = "CHB_IN_PLACE is defined for allreduce, reduce-scatter and allgather only"; return CHB_ERR_ARG; }
+  }
   return chb_collective(comm, coll, algo, k, b, aux, dt, op, &in, &recvbuf, count, 1.0f, 0, g_compat_stream);
 }
 

@@ -114,6 +114,7 @@ int chb_bootstrap_create(const char* name, int rank, int world, int timeout_ms, 
 
 int chb_bootstrap_rank(const chb_bootstrap* b) { return b ? b->rank : -1; }
 int chb_bootstrap_world(const chb_bootstrap* b) { return b ? b->world : 0; }
+const char* chb_bootstrap_name(const chb_bootstrap* b) { return b ? b->name.c_str() : ""; }
 
 int chb_bootstrap_barrier(chb_bootstrap* b) {
   if (!b) return CHB_ERR_ARG;

@@ -24,9 +24,15 @@ typedef struct chb_bootstrap chb_bootstrap;
 int chb_bootstrap_create(const char* name, int rank, int world, int timeout_ms, chb_bootstrap** out);
 int chb_bootstrap_rank(const chb_bootstrap* b);
 int chb_bootstrap_world(const chb_bootstrap* b);
+const char* chb_bootstrap_name(const chb_bootstrap* b);
 /* all[r * bytes .. ) = rank r's `mine`; bytes <= CHB_BOOT_SLOT_BYTES. */
 int chb_bootstrap_allgather(chb_bootstrap* b, const void* mine, void* all, size_t bytes);
 int chb_bootstrap_barrier(chb_bootstrap* b);
+/* File descriptors cross process boundaries as ancillary data of Unix datagrams (SCM_RIGHTS); every rank
+ * listens on an abstract socket derived from the rendezvous name.  my_fd < 0: this rank has nothing to hand
+ * out.  On return fds[r] is this process's duplicate of rank r's descriptor (-1 if r offered none; fds[rank]
+ * is my_fd itself).  The caller closes what it receives.  Bounded by the rendezvous timeout. */
+int chb_bootstrap_exchange_fds(chb_bootstrap* b, int my_fd, int* fds);
 /* Tell the others to give up (their current or next wait returns CHB_ERR_OTHER at once). */
 void chb_bootstrap_abort(chb_bootstrap* b);
 void chb_bootstrap_destroy(chb_bootstrap* b);

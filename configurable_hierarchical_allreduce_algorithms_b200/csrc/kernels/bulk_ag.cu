@@ -104,6 +104,8 @@ ag_bulk_kernel(World w, BulkIo io, long long nbytes) {
       bulk_load(smem_addr(stage[k % kBulkStages]), src, bytes, bar);
     }
     bool failed = false;
+    long long issued = pre;                          // loads started so far (items 0 .. issued-1)
+    long long k_failed = -1;
     for (long long k = 0; k < mine && !failed; ++k) {
       const int s = (int)(k % kBulkStages);
       const unsigned bar = smem_addr(&bars[s]);
@@ -115,6 +117,7 @@ ag_bulk_kernel(World w, BulkIo io, long long nbytes) {
           if ((++spins & 63u) == 0u && globaltimer_ns() - t0 > w.timeout_ns) {
             record_timeout(c, ST_TIMEOUT_ROUND, rank, (int)k, -3, (unsigned long long)k, 0ull);
             failed = true;
+            k_failed = k;
             break;
           }
         }
@@ -131,7 +134,24 @@ ag_bulk_kernel(World w, BulkIo io, long long nbytes) {
         item(j + kBulkStages, src, dst, bytes);
         mbar_expect_tx(barj, bytes);
         bulk_load(smem_addr(stage[sj]), src, bytes, barj);
+        issued = j + kBulkStages + 1;
       }
+    }
+    if (failed) {
+      // Loads k_failed .. issued-1 may still be writing this CTA's shared memory: give each one more bounded
+      // wait before the CTA (and with it the shared memory) goes away; what is still pending after that is
+      // noted in the status word (seen = number of loads that never completed).
+      unsigned long long pending = 0;
+      for (long long i = k_failed; i < issued; ++i) {
+        const unsigned bar = smem_addr(&bars[i % kBulkStages]);
+        const unsigned parity = (unsigned)((i / kBulkStages) & 1);
+        const unsigned long long t0 = globaltimer_ns();
+        bool done = mbar_try_wait(bar, parity);
+        unsigned spins = 0;
+        while (!done && !((++spins & 63u) == 0u && globaltimer_ns() - t0 > w.timeout_ns)) done = mbar_try_wait(bar, parity);
+        if (!done) ++pending;
+      }
+      c->status[5] = pending;
     }
     bulk_wait_all();                                 // all my stores have landed
     if (failed) ok = false;

@@ -185,10 +185,13 @@ int chb_allreduce_oneshot_noalloc(int P, int dtype, int op, const void* const* i
   NaFn fn = pick(dtype);
   if (!fn) { std::snprintf(msg, sizeof msg, "unknown dtype %d", dtype); return fail(CHB_ERR_ARG); }
   if (op < OP_SUM || op > OP_PROD) { std::snprintf(msg, sizeof msg, "unknown reduction %d", op); return fail(CHB_ERR_OP); }
-  const long long nbytes = (long long)count * dtype_size(dtype);
-  if (count < 0 || nbytes > CHB_NOALLOC_MAX_BYTES) {
-    std::snprintf(msg, sizeof msg, "%lld bytes per rank exceed the fixed scratch capacity of %d bytes; "
-                  "use a communicator for larger messages", nbytes, CHB_NOALLOC_MAX_BYTES);
+  // the range test comes before the multiplication: a huge count must not wrap around to a small size
+  const long long max_count = CHB_NOALLOC_MAX_BYTES / dtype_size(dtype);
+  const long long nbytes = (count < 0 || count > max_count) ? -1 : (long long)count * dtype_size(dtype);
+  if (nbytes < 0) {
+    std::snprintf(msg, sizeof msg, "%lld elements per rank exceed the fixed scratch capacity of %d bytes "
+                  "(%lld elements of this type); use a communicator for larger messages",
+                  (long long)count, CHB_NOALLOC_MAX_BYTES, max_count);
     return fail(CHB_ERR_COUNT);
   }
   NaIo io{};
@@ -203,11 +206,15 @@ int chb_allreduce_oneshot_noalloc(int P, int dtype, int op, const void* const* i
   if (nbytes == 0) return CHB_SUCCESS;
   unsigned char* scratch = scratch_for_current_device(msg, sizeof msg);
   if (!scratch) return fail(CHB_ERR_CUDA);
-  // The array still holds the previous call's flags and status: clear the
-  // control words and the inboxes of the P ranks in stream order.
-  cudaError_t e = cudaMemsetAsync(scratch, 0, (size_t)(kNaCtrlBytes + (long long)P * kNaInboxPerRank), stream);
-  if (e != cudaSuccess) { std::snprintf(msg, sizeof msg, "clearing the scratch array failed: %s", cudaGetErrorString(e)); return fail(CHB_ERR_CUDA); }
+  // The array still holds the previous call's flags and status: clear, in stream order, the control
+  // words and exactly the lines this call uses.  The inbox is a table of (destination, source) rows of
+  // kNaLines lines each; the first nlines lines of the rows of the P destinations are one 2-D fill.
   const long long nlines = (nbytes + 7) / 8;
+  cudaError_t e = cudaMemsetAsync(scratch, 0, (size_t)kNaCtrlBytes, stream);
+  if (e == cudaSuccess)
+    e = cudaMemset2DAsync(scratch + kNaCtrlBytes, (size_t)(kNaLines * 16), 0, (size_t)(nlines * 16),
+                          (size_t)P * CHB_NOALLOC_MAX_RANKS, stream);
+  if (e != cudaSuccess) { std::snprintf(msg, sizeof msg, "clearing the scratch array failed: %s", cudaGetErrorString(e)); return fail(CHB_ERR_CUDA); }
   int nctas = (int)((nlines + kNaThreads - 1) / kNaThreads);
   if (nctas > 4) nctas = 4;
   dim3 grid((unsigned)nctas, (unsigned)P, 1), block(kNaThreads, 1, 1);

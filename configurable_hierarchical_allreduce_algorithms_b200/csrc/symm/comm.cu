@@ -7,6 +7,7 @@
 #include "../api/chb.h"
 #include "../boot/bootstrap.h"
 #include "comm.h"
+#include "vmm.h"
 
 using namespace chb;
 
@@ -128,6 +129,7 @@ void chb_comm_destroy(chb_comm* c) {
   if (c->trace) cudaFree(c->trace);
   for (void* q : c->ipc_opened) cudaIpcCloseMemHandle(q);
   if (c->owned_heap) cudaFree(c->owned_heap);
+  if (c->vmm) chb_vmm_destroy(c->vmm);      // collective: every rank destroys its communicator
   delete c;
 }
 
@@ -317,6 +319,47 @@ chb_comm* chb_comm_create_ipc(chb_bootstrap* boot, size_t ll_payload_bytes, size
   c->ipc_opened = opened;
   // nobody signals into a heap before every rank has set up
   if (chb_bootstrap_barrier(boot) != CHB_SUCCESS) { chb_comm_destroy(c); return fail("ranks did not all finish the set-up"); }
+  return c;
+}
+
+// One rank per process and per GPU of one box, heaps from the virtual-memory allocator (symm/vmm.cc): peers are
+// mapped through shareable allocation handles, and when every device supports it the heaps also get an
+// NVLink multicast alias, so that the multimem kernels run without Python.  want_multicast: 0 / 1.
+// Returns NULL with CHB_ERR_UNSUPPORTED in *code (if given) when the platform lacks shareable handles: callers
+// fall back to chb_comm_create_ipc.
+chb_comm* chb_comm_create_vmm(chb_bootstrap* boot, size_t ll_payload_bytes, size_t scratch_bytes, size_t user_bytes,
+                              int want_multicast, int* code, char* err, int errlen) {
+  auto fail = [&](int rc, const std::string& m) -> chb_comm* {
+    if (code) *code = rc;
+    if (err && errlen > 0) std::snprintf(err, (size_t)errlen, "%s", m.c_str());
+    return nullptr;
+  };
+  if (code) *code = CHB_SUCCESS;
+  if (!boot) return fail(CHB_ERR_ARG, "null bootstrap");
+  const int P = chb_bootstrap_world(boot), rank = chb_bootstrap_rank(boot);
+  if (P < 1 || P > kMaxRanks) return fail(CHB_ERR_ARG, "number of ranks must be between 1 and 16");
+  cudaFree(nullptr);                                   // the primary context exists before the driver API is used
+  const size_t hb = chb_heap_bytes(P, ll_payload_bytes, scratch_bytes, user_bytes);
+  chb_vmm_heap* heap = nullptr;
+  char why[256] = {0};
+  int rc = chb_vmm_create(boot, hb, want_multicast, &heap, why, sizeof why);
+  if (rc) return fail(rc, why);
+  // pads and inboxes start at zero, and nobody signals into a heap before every rank has cleared its own
+  if (cudaMemset(chb_vmm_ptr(heap, rank), 0, chb_vmm_bytes(heap)) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+    chb_bootstrap_abort(boot);
+    return fail(CHB_ERR_CUDA, "clearing the heap failed");
+  }
+  if (chb_bootstrap_barrier(boot)) return fail(CHB_ERR_OTHER, "ranks did not all finish the set-up");
+  void* ptrs[kMaxRanks];
+  for (int p = 0; p < P; ++p) ptrs[p] = chb_vmm_ptr(heap, p);
+  chb_comm* c = chb_comm_create(rank, P, 1, ptrs, chb_vmm_multicast_ptr(heap), ll_payload_bytes, scratch_bytes, user_bytes, err, errlen);
+  if (!c) {
+    chb_bootstrap_abort(boot);
+    if (code) *code = CHB_ERR_OTHER;
+    return nullptr;
+  }
+  c->vmm = heap;
+  if (chb_bootstrap_barrier(boot) != CHB_SUCCESS) { chb_comm_destroy(c); return fail(CHB_ERR_OTHER, "ranks did not all finish the set-up"); }
   return c;
 }
 

@@ -45,6 +45,7 @@ struct chb_comm {
   // set only by the native constructors (chb_comm_create_ipc / chb_comm_create_emulated), which own the heap
   void* owned_heap = nullptr;
   std::vector<void*> ipc_opened;
+  struct chb_vmm_heap* vmm = nullptr;   // heaps (and multicast alias) from the virtual-memory allocator
 
   char* sig_ptr(int p) const { return heap[p]; }
   char* ll_ptr(int p) const { return heap[p] + sig_bytes; }

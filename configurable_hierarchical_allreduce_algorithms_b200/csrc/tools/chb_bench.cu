@@ -232,7 +232,7 @@ int run(const Opts& o, chb_comm* comm, chb_bootstrap* boot, int P, int rank0, in
     const bool fresh = o.overwrite || access(path.c_str(), F_OK) != 0;
     csv = std::fopen(path.c_str(), fresh ? "w" : "a");
     if (!csv) { std::fprintf(stderr, "cannot open %s\n", path.c_str()); return 1; }
-    if (fresh) std::fprintf(csv, "algorithm_name,k,b,nprocs,send_count,time,is_correct,dtype,op,bytes,algbw_GBs,busbw_GBs,ngpus\n");
+    if (fresh) std::fprintf(csv, "algorithm_name,k,b,nprocs,send_count,time,is_correct,dtype,op,bytes,algbw_GBs,busbw_GBs,ngpus,p50_us,roofline_frac\n");
   }
   std::vector<std::string> algos = split(o.algos);
   if (algos.empty()) {
@@ -254,6 +254,20 @@ int run(const Opts& o, chb_comm* comm, chb_bootstrap* boot, int P, int rank0, in
     const long long count = coll == CHB_ALLREDUCE ? n * P : n;       // chb_collective's count convention
     const long long n_out = coll == CHB_REDUCE_SCATTER ? n : n * P;
     const int kk = k ? k : 2, gb = bb ? bb : 1;
+    std::vector<std::pair<double, std::string>> rows;    // one per repetition, written once their median is known
+    auto flush_rows = [&]() {
+      if (!csv || rows.empty()) return;
+      std::vector<double> ts;
+      for (auto& r : rows) ts.push_back(r.first);
+      std::sort(ts.begin(), ts.end());
+      const double p50 = ts[ts.size() / 2];
+      // share of the NVLink roofline: bytes one GPU moves per direction over the measured 770 GB/s peer rate
+      const double total = (double)n * P * d->size;
+      const double factor = coll == CHB_ALLREDUCE ? 2.0 * (P - 1) / P : (double)(P - 1) / P;
+      const double frac = (ngpus > 1 && P > 1) ? (total * factor / 770e9) / p50 : 0.0;
+      for (auto& r : rows) std::fprintf(csv, "%s,%.3f,%.4f\n", r.second.c_str(), p50 * 1e6, frac);
+      std::fflush(csv);
+    };
     for (int rep = 0; rep < o.reps; ++rep) {
       for (int l = 0; l < nlocal; ++l) cudaMemsetAsync(out[l], 0xFF, (size_t)n_out * d->size);
       cudaDeviceSynchronize();
@@ -294,11 +308,13 @@ int run(const Opts& o, chb_comm* comm, chb_bootstrap* boot, int P, int rank0, in
       if (csv) {
         const double total = (double)n * P * d->size;
         const double factor = coll == CHB_ALLREDUCE ? 2.0 * (P - 1) / P : (double)(P - 1) / P;
-        std::fprintf(csv, "%s,%d,%d,%d,%lld,%.9f,%d,%s,%s,%.0f,%.4f,%.4f,%d\n", name.c_str(), k, bb, P, n, t, ok, d->name,
-                     o.op.c_str(), total, total / t / 1e9, total / t / 1e9 * factor, ngpus);
-        std::fflush(csv);
+        char line[512];
+        std::snprintf(line, sizeof line, "%s,%d,%d,%d,%lld,%.9f,%d,%s,%s,%.0f,%.4f,%.4f,%d", name.c_str(), k, bb, P, n, t, ok,
+                      d->name, o.op.c_str(), total, total / t / 1e9, total / t / 1e9 * factor, ngpus);
+        rows.emplace_back(t, line);
       }
     }
+    flush_rows();
     return 0;
   };
 
@@ -374,7 +390,18 @@ int main(int argc, char** argv) {
       chb_bootstrap* boot = nullptr;
       if (chb_bootstrap_create(name, r, P, 60000, &boot)) { std::fprintf(stderr, "rank %d: rendezvous failed\n", r); _exit(1); }
       const size_t total = (size_t)(o.base << std::max(0, o.n_iter - 1)) * P * esz;
-      chb_comm* c = chb_comm_create_ipc(boot, 1 << 20, 4 * total + (32u << 20), o.symmetric ? 2 * total + 4096 : 4096, err, sizeof err);
+      // heaps from the virtual-memory allocator (with the NVLink multicast alias where the devices have one, so that
+      // algos=nvls works here too); cudaIpc heaps where shareable allocation handles are missing, or with CHB_VMM=0
+      chb_comm* c = nullptr;
+      const char* vmm_env = std::getenv("CHB_VMM");
+      if (!vmm_env || std::strcmp(vmm_env, "0") != 0) {
+        const char* nvls_env = std::getenv("CHB_NVLS");
+        int code = 0;
+        c = chb_comm_create_vmm(boot, 1 << 20, 4 * total + (32u << 20), o.symmetric ? 2 * total + 4096 : 4096,
+                                (nvls_env && !std::strcmp(nvls_env, "0")) ? 0 : 1, &code, err, sizeof err);
+        if (!c && code != CHB_ERR_UNSUPPORTED) { std::fprintf(stderr, "rank %d: communicator: %s\n", r, err); chb_bootstrap_destroy(boot); _exit(1); }
+      }
+      if (!c) c = chb_comm_create_ipc(boot, 1 << 20, 4 * total + (32u << 20), o.symmetric ? 2 * total + 4096 : 4096, err, sizeof err);
       if (!c) { std::fprintf(stderr, "rank %d: communicator: %s\n", r, err); chb_bootstrap_destroy(boot); _exit(1); }
       int rc = run(o, c, boot, P, r, 1, P);
       if (rc == 1) chb_bootstrap_abort(boot);      // the others stop waiting for this rank

@@ -57,6 +57,7 @@ N.optional("chb_bootstrap_create", i32, [C.c_char_p, i32, i32, i32, C.POINTER(vp
 N.optional("chb_bootstrap_barrier", i32, [vp])
 N.optional("chb_bootstrap_destroy", None, [vp])
 N.optional("chb_comm_create_ipc", vp, [vp, C.c_size_t, C.c_size_t, C.c_size_t, C.c_char_p, i32])
+N.optional("chb_comm_create_vmm", vp, [vp, C.c_size_t, C.c_size_t, C.c_size_t, i32, C.POINTER(i32), C.c_char_p, i32])
 N.optional("chb_nvls_collective", i32, [vp, i32, i32, vp, vp, C.c_longlong, f32, i32, vp])
 
 DTYPES = {
@@ -187,10 +188,13 @@ class Communicator:
     @classmethod
     def from_shared_memory(cls, name: str, rank: int, world: int, ll_bytes: int = 1 << 20,
                            scratch_bytes: int = 256 << 20, user_bytes: int = 64 << 20,
-                           timeout_us: int = 10_000_000, rendezvous_timeout_ms: int = 60_000):
+                           timeout_us: int = 10_000_000, rendezvous_timeout_ms: int = 60_000,
+                           heap: str = "auto", multicast: bool = True):
         """One rank per process without ``torch.distributed``: the ranks of one box meet through the
-        native shared-memory bootstrap (``name`` = "/something", the same on every rank, unique per job)
-        and exchange cudaIpc handles of their heaps there.  The path the native launcher uses."""
+        native shared-memory bootstrap (``name`` = "/something", the same on every rank, unique per job).
+        ``heap="vmm"``: heaps from CUDA's virtual-memory allocator, shared as file descriptors, with an NVLink
+        multicast alias when ``multicast`` and every device has one (the ``multimem`` kernels then run);
+        ``heap="ipc"``: cudaIpc handles; ``"auto"``: vmm, else ipc.  The path the native launcher uses."""
         L = N.lib()
         if not hasattr(L, "chb_comm_create_ipc"):
             raise N.NativeLibraryMissing("libchb.so was built without its CUDA half")
@@ -204,12 +208,24 @@ class Communicator:
             raise CollectiveError(rc, f"rendezvous '{name}' of {world} ranks failed")
         self._boot = boot
         err = C.create_string_buffer(256)
-        h = L.chb_comm_create_ipc(boot, ll_bytes, scratch_bytes, user_bytes, err, len(err))
+        h = None
+        self.backend = "ipc-native"
+        if heap in ("auto", "vmm") and os.environ.get("CHB_VMM", "1") != "0":
+            code = i32(0)
+            want_mc = 1 if (multicast and os.environ.get("CHB_NVLS", "1") != "0") else 0
+            h = L.chb_comm_create_vmm(boot, ll_bytes, scratch_bytes, user_bytes, want_mc, C.byref(code), err, len(err))
+            if h:
+                self.backend = "vmm-native"
+            elif heap == "vmm" or code.value != N.ERR_UNSUPPORTED:
+                L.chb_bootstrap_destroy(boot)
+                self._boot = None
+                raise CollectiveError(code.value or N.ERR_OTHER, err.value.decode())
+        if not h:
+            h = L.chb_comm_create_ipc(boot, ll_bytes, scratch_bytes, user_bytes, err, len(err))
         if not h:
             L.chb_bootstrap_destroy(boot)
             self._boot = None
             raise CollectiveError(N.ERR_OTHER, err.value.decode())
-        self.backend = "ipc-native"
         self._adopt(h, world, rank, 1, dev, timeout_us)
         return self
 

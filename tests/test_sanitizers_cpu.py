@@ -65,7 +65,7 @@ def test_bootstrap_under_asan_ubsan(tmp_path):
                         str(ROOT / "tests" / "native" / "bootstrap_test.c"), "-o", str(obj)], capture_output=True, text=True)
     assert r.returncode == 0, r.stderr[-3000:]
     exe = tmp_path / "bootstrap_san"
-    r = subprocess.run([CXX, "-std=c++17", "-O1", "-g", *flags, "-I", str(CSRC), str(obj), str(CSRC / "boot" / "bootstrap.cc"),
+    r = subprocess.run([CXX, "-std=c++17", "-O1", "-g", *flags, "-I", str(CSRC), str(obj), str(CSRC / "boot" / "bootstrap.cc"), str(CSRC / "boot" / "fdpass.cc"),
                         "-o", str(exe), "-lpthread", "-lrt"], capture_output=True, text=True)
     assert r.returncode == 0, r.stderr[-3000:]
     r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)

@@ -73,6 +73,16 @@ def test_matches_communicator_kernel_on_two_calls_in_a_row(cuda):
             assert torch.cuda.memory_allocated() == before
             want = chb.all_reduce(comm, ins, op=op, algo="ll", scale=scale)
             torch.cuda.synchronize()
+            # an oracle that is none of this library's kernels: the same reduction in fp64 / int64 by PyTorch
+            hi = torch.float64 if dtype.is_floating_point else torch.int64
+            st = torch.stack([x.to(hi) for x in ins])
+            oracle = (st.sum(0) if op == "sum" else st.max(0).values) * (scale if dtype.is_floating_point else 1)
+            for r in range(P):
+                if dtype.is_floating_point:
+                    tol = {torch.float32: 1e-5, torch.bfloat16: 2e-2}[dtype]
+                    torch.testing.assert_close(outs[r].double(), oracle, rtol=tol, atol=tol * P)
+                else:
+                    assert torch.equal(outs[r].to(hi), oracle)
             for r in range(P):
                 if dtype.is_floating_point:
                     tol = {torch.float32: 1e-5, torch.bfloat16: 2e-2}[dtype]
@@ -94,6 +104,14 @@ def test_refuses_what_does_not_fit(cuda):
     many = _inputs(MAX_RANKS + 1, 8, torch.float32, 2)
     rc, msg = _call(fn, many, [torch.zeros_like(x) for x in many])
     assert rc == N.ERR_COUNT and "capacity" in msg
+    # a count so large that count * element size wraps around is refused like any other, not taken for a small one
+    small = _inputs(2, 8, torch.float32, 4)
+    souts = [torch.zeros_like(x) for x in small]
+    err = C.create_string_buffer(256)
+    rc = fn(2, DTYPES[torch.float32], OPS["sum"], (C.c_void_p * 2)(*[t.data_ptr() for t in small]),
+            (C.c_void_p * 2)(*[t.data_ptr() for t in souts]), 1 << 62, 1.0,
+            torch.cuda.current_stream().cuda_stream, err, len(err))
+    assert rc == N.ERR_COUNT and "exceed" in err.value.decode()
     # the largest request that fits works
     ins = _inputs(MAX_RANKS, MAX_BYTES // 4, torch.float32, 3)
     outs = [torch.zeros_like(x) for x in ins]

@@ -434,12 +434,13 @@ def main():
         tol_ = (1e-5 if dtype == torch.float32 else 2e-2) * max(N, 1)
         return bool(torch.allclose(a.float(), b.float(), rtol=tol_, atol=tol_))
 
-    if args.sweep:
-        scratch_ref = torch.empty(min(nelem, 1 << 26), dtype=torch.float32, device="cuda")   # NCCL's output for the checks
+    scratch_ref = torch.empty(min(nelem, 1 << 26), dtype=torch.float32, device="cuda") if args.sweep else None   # NCCL's output for the checks
+
+    def run_sweep(dtype, dname):
         for sz in [int(s) for s in args.sweep.split(",") if s]:
             if sz > S:
                 continue
-            for dtype, dname in ((torch.float32, "fp32"), (torch.bfloat16, "bf16")):
+            if True:
                 esz = 4 if dtype == torch.float32 else 2
                 ne = max(1, sz // esz)
                 ne_rs = max(1, ne // max(N, 1))
@@ -485,8 +486,10 @@ def main():
                         row[name]["nccl_busbw_GBps"] = total_bytes / (p50n * 1e-3) / 1e9 * factor
                         row[name]["vs_nccl"] = p50n / p50
                 sweep.append(row)
-        del scratch_ref
         comm.check()
+
+    if args.sweep:
+        run_sweep(torch.float32, "fp32")
 
     # ---- the (k, b) grid of the hierarchical allreduce, the MPICH-style reference algorithms as programs on the
     # GPU, and NCCL pinned to ring / tree: fp32 sum allreduce, p50 of individually timed calls, checked against NCCL
@@ -574,6 +577,18 @@ def main():
             comm.check()
         except Exception as e:  # noqa: BLE001 - an optional table must not cost the headline
             graph_lat = [{"error": repr(e)[:200]}]
+
+    # ---- the same table on bf16 data: the input buffer is refilled with bf16 values first (an fp32 vector seen as
+    # bf16 would be full of NaN and huge values), which is why this comes after everything that wants the fp32 input
+    if args.sweep:
+        g = torch.Generator(device="cuda").manual_seed(4321 + rank)
+        xb = x.view(torch.bfloat16)
+        half = xb.numel() // 2
+        for lo in (0, half):                                   # in two pieces: no second full-size temporary
+            xb[lo:lo + half].copy_((torch.rand(half, generator=g, device="cuda") * 2 - 1).to(torch.bfloat16))
+        run_sweep(torch.bfloat16, "bf16")
+        sweep.sort(key=lambda r: (r["bytes"], r["dtype"] != "fp32"))
+    scratch_ref = None
 
     if rank == 0:
         peaks = {}

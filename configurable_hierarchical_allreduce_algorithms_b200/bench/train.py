@@ -39,6 +39,8 @@ def main(argv=None):
     ap.add_argument("--algo", default="auto")
     ap.add_argument("--k", type=int, default=2)
     ap.add_argument("--b", type=int, default=1)
+    ap.add_argument("--comm-ctas", type=int, default=0, help="dp: CTAs of each bucket's allreduce kernel (0 = its own choice)")
+    ap.add_argument("--out", default="", help="append the JSON line to this file as well")
     args = ap.parse_args(argv)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -72,7 +74,7 @@ def main(argv=None):
         topt = torch.optim.AdamW(model.parameters(), lr=3e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
         ddp, opt = None, None
     elif args.mode == "dp":
-        ddp = DataParallel(model, comm=comm if ours else None, algo=args.algo, k=args.k, b=args.b)
+        ddp = DataParallel(model, comm=comm if ours else None, algo=args.algo, k=args.k, b=args.b, comm_ctas=args.comm_ctas)
         if not ours:
             ddp.cuda = False     # library collectives on CUDA tensors through torch.distributed
         opt = FusedMasterAdamW(ddp) if ours else MasterAdamW(ddp)
@@ -136,8 +138,13 @@ def main(argv=None):
             "exposed_comm_ms": exposed[-1] if exposed else None,
             "collective_launches": (comm.launches - l0) if comm else None,
             "h2d_bytes_per_step": mb * T * 8, "d2h_bytes_per_step": 4, "wall_ms_per_step": wall * 1e3 / args.steps,
-            "algo": args.algo, "k": args.k, "b": args.b, "data": "synthetic"}
+            "algo": args.algo, "k": args.k, "b": args.b, "comm_ctas": args.comm_ctas, "data": "synthetic"}
+        if args.mode == "zero" and ours:
+            out["param_allgather"] = "%s k=%d b=%d" % opt.ag_choice()
         print(json.dumps(out), flush=True)
+        if args.out:
+            with open(args.out, "a") as f:
+                f.write(json.dumps(out) + "\n")
     if comm:
         comm.close()
     if world > 1:

@@ -30,8 +30,21 @@ from ..utils import autotune
 DT = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}
 
 
-def candidates(coll: str, P: int, nbytes: int, comm) -> list[tuple]:
-    """(algo, k, b, nctas) tuples worth timing for this cell."""
+def canonical(k: int, b: int) -> tuple[int, int]:
+    """(k, b) cells that compile to the same program share one measurement: without groups (b = 1) the radix
+    plays no part, and a radix above the group size behaves like the group size (one phase either way)."""
+    return (2, 1) if b <= 1 else (min(k, b), b)
+
+
+def grid_cells(P: int) -> list[tuple[int, int]]:
+    """The k in {2, 4, 8} x b in {1, 2, 4} grid (plus b = P), as distinct programs."""
+    return sorted({canonical(k, b) for b in (1, 2, 4, P) if b <= P and P % b == 0 for k in (2, 4, 8)})
+
+
+def candidates(coll: str, P: int, nbytes: int, comm, total: int | None = None) -> list[tuple]:
+    """(algo, k, b, nctas) tuples worth timing for this cell.  ``nbytes``: payload per rank pair (the size
+    the tuned table is keyed by); ``total``: bytes of the whole vector."""
+    total = total if total is not None else nbytes
     out = []
     if nbytes <= comm.ll_max_bytes:
         out.append(("ll", 2, 1, 0))
@@ -39,29 +52,30 @@ def candidates(coll: str, P: int, nbytes: int, comm) -> list[tuple]:
         out.append(("ll2", 2, 1, 0))
         if nbytes >= (1 << 20):
             out.append(("ll2", 2, 1, 64))
-    divs = [b for b in (1, 2, 4, 8) if P % b == 0 and b <= P]
-    for b in divs:
-        ks = sorted({2, 4, max(2, b)}) if b > 2 else [2]
-        for k in ks:
-            if nbytes <= (256 << 10):
-                out.append(("radix_batch", k, b, 1))
-                out.append(("radix_batch", k, b, 4))
-            elif nbytes <= (4 << 20):
-                for n in (4, 16, 32):
-                    out.append(("radix_batch", k, b, n))
-            else:
-                for n in (32, 64, 128):
-                    out.append(("radix_batch", k, b, n))
+    for k, b in grid_cells(P):
+        flat = b == 1
+        if total <= (4 << 20):                       # owners push flagged lines: one traversal per round
+            out.append(("radix_batch:ll", k, b, 0))
+        if total <= (64 << 10):                      # readers pull: the persistent interpreter
+            out.append(("radix_batch:pull", k, b, 1))
+        elif total <= (4 << 20):
+            out += [("radix_batch:pull", k, b, n) for n in ((8, 32) if flat else (16,))]
+        else:
+            out += [("radix_batch:pull", k, b, n) for n in ((32, 64, 128) if flat else (64,))]
     if comm.has_multicast and nbytes % 16 == 0 and nbytes >= 16 * P:
-        for n in ((1, 4, 16) if nbytes <= (1 << 20) else (8, 16, 24, 32, 64)):
+        for n in ((1, 4, 16) if nbytes <= (1 << 20) else (8, 16, 32, 64)):
             out.append(("nvls", 2, 1, n))
             if coll == "allreduce" and nbytes <= (4 << 20):
                 out.append(("nvls1", 2, 1, n))
     if coll == "allgather" and nbytes % 16 == 0 and nbytes >= (1 << 20):
         for n in (64, 128):
             out.append(("bulk", 2, 1, n))
-    if coll == "allreduce" and nbytes <= (4 << 20):
-        out += [("recursive_doubling", 2, 1, 1 if nbytes <= (1 << 20) else 16)]
+    if coll == "allreduce":                          # the reference's MPICH-style baselines as programs on the GPU
+        for a in ("recursive_doubling", "reduce_scatter_allgather"):
+            if total <= (4 << 20):
+                out.append((a + ":ll", 2, 1, 0))
+            else:
+                out.append((a + ":pull", 2, 1, 64))
     return out
 
 
@@ -94,6 +108,8 @@ def main(argv=None):
     ap.add_argument("--out", default=str(autotune.DEFAULT_TABLE))
     ap.add_argument("--csv", default="")
     ap.add_argument("--no-save", action="store_true")
+    ap.add_argument("--no-nccl-algos", action="store_true", help="skip the NCCL ring / tree rows")
+    ap.add_argument("--md", default="", help="write a markdown summary (winners, the (k, b) grid, NCCL) to this file")
     args = ap.parse_args(argv)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -104,8 +120,22 @@ def main(argv=None):
     dist.init_process_group("nccl", device_id=torch.device("cuda", lr))
     sizes = [int(s) for s in args.sizes.split(",") if s]
     smax = max(sizes)
-    comm = Communicator.from_process_group(scratch_bytes=smax + (32 << 20), user_bytes=2 * smax + (64 << 20))
+    comm = Communicator.from_process_group(scratch_bytes=2 * smax + (32 << 20), user_bytes=2 * smax + (64 << 20))
     P = comm.P
+    nccl_groups = {}
+    if world > 1 and not args.no_nccl_algos:
+        for name in ("Ring", "Tree"):                  # NCCL pinned to one algorithm: read when a group's communicator is set up
+            try:
+                os.environ["NCCL_ALGO"] = name
+                grp = dist.new_group(ranks=list(range(world)), backend="nccl")
+                dist.all_reduce(torch.ones(8, device="cuda"), group=grp)
+                torch.cuda.synchronize()
+                nccl_groups[name.lower()] = grp
+            except Exception as e:  # noqa: BLE001
+                if rank == 0:
+                    print(f"# NCCL_ALGO={name}: {e!r}"[:200], flush=True)
+            finally:
+                os.environ.pop("NCCL_ALGO", None)
     xb = comm.empty(smax, torch.uint8)
     yb = comm.empty(smax, torch.uint8)
     xb.copy_(torch.randint(0, 60, (smax,), device="cuda", dtype=torch.uint8))
@@ -123,28 +153,60 @@ def main(argv=None):
                     xin, yout, payload = x[:n * P], y[:n * P], n * P * esz
                     call = lambda a, k, b, c: all_reduce(comm, xin, out=yout, algo=a, k=k, b=b, nctas=c)
                     ref = lambda: dist.all_reduce(yout)
+                    ref_g = lambda g_: dist.all_reduce(yout, group=g_)
                     factor = 2 * (P - 1) / P
                 elif coll == "reduce_scatter":
                     xin, yout, payload = x[:n * P], y[:n], n * esz
                     call = lambda a, k, b, c: reduce_scatter(comm, xin, out=yout, algo=a, k=k, b=b, nctas=c)
                     ref = lambda: dist.reduce_scatter_tensor(yout, xin)
+                    ref_g = lambda g_: dist.reduce_scatter_tensor(yout, xin, group=g_)
                     factor = (P - 1) / P
                 else:
                     xin, yout, payload = x[:n], y[:n * P], n * esz
                     call = lambda a, k, b, c: all_gather(comm, xin, out=yout, algo=a, k=k, b=b, nctas=c)
                     ref = lambda: dist.all_gather_into_tensor(yout, xin)
+                    ref_g = lambda g_: dist.all_gather_into_tensor(yout, xin, group=g_)
                     factor = (P - 1) / P
                 total = n * P * esz
+                expected = None
+                if total <= (64 << 20):                    # NCCL's result for this cell, kept for the checks below
+                    if coll == "allreduce":
+                        expected = xin.clone()
+                        dist.all_reduce(expected)
+                    elif coll == "reduce_scatter":
+                        expected = torch.empty_like(yout)
+                        dist.reduce_scatter_tensor(expected, xin)
+                    else:
+                        expected = torch.empty_like(yout)
+                        dist.all_gather_into_tensor(expected, xin)
                 for _ in range(3):
                     ref()
                 t_nccl = time_call(ref, args.iters, world)
                 best = None
-                for (a, k, b, c) in candidates(coll, P, payload, comm):
+                for gname, grp in nccl_groups.items():
+                    for _ in range(3):
+                        ref_g(grp)
+                    tg = time_call(lambda: ref_g(grp), args.iters, world)
+                    rows.append([f"{coll}_nccl_{gname}", 0, 0, P, n, tg * 1e-3, 1, dname, "sum", total,
+                                 total / (tg * 1e-3) / 1e9, total / (tg * 1e-3) / 1e9 * factor, tg * 1e3, P, 0])
+                for (a, k, b, c) in candidates(coll, P, payload, comm, total):
                     try:
                         for _ in range(2):
                             call(a, k, b, c)
+                        ok = 1
+                        if expected is not None:           # the candidate's output against NCCL's, all ranks
+                            tol = (1e-5 if dname == "fp32" else 2e-2) * P
+                            flag = torch.tensor([1 if torch.allclose(yout.float(), expected.float(), rtol=tol, atol=1e-30) else 0], device="cuda")
+                            if world > 1:
+                                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                            ok = int(flag.item())
                         t = time_call(lambda: call(a, k, b, c), args.iters, world)
                         comm.check()
+                        if not ok:
+                            if rank == 0:
+                                print(f"# WRONG RESULT {coll} {a} k={k} b={b} ctas={c} {dname} {total} B", flush=True)
+                            rows.append([f"{coll}_{a}", k, b, P, n, t * 1e-3, 0, dname, "sum", total, 0, 0, t * 1e3, P, c])
+                            continue
                     except CollectiveError as e:
                         if rank == 0:
                             print(f"# skip {coll} {a} k={k} b={b}: {e}", flush=True)
@@ -184,12 +246,70 @@ def main(argv=None):
                 w.writerow(["algorithm_name", "k", "b", "nprocs", "send_count", "time", "is_correct", "dtype", "op",
                             "bytes", "algbw_GBs", "busbw_GBs", "p50_us", "ngpus", "nctas"])
                 w.writerows(rows)
+        if args.md:
+            write_markdown(args.md, rows, P, gpu, " ".join(sys.argv if argv is None else ["tune"] + list(argv)))
         table = autotune.build_table(samples, gpu, P)
         if not args.no_save:
             autotune.save_table(table, args.out)
         print(json.dumps(table))
     comm.close()
     dist.destroy_process_group()
+
+
+def write_markdown(path: str, rows: list, P: int, gpu: str, cmdline: str) -> None:
+    """Winners per cell, the best time of every (k, b) shape of the hierarchical algorithm, and NCCL (its default
+    and pinned to ring / tree), from the rows of one sweep."""
+    import collections
+
+    cells = collections.OrderedDict()
+    for r in rows:
+        name, k, b, _, _, t, ok, dname, _, total = r[:10]
+        ctas = r[14] if len(r) > 14 else 0
+        coll = next(c for c in ("allreduce", "reduce_scatter", "allgather") if name.startswith(c))
+        cells.setdefault((coll, dname, int(total)), []).append((name[len(coll) + 1:], int(k), int(b), int(ctas), float(t) * 1e6, int(ok)))
+    L = [f"# Sweep on {P} x {gpu}: median device time per call (us), max over ranks", "",
+         "Made by (from the repository root, on the GPUs named above):", "", "```",
+         f"python -m torch.distributed.run --nnodes=1 --nproc-per-node {P} --master-addr 127.0.0.1 -m "
+         f"configurable_hierarchical_allreduce_algorithms_b200.bench.tune {cmdline.split('tune', 1)[-1].strip()}", "```", "",
+         "Size = bytes of the whole vector (allreduce) or of all P blocks (reduce-scatter, allgather).  `rb` = the hierarchical",
+         "radix-k / group-b program (`radix_batch`), `:ll` = owners push flagged lines, `:pull` = readers pull (persistent",
+         "interpreter).  Cells of the k x b grid that compile to the same program are measured once: b = 1 ignores k, and a radix",
+         "above the group size equals the group size.  A row with a wrong result is listed as WRONG and never wins.", ""]
+    for coll in ("allreduce", "reduce_scatter", "allgather"):
+        for dname in sorted({c[1] for c in cells}):
+            sizes = sorted({c[2] for c in cells if c[0] == coll and c[1] == dname})
+            if not sizes:
+                continue
+            shapes = sorted({(k, b) for (c, d, _), v in cells.items() if c == coll and d == dname for (a, k, b, _, _, _) in v if a.startswith("radix_batch")})
+            L += [f"## {coll}, {dname}", "",
+                  "| size | best of this library | us | best rb cell | us | NCCL | ring | tree | best / NCCL | best rb / NCCL |",
+                  "|---|---|---|---|---|---|---|---|---|---|"]
+            for sz in sizes:
+                v = cells[(coll, dname, sz)]
+                ours = [x for x in v if not x[0].startswith("nccl") and x[0] != "fp8wire" and x[5] == 1]
+                rb = [x for x in ours if x[0].startswith("radix_batch")]
+                nc = {x[0]: x[4] for x in v if x[0].startswith("nccl")}
+                if not ours or "nccl" not in nc:
+                    continue
+                bo, br = min(ours, key=lambda x: x[4]), (min(rb, key=lambda x: x[4]) if rb else None)
+                fmt = lambda x: f"{x[0]} k={x[1]} b={x[2]} ctas={x[3]}"
+                L.append(f"| {sz} | {fmt(bo)} | {bo[4]:.1f} | {fmt(br) if br else '-'} | {br[4] if br else 0:.1f} | {nc['nccl']:.1f} | "
+                         f"{nc.get('nccl_ring', 0):.1f} | {nc.get('nccl_tree', 0):.1f} | {nc['nccl'] / bo[4]:.2f}x | "
+                         f"{(nc['nccl'] / br[4]) if br else 0:.2f}x |")
+            L += ["", "Best time (us) of every (k, b) shape over its execution modes and CTA counts:", "",
+                  "| size | " + " | ".join(f"k={k} b={b}" for k, b in shapes) + " | recursive doubling | Rabenseifner |",
+                  "|---|" + "---|" * (len(shapes) + 2)]
+            for sz in sizes:
+                v = cells[(coll, dname, sz)]
+                def best(pred):
+                    xs = [x[4] for x in v if pred(x) and x[5] == 1]
+                    bad = any(pred(x) and x[5] != 1 for x in v)
+                    return (f"{min(xs):.1f}" if xs else "-") + (" (WRONG rows)" if bad else "")
+                L.append(f"| {sz} | " + " | ".join(best(lambda x, k=k, b=b: x[0].startswith("radix_batch") and (x[1], x[2]) == (k, b)) for k, b in shapes)
+                         + f" | {best(lambda x: x[0].startswith('recursive_doubling'))} | {best(lambda x: x[0].startswith('reduce_scatter_allgather'))} |")
+            L.append("")
+    with open(path, "w") as f:
+        f.write("\n".join(L) + "\n")
 
 
 if __name__ == "__main__":

@@ -132,9 +132,9 @@ static std::vector<char> make_blob(const Program& p) {
 // ------------------------------------------------------------------ one step (or one tile of it)
 // Elements [e0, e0 + cnt) of step `st`, strided over `nparts` CTAs of which this one is `part`.
 // Sources are combined left to right (the order in which the reference receives and reduces), but
-// their loads are issued kSrcGroup sources at a time, so that a step with k-1 or P-1 remote sources
-// keeps that many NVLink round trips in flight per thread instead of one.
-constexpr int kSrcGroup = 4;
+// their loads are issued kSrcGroup sources at a time and two vectors deep, so that every thread keeps
+// 128 bytes of NVLink round trips in flight whether a step has one remote source or P-1 of them.
+constexpr int kSrcGroup = 2;
 
 template <typename T>
 __device__ __forceinline__ void run_step(const DevStep& st, const DevSrc* __restrict__ srcs, const World& w,
@@ -212,7 +212,7 @@ __device__ __forceinline__ void run_step(const DevStep& st, const DevSrc* __rest
         d += UC * stride;
       }
     }
-    constexpr int UW = 1;
+    constexpr int UW = 2;
     for (; j0 < nw; j0 += TT * UW) {
       Acc a[UW][2][VE];
       for (int s = 0; s < nsrc; s += G) {
@@ -592,7 +592,9 @@ int chb_run_program(chb_comm* c, const chb_program* p, int dtype, int op, const 
   if (nctas <= 0) {
     // enough CTAs to keep NVLink busy for large steps, one for latency-bound programs
     long long bytes = (long long)std::max(g.in_elems, g.out_elems) * (long long)esz;
-    nctas = bytes <= (64 << 10) ? 1 : (bytes <= (1 << 20) ? 8 : (bytes <= (16 << 20) ? 32 : 64));
+    // NVLink wants about 2 MB in flight per GPU (rate x loaded latency) and a thread keeps 128 bytes in flight:
+    // bandwidth-bound sizes take (nearly) every SM, one CTA each
+    nctas = bytes <= (64 << 10) ? 1 : (bytes <= (1 << 20) ? 16 : (bytes <= (4 << 20) ? 64 : 128));
     // a single-rank world only copies locally: HBM-bound, wants every SM
     if (c->P == 1 && bytes > (16 << 20)) nctas = per_rank_budget;
   }

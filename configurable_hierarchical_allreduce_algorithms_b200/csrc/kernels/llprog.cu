@@ -17,7 +17,17 @@
 //   2. execute my steps of level t: local sources are loaded, remote ones are
 //      polled in the inbox, combined left to right, stored once.
 // Steps of one level never conflict (the lowering guarantees it), so 1 and 2 of
-// the same level need no ordering; levels are separated by a rank-local barrier.
+// the same level need no ordering.
+//
+// Levels overlap line by line.  When a region that a peer reads at level t + 1
+// lies inside the destination of one of my steps of level t, the thread that
+// produces a line of that step forwards it to the peer at once, from registers:
+// the peer's next round starts on line c as soon as line c of this round
+// exists, not when the round is complete (the reference waits for whole rounds:
+// MPI_Waitall at testing/custom_implementations/work_dir/all_reduce/all_reduce_radix_batch.cpp:622).
+// A rank-local barrier separates two levels only where the later one reads or
+// overwrites local memory that the earlier one wrote or read; for the flat
+// two-round allreduce, for instance, none is left.
 // Owners push from inside their own launch, so an input is never read before
 // its owner's stream has produced it, and nobody reads a peer's buffers: no
 // entry handshake, no exit waits, no staging of caller buffers.
@@ -41,13 +51,15 @@ namespace chb {
 
 constexpr int kLPThreads = 512;
 
-struct LPLevel { int step_begin, step_end, send_begin, send_end; long long step_lines, send_lines; };
-struct LPStep { long long dst_off, count, line_prefix; int dst_buf, nsrc, src_begin; unsigned flags; };
+struct LPLevel { int step_begin, step_end, send_begin, send_end; long long step_lines, send_lines; int barrier_before, pad; };
+struct LPStep { long long dst_off, count, line_prefix; int dst_buf, nsrc, src_begin; unsigned flags; int fwd_begin, nfwd; };
+// lines [line_begin, line_begin + nlines) of a step's result go to inbox_line.. of dst_rank as they are produced
+struct LPFwd { long long line_begin, nlines, inbox_line; int dst_rank, pad; };
 struct LPSrc { long long off, inbox_line; int peer, buf; };          // inbox_line < 0: local source
 struct LPSend { long long src_off, count, inbox_line, line_prefix; int dst_rank, src_buf; };
 struct LPHeader {
   int P, nlevels, nsteps, nsrcs, nsends, esz;
-  long long off_levels, off_steps, off_srcs, off_sends;
+  long long off_levels, off_steps, off_srcs, off_sends, off_fwds;
   long long max_level_lines;     // busiest (rank, level): lines pushed + lines executed
   long long inbox_lines;         // lines needed in the fullest inbox
 };
@@ -100,6 +112,66 @@ static std::vector<char> make_ll_blob(const Program& p, int esz, LPHeader* hout)
       lv.step_end = (int)steps.size();
       lv.step_lines = pre;
     }
+  // forwarding: a send of level t + 1 whose source lies inside the destination of ONE step of level t (same
+  // buffer, offset difference a whole number of lines) is issued by that step's threads instead
+  std::vector<std::vector<LPFwd>> fwd_of(steps.size());
+  for (int r = 0; r < P; ++r)
+    for (int t = 0; t + 1 < T; ++t) {
+      const LPLevel& lv = levels[(size_t)r * T + t];
+      std::vector<LPSend>& next = sends_of[(size_t)r * T + t + 1];
+      std::vector<LPSend> keep;
+      for (const LPSend& sd : next) {
+        bool done = false;
+        for (int si = lv.step_begin; si < lv.step_end && !done; ++si) {
+          const LPStep& st = steps[(size_t)si];
+          if (st.dst_buf != sd.src_buf || sd.src_off < st.dst_off || sd.src_off + sd.count > st.dst_off + st.count) continue;
+          const long long delta = (sd.src_off - st.dst_off) * esz;
+          if (delta % 8) continue;
+          fwd_of[(size_t)si].push_back(LPFwd{delta / 8, lines_of(sd.count, esz), sd.inbox_line, sd.dst_rank, 0});
+          done = true;
+        }
+        if (!done) keep.push_back(sd);
+      }
+      next.swap(keep);
+    }
+  std::vector<LPFwd> fwds;
+  for (size_t si = 0; si < steps.size(); ++si) {
+    steps[si].fwd_begin = (int)fwds.size();
+    steps[si].nfwd = (int)fwd_of[si].size();
+    for (const LPFwd& f : fwd_of[si]) fwds.push_back(f);
+  }
+  // barriers: before level t only if it reads local memory written since the last barrier, or overwrites local
+  // memory read or written since then (the caller's input is never written; inbox lines carry their own flags)
+  struct Reg { int buf; long long lo, hi; };
+  auto hits = [](const std::vector<Reg>& a, const Reg& x) {
+    for (const Reg& y : a)
+      if (y.buf == x.buf && x.lo < y.hi && y.lo < x.hi) return true;
+    return false;
+  };
+  for (int r = 0; r < P; ++r) {
+    std::vector<Reg> wr, rd;
+    for (int t = 0; t < T; ++t) {
+      LPLevel& lv = levels[(size_t)r * T + t];
+      std::vector<Reg> reads, writes;
+      for (int si = lv.step_begin; si < lv.step_end; ++si) {
+        const LPStep& st = steps[(size_t)si];
+        writes.push_back(Reg{st.dst_buf, st.dst_off, st.dst_off + st.count});
+        if (st.flags & 0x100u) reads.push_back(Reg{st.dst_buf, st.dst_off, st.dst_off + st.count});
+        for (int j = 0; j < st.nsrc; ++j) {
+          const LPSrc& x = srcs[(size_t)st.src_begin + j];
+          if (x.inbox_line < 0) reads.push_back(Reg{x.buf, x.off, x.off + st.count});
+        }
+      }
+      for (const LPSend& sd : sends_of[(size_t)r * T + t]) reads.push_back(Reg{sd.src_buf, sd.src_off, sd.src_off + sd.count});
+      bool need = false;
+      for (const Reg& x : reads) need = need || hits(wr, x);
+      for (const Reg& x : writes) need = need || hits(wr, x) || hits(rd, x);
+      lv.barrier_before = (t > 0 && need) ? 1 : 0;
+      if (lv.barrier_before) { wr.clear(); rd.clear(); }
+      wr.insert(wr.end(), writes.begin(), writes.end());
+      rd.insert(rd.end(), reads.begin(), reads.end());
+    }
+  }
   std::vector<LPSend> sends;
   for (int r = 0; r < P; ++r)
     for (int t = 0; t < T; ++t) {
@@ -128,6 +200,7 @@ static std::vector<char> make_ll_blob(const Program& p, int esz, LPHeader* hout)
   h.off_steps = (long long)off;  off = al(off + steps.size() * sizeof(LPStep));
   h.off_srcs = (long long)off;   off = al(off + srcs.size() * sizeof(LPSrc));
   h.off_sends = (long long)off;  off = al(off + sends.size() * sizeof(LPSend));
+  h.off_fwds = (long long)off;   off = al(off + fwds.size() * sizeof(LPFwd));
   std::vector<char> blob(off, 0);
   std::memcpy(blob.data(), &h, sizeof(h));
   auto put = [&](long long o, const void* src, size_t n) { if (n) std::memcpy(blob.data() + o, src, n); };
@@ -135,6 +208,7 @@ static std::vector<char> make_ll_blob(const Program& p, int esz, LPHeader* hout)
   put(h.off_steps, steps.data(), steps.size() * sizeof(LPStep));
   put(h.off_srcs, srcs.data(), srcs.size() * sizeof(LPSrc));
   put(h.off_sends, sends.data(), sends.size() * sizeof(LPSend));
+  put(h.off_fwds, fwds.data(), fwds.size() * sizeof(LPFwd));
   *hout = h;
   return blob;
 }
@@ -165,12 +239,13 @@ llprog_kernel(World w, const char* __restrict__ blob, LPIo io, int op, float sca
   const LPStep* steps = reinterpret_cast<const LPStep*>(blob + h->off_steps);
   const LPSrc* srcs = reinterpret_cast<const LPSrc*>(blob + h->off_srcs);
   const LPSend* sends = reinterpret_cast<const LPSend*>(blob + h->off_sends);
+  const LPFwd* fwds = reinterpret_cast<const LPFwd*>(blob + h->off_fwds);
   __shared__ unsigned long long s_seq;
   __shared__ int s_abort;
   if (threadIdx.x == 0) { s_seq = ld_volatile_u64(&c->ll_seq); s_abort = ld_volatile_u32(&c->abort); }
   __syncthreads();
   const unsigned long long seq = s_seq;
-  bool ok = s_abort == 0;
+  bool dead = s_abort != 0;                 // this thread does no more work (an expired wait, or an aborted rank)
   const unsigned flag = (unsigned)(seq % 0xFFFFFFFFull) + 1u;
   const long long half = (long long)(seq & 1ull) * w.P * lines_per_src;
   const long long TT = (long long)nct * blockDim.x;
@@ -182,20 +257,38 @@ llprog_kernel(World w, const char* __restrict__ blob, LPIo io, int op, float sca
   const char* inbox = w.ll[rank] + half * 16;
   unsigned gen = 0;
 
-  for (int t = 0; t < nlevels && ok; ++t) {
+  for (int t = 0; t < nlevels; ++t) {
     const LPLevel L = levels[t];
-    // ---- 1. push what peers' steps of this level read from me
-    for (long long gl = gtid; gl < L.send_lines; gl += TT) {
-      const LPSend S = sends[find_item(sends, L.send_begin, L.send_end, gl)];
-      const long long l = gl - S.line_prefix;
-      const char* base = (S.src_buf == 0 ? my_in : (S.src_buf == 1 ? my_out : my_work)) + S.src_off * (long long)sizeof(T);
-      const uint2 v = load_payload(base, l * 8, S.count * (long long)sizeof(T));
-      st_line(w.ll[S.dst_rank] + (half + S.inbox_line + l) * 16, v.x, v.y, flag);
+    // a level that touches local memory of the levels before it starts only when those are complete on this rank;
+    // all threads take part in the barrier, also those that have given up, and an aborted rank leaves here together
+    if (L.barrier_before && !rank_barrier(c, nct, gen, w.timeout_ns, rank, t)) break;
+    // ---- 1. push what peers' steps of this level read from me (and no step of mine has forwarded already)
+    {
+      int cur = -1;
+      LPSend S{};
+      long long end = 0;
+      for (long long gl = gtid; gl < L.send_lines && !dead; gl += TT) {
+        if (cur < 0 || gl >= end) {
+          cur = find_item(sends, L.send_begin, L.send_end, gl);
+          S = sends[cur];
+          end = S.line_prefix + (S.count * (long long)sizeof(T) + 7) / 8;
+        }
+        const long long l = gl - S.line_prefix;
+        const char* base = (S.src_buf == 0 ? my_in : (S.src_buf == 1 ? my_out : my_work)) + S.src_off * (long long)sizeof(T);
+        const uint2 v = load_payload(base, l * 8, S.count * (long long)sizeof(T));
+        st_line(w.ll[S.dst_rank] + (half + S.inbox_line + l) * 16, v.x, v.y, flag);
+      }
     }
     // ---- 2. my steps of this level
-    bool failed = false;
-    for (long long gl = gtid; gl < L.step_lines && !failed; gl += TT) {
-      const LPStep st = steps[find_item(steps, L.step_begin, L.step_end, gl)];
+    int cur = -1;
+    LPStep st{};
+    long long end = 0;
+    for (long long gl = gtid; gl < L.step_lines && !dead; gl += TT) {
+      if (cur < 0 || gl >= end) {
+        cur = find_item(steps, L.step_begin, L.step_end, gl);
+        st = steps[cur];
+        end = st.line_prefix + (st.count * (long long)sizeof(T) + 7) / 8;
+      }
       const long long l = gl - st.line_prefix;
       const long long nbytes = st.count * (long long)sizeof(T);
       char* dst = (st.dst_buf == 1 ? my_out : my_work) + st.dst_off * (long long)sizeof(T);
@@ -205,25 +298,29 @@ llprog_kernel(World w, const char* __restrict__ blob, LPIo io, int op, float sca
       bool have = false;
       if (acc) { payload_to_acc<T>(load_payload(dst, l * 8, nbytes), a); have = true; }
       for (int j = 0; j < st.nsrc; ++j) {
-        const LPSrc s = srcs[st.src_begin + j];
-        if (s.inbox_line < 0) {
-          const char* base = (s.buf == 0 ? my_in : (s.buf == 1 ? my_out : my_work)) + s.off * (long long)sizeof(T);
+        const LPSrc sc = srcs[st.src_begin + j];
+        if (sc.inbox_line < 0) {
+          const char* base = (sc.buf == 0 ? my_in : (sc.buf == 1 ? my_out : my_work)) + sc.off * (long long)sizeof(T);
           v = load_payload(base, l * 8, nbytes);
-        } else if (!poll_line(inbox + (s.inbox_line + l) * 16, flag, v, c, w.timeout_ns, rank, l, s.peer)) {
-          failed = true;
+        } else if (!poll_line(inbox + (sc.inbox_line + l) * 16, flag, v, c, w.timeout_ns, rank, l, sc.peer)) {
+          dead = true;
           break;
         }
         if (!have) { payload_to_acc<T>(v, a); have = true; }
         else payload_combine<T>(op, v, a);
       }
-      if (failed) break;
+      if (dead) break;
       // a plain copy keeps the payload's bits; everything else goes through the accumulator type
       if (acc || st.nsrc > 1 || (do_scale && (st.flags & OPF_FINAL)))
         v = acc_to_payload<T>(a, scale, do_scale && (st.flags & OPF_FINAL));
       store_payload(dst, l * 8, nbytes, v);
+      // the next level's readers of this line get it now, from registers
+      for (int f = 0; f < st.nfwd; ++f) {
+        const LPFwd F = fwds[st.fwd_begin + f];
+        const long long lf = l - F.line_begin;
+        if (lf >= 0 && lf < F.nlines) st_line(w.ll[F.dst_rank] + (half + F.inbox_line + lf) * 16, v.x, v.y, flag);
+      }
     }
-    // ---- levels are ordered on this rank; a failed wait ends the launch for all its CTAs
-    if (t + 1 < nlevels) ok = rank_barrier(c, nct, gen, w.timeout_ns, rank, t);
   }
   rank_exit(c, nct, [&](Ctrl* cc) { cc->ll_seq = seq + 1ull; });
 }

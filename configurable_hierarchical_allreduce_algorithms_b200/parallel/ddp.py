@@ -32,9 +32,11 @@ class _Bucket:
 
 class DataParallel:
     def __init__(self, module: torch.nn.Module, comm=None, bucket_bytes: int = 25 << 20, overlap: bool = True,
-                 algo: str = "auto", k: int = 2, b: int = 1, group=None):
+                 algo: str = "auto", k: int = 2, b: int = 1, group=None, comm_ctas: int = 0):
+        """``comm_ctas``: CTAs of each bucket's allreduce kernel (0 = the kernel's own choice).  A small number
+        leaves the SMs and HBM bandwidth to the backward kernels it overlaps with."""
         self.module, self.comm, self.group = module, comm, group
-        self.algo, self.k, self.b, self.overlap = algo, k, b, overlap
+        self.algo, self.k, self.b, self.overlap, self.comm_ctas = algo, k, b, overlap, comm_ctas
         self.world = comm.P if comm is not None else (dist.get_world_size(group) if dist.is_initialized() else 1)
         self.cuda = comm is not None
         self.side = torch.cuda.Stream() if self.cuda else None
@@ -122,7 +124,7 @@ class DataParallel:
         else:
             stream = None
         collectives.all_reduce(self.comm, bk.acc, out=bk.red, algo=self.algo, k=self.k, b=self.b, scale=scale,
-                               stream=stream)
+                               nctas=self.comm_ctas, stream=stream)
 
     # ------------------------------------------------------------------ step protocol
     def forward(self, *a, **kw):

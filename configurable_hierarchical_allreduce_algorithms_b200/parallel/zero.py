@@ -49,6 +49,9 @@ class ShardedAdamW:
             self.param_flat = torch.zeros(total, dtype=self.params[0].dtype, device=dev)
         self.grad_flat.zero_()
         self.param_flat.zero_()
+        self._off = dict(zip(self.params, offs))
+        self._queued = []                  # (parameter, gradient) pairs not yet moved into the flat buffer
+        self._fresh = set()                # parameters whose next gradient overwrites its slot (after zero_grad)
         for p, off in zip(self.params, offs):
             self.param_flat[off:off + p.numel()].copy_(p.detach().reshape(-1))
             p.data = self.param_flat[off:off + p.numel()].view_as(p)     # the model now lives in the flat buffer
@@ -60,17 +63,54 @@ class ShardedAdamW:
         self.exp_avg_sq = torch.zeros(self.n, device=dev)
         self.t = 0
 
-    @staticmethod
-    def _hook(p):
-        p.main_grad.add_(p.grad)
+    _FLUSH_AT = 48                         # gradients per fill kernel (one launch's table)
+
+    def _hook(self, p):
+        # queued, then moved in groups by one multi-tensor kernel (bf16 -> fp32, overwrite or accumulate)
+        self._queued.append((p, p.grad))
         p.grad = None
+        if len(self._queued) >= self._FLUSH_AT:
+            self._flush()
+
+    def _flush(self):
+        if not self._queued:
+            return
+        if self.comm is not None and self.grad_flat.is_cuda:
+            fused.bucket_fill(self.grad_flat, [(g, self._off[p], p in self._fresh) for p, g in self._queued])
+        else:
+            for p, g in self._queued:
+                if p in self._fresh:
+                    p.main_grad.copy_(g)
+                else:
+                    p.main_grad.add_(g)
+        for p, _ in self._queued:
+            self._fresh.discard(p)
+        self._queued = []
 
     def zero_grad(self):
-        self.grad_flat.zero_()
+        """Start a new accumulation without touching memory: the first gradient of every parameter
+        overwrites its slot; slots that receive none are cleared when the step is taken."""
+        self._flush()
+        self._fresh = set(self.params)
+
+    def ag_choice(self):
+        """(algorithm, k, b) the parameter allgather runs with: the pinned one, or what the tuned table
+        answers for this shard size."""
+        if self.comm is None:
+            return ("library", 0, 0)
+        if self.ag_algo != "auto":
+            return (self.ag_algo, self.ag_k, self.ag_b)
+        from ..utils import autotune
+        c = autotune.choose(self.comm, "allgather", self.n * self.param_flat.element_size(), self.param_flat.dtype, True)
+        return (c.algo, c.k, c.b)
 
     @torch.no_grad()
     def step(self, stream=None):
         self.t += 1
+        self._flush()
+        for p in self._fresh:              # no gradient since zero_grad: the slot still holds the previous step's values
+            p.main_grad.zero_()
+        self._fresh = set()
         lo = self.rank * self.n
         shard = self.param_flat[lo:lo + self.n]
         if self.comm is not None:

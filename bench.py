@@ -504,6 +504,8 @@ def main():
             refbuf[:ne].copy_(xv)
             dist.all_reduce(refbuf[:ne])
             iters = 5 if sz >= (256 << 20) else args.sweep_iters
+            # the same amount of back-to-back warm-up calls as in the sweep: the first calls after an idle spell are slow
+            n_warm = min(100, max(3, int(20e-3 / (20e-6 + ne * 4 / 2e11))))
             cands = [("radix_batch", k, b) for b in (1, 2, 4) if N % b == 0 and b <= N for k in (2, 4, 8)]
             cands += [("recursive_doubling", 2, 1), ("reduce_scatter_allgather", 2, 1), ("ring", 2, 1)]
             for algo, k, b in cands:
@@ -511,7 +513,7 @@ def main():
                 try:
                     fn = lambda: chb.all_reduce(comm, xv, out=yv, algo=algo, k=k, b=b)
                     yv.zero_()
-                    for _ in range(3):
+                    for _ in range(n_warm):
                         fn()
                     torch.cuda.synchronize()
                     comm.check()
@@ -529,7 +531,7 @@ def main():
                         grid.append({"bytes": ne * 4, "algo": name, "skipped": "group could not be created"})
                         continue
                     fn = (lambda: dist.all_reduce(yv, group=grp)) if grp is not None else (lambda: dist.all_reduce(yv))
-                    for _ in range(3):
+                    for _ in range(n_warm):
                         fn()
                     t = [max_over_ranks(v) for v in per_call_ms(fn, iters, flush, barrier)]
                     p50 = statistics.median(t)

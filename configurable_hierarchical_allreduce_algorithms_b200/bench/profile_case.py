@@ -3,7 +3,8 @@ on it): a few launches of one kernel, inputs larger than L2, about a GB held.
 
     python -m configurable_hierarchical_allreduce_algorithms_b200.bench.profile_case --case interp_ar [--mib 32]
       interp_ar  8 emulated ranks, allreduce radix_batch k=2 b=1 on symmetric buffers (program interpreter)
-      interp_kb  same with k=2 b=4 (hierarchical schedule)
+      interp_kb  same with k=2 b=4 (hierarchical schedule: entry round + five rounds, pull interpreter)
+      llprog_ar  8 emulated ranks, allreduce radix_batch k=2 b=2 of 256 KiB with flagged lines (four rounds, push)
       ll_ar      8 emulated ranks, one-shot flagged-line allreduce of 64 KiB
       ll2_ar     8 emulated ranks, two-shot flagged-line allreduce of 1 MiB
       fp8_rs     4 emulated ranks, fp8 block-scaled wire reduce-scatter, --mib MiB of bf16 per rank
@@ -33,17 +34,20 @@ def main():
     a = ap.parse_args()
     torch.cuda.set_device(0)
     n = (a.mib << 20) // 4
-    if a.case in ("interp_ar", "interp_kb", "ll_ar", "ll2_ar"):
+    if a.case in ("interp_ar", "interp_kb", "ll_ar", "ll2_ar", "llprog_ar"):
         P = 8
         if a.case == "ll_ar":
             n = (64 << 10) // 4
         if a.case == "ll2_ar":
             n = (1 << 20) // 4
+        if a.case == "llprog_ar":
+            n = (256 << 10) // 4
         comm = Communicator.emulated(P, scratch_bytes=n * 4 + (8 << 20), user_bytes=2 * n * 4 + (1 << 20))
         xs, ys = comm.empty(n, torch.float32), comm.empty(n, torch.float32)
         for i, x in enumerate(xs):
             x.copy_(torch.rand(n, device="cuda") + i)
-        kw = {"interp_ar": dict(algo="radix_batch", k=2, b=1), "interp_kb": dict(algo="radix_batch", k=2, b=4),
+        kw = {"interp_ar": dict(algo="radix_batch:pull", k=2, b=1), "interp_kb": dict(algo="radix_batch:pull", k=2, b=4),
+              "llprog_ar": dict(algo="radix_batch:ll", k=2, b=2),
               "ll_ar": dict(algo="ll"), "ll2_ar": dict(algo="ll2")}[a.case]
         fn = lambda: all_reduce(comm, xs, out=ys, **kw)
         nbytes = n * 4

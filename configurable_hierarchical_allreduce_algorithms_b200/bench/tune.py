@@ -184,6 +184,8 @@ def main(argv=None):
                 t_nccl = time_call(ref, args.iters, world)
                 best = None
                 for gname, grp in nccl_groups.items():
+                    if gname == "tree" and coll != "allreduce":
+                        continue                           # NCCL has no tree form of reduce-scatter / allgather
                     for _ in range(3):
                         ref_g(grp)
                     tg = time_call(lambda: ref_g(grp), args.iters, world)

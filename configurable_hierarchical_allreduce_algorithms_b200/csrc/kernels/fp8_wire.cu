@@ -192,7 +192,7 @@ fp8_rs_kernel(World w, Fp8Io io, long long n, float out_scale) {
       // egress instead of every rank starting at rank 0)
       for (int j0 = 0; j0 < P - 1; j0 += kPeerBatch) {
         uint2 packed[kPeerBatch][U];
-        float sc[kPeerBatch][U];
+        float sc_lane[kPeerBatch];     // lane u of a half-warp holds the scale of its group u: one request per peer, not U
 #pragma unroll
         for (int jj = 0; jj < kPeerBatch; ++jj) {
           const int j = j0 + jj;
@@ -206,9 +206,14 @@ fp8_rs_kernel(World w, Fp8Io io, long long n, float out_scale) {
             const long long gg = (long long)rank * gpb + g0 + u;
             const bool lv = pv && g0 + u < gpb;
             packed[jj][u] = lv ? __ldcg(reinterpret_cast<const uint2*>(pw + gg * kGroup + sub * 8)) : make_uint2(0u, 0u);
-            sc[jj][u] = lv ? __ldcg(ps + gg) : 0.f;
           }
+          sc_lane[jj] = (pv && sub < U && g0 + sub < gpb) ? __ldcg(ps + (long long)rank * gpb + g0 + sub) : 0.f;
         }
+        float sc[kPeerBatch][U];
+#pragma unroll
+        for (int jj = 0; jj < kPeerBatch; ++jj)
+#pragma unroll
+          for (int u = 0; u < U; ++u) sc[jj][u] = __shfl_sync(0xffffffffu, sc_lane[jj], hw * 16 + u);
 #pragma unroll
         for (int jj = 0; jj < kPeerBatch; ++jj)
 #pragma unroll

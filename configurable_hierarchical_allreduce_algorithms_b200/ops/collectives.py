@@ -59,7 +59,8 @@ _NVTX = __import__("os").environ.get("CHB_NVTX", "0") == "1"   # NVTX range arou
 def _run(comm: Communicator, coll: str, ins, outs, count: int, op, algo, k, b, aux, scale, nctas, stream,
          payload_bytes: int, ll_mode: int):
     """Pick the kernel and enqueue it with a single native call."""
-    if algo == "auto":
+    auto = algo == "auto"
+    if auto:
         sym = comm.is_symmetric(ins[0]) and comm.is_symmetric(outs[0])
         key = (coll, payload_bytes, ins[0].dtype, sym)
         choice = comm._choices.get(key)
@@ -91,6 +92,13 @@ def _run(comm: Communicator, coll: str, ins, outs, count: int, op, algo, k, b, a
                                 (C.c_void_p * n)(*[t.data_ptr() for t in ins]),
                                 (C.c_void_p * n)(*[t.data_ptr() for t in outs]),
                                 count, scale, nctas, _stream_ptr(stream))
+    if rc == N.ERR_COUNT and auto and algo.endswith(":ll"):
+        # the tuned row was measured with a larger flagged-line inbox than this communicator has: same program, pulled
+        ab = (algo[:-3] + ":pull").encode()
+        rc = N.lib().chb_collective(comm._h, _COLL[coll], ab, k, b, aux, DTYPES[ins[0].dtype], OPS[op],
+                                    (C.c_void_p * n)(*[t.data_ptr() for t in ins]),
+                                    (C.c_void_p * n)(*[t.data_ptr() for t in outs]),
+                                    count, scale, nctas, _stream_ptr(stream))
     if _NVTX:
         torch.cuda.nvtx.range_pop()
     if rc:

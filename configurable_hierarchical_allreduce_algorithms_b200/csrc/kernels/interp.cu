@@ -27,15 +27,16 @@ namespace chb {
 
 constexpr int kInterpThreads = 512;
 constexpr int kMaxSrc = 40;              // sources per step (incl. the accumulate operand)
-constexpr long long kSmallStepBytes = 64 << 10;  // below this one CTA runs the whole step
+constexpr long long kSmallStepElems = 16 << 10;  // steps below this many elements are run whole, by one CTA
 
 struct DevStep { long long dst_off; long long count; int dst_buf; int nsrc; int src_begin; unsigned flags; };
 struct DevSrc { long long off; int peer; int buf; };
 struct DevWait { int peer; int need; };
-struct DevRound { int step_begin, step_end, wait_begin, wait_end, sig_begin, sig_end; };
+// order[ord_begin ..): the round's steps, the nbig large ones first (big_tot / big_max: their total and largest count)
+struct DevRound { int step_begin, step_end, wait_begin, wait_end, sig_begin, sig_end, ord_begin, nbig; long long big_tot, big_max; };
 struct DevHeader {
   int P, nrounds, nsteps, nsrcs, nwaits, nsigs;
-  long long off_rounds, off_steps, off_srcs, off_waits, off_sigs, off_exit;
+  long long off_rounds, off_steps, off_srcs, off_waits, off_sigs, off_exit, off_order;
   long long limit[3];   // elements of the caller input, caller output and scratch (for range checks)
 };
 
@@ -74,6 +75,7 @@ static std::vector<char> make_blob(const Program& p) {
   std::vector<DevSrc> srcs;
   std::vector<DevWait> waits;
   std::vector<int> sigs;
+  std::vector<int> order;
   std::vector<int> exits((size_t)p.P * 2);
   for (int r = 0; r < p.P; ++r)
     for (int t = 0; t < p.nrounds; ++t) {
@@ -93,6 +95,19 @@ static std::vector<char> make_blob(const Program& p) {
         steps.push_back(s);
       }
       d.step_end = (int)steps.size();
+      // what the tile scheduler needs, worked out here once instead of by one thread per round and launch
+      d.ord_begin = (int)order.size();
+      for (int pass = 0; pass < 2; ++pass)
+        for (int si = d.step_begin; si < d.step_end; ++si) {
+          const bool big = steps[(size_t)si].count >= kSmallStepElems;
+          if (big != (pass == 0)) continue;
+          order.push_back(si);
+          if (big) {
+            ++d.nbig;
+            d.big_tot += steps[(size_t)si].count;
+            d.big_max = std::max<long long>(d.big_max, steps[(size_t)si].count);
+          }
+        }
       d.wait_begin = (int)waits.size();
       for (const Wait& w : rr.waits) waits.push_back(DevWait{w.peer, w.need});
       d.wait_end = (int)waits.size();
@@ -117,6 +132,7 @@ static std::vector<char> make_blob(const Program& p) {
   h.off_waits = (long long)off;  off = al(off + waits.size() * sizeof(DevWait));
   h.off_sigs = (long long)off;   off = al(off + sigs.size() * sizeof(int));
   h.off_exit = (long long)off;   off = al(off + exits.size() * sizeof(int));
+  h.off_order = (long long)off;  off = al(off + order.size() * sizeof(int));
   std::vector<char> blob(off, 0);
   std::memcpy(blob.data(), &h, sizeof(h));
   auto put = [&](long long o, const void* src, size_t n) { if (n) std::memcpy(blob.data() + o, src, n); };
@@ -126,6 +142,7 @@ static std::vector<char> make_blob(const Program& p) {
   put(h.off_waits, waits.data(), waits.size() * sizeof(DevWait));
   put(h.off_sigs, sigs.data(), sigs.size() * sizeof(int));
   put(h.off_exit, exits.data(), exits.size() * sizeof(int));
+  put(h.off_order, order.data(), order.size() * sizeof(int));
   return blob;
 }
 
@@ -135,6 +152,54 @@ static std::vector<char> make_blob(const Program& p) {
 // their loads are issued kSrcGroup sources at a time and two vectors deep, so that every thread keeps
 // 128 bytes of NVLink round trips in flight whether a step has one remote source or P-1 of them.
 constexpr int kSrcGroup = 2;
+
+// 256-bit reduce loop over vectors [j0, nw) strided by TT: G sources x UW vectors in flight per thread.
+// (not inlined: each variant gets a register allocation of its own instead of inflating the interpreter's)
+template <typename T, int G, int UW>
+__device__ __noinline__ void reduce_loop32(const char* const* s_ptr, char* dst, int nsrc, long long j0, long long nw,
+                                              long long TT, int op, bool do_scale, float scale) {
+  using Acc = typename Elem<T>::Acc;
+  constexpr int VE = Elem<T>::kPerVec;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  for (; j0 < nw; j0 += TT * UW) {
+    Acc a[UW][2][VE];
+    for (int s = 0; s < nsrc; s += G) {
+      uint4 x[G][UW][2];
+#pragma unroll
+      for (int gi = 0; gi < G; ++gi) {
+        if (s + gi < nsrc) {
+          const char* p0 = s_ptr[s + gi];
+#pragma unroll
+          for (int u = 0; u < UW; ++u) {
+            const long long j = j0 + (long long)u * TT;
+            if (j < nw) ld32_cg(p0 + j * 32, x[gi][u][0], x[gi][u][1]);
+            else x[gi][u][0] = x[gi][u][1] = zero;
+          }
+        }
+      }
+#pragma unroll
+      for (int gi = 0; gi < G; ++gi) {
+        if (s + gi < nsrc) {
+          if (gi == 0 && s == 0) {
+#pragma unroll
+            for (int u = 0; u < UW; ++u) { vec_to_acc<T>(x[0][u][0], a[u][0]); vec_to_acc<T>(x[0][u][1], a[u][1]); }
+          } else {
+#pragma unroll
+            for (int u = 0; u < UW; ++u) { vec_combine<T>(op, x[gi][u][0], a[u][0]); vec_combine<T>(op, x[gi][u][1], a[u][1]); }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UW; ++u) {
+      const long long j = j0 + (long long)u * TT;
+      if (j < nw) {
+        if (do_scale) { acc_scale<T>(a[u][0], scale); acc_scale<T>(a[u][1], scale); }
+        st32(dst + j * 32, acc_to_vec<T>(a[u][0]), acc_to_vec<T>(a[u][1]));
+      }
+    }
+  }
+}
 
 template <typename T>
 __device__ __forceinline__ void run_step(const DevStep& st, const DevSrc* __restrict__ srcs, const World& w,
@@ -176,13 +241,10 @@ __device__ __forceinline__ void run_step(const DevStep& st, const DevSrc* __rest
   if (s_meta[0] < 0) return;
 #endif
   __syncthreads();
-  if (tid == 0) {
-    unsigned long long m = (unsigned long long)s_ptr[kMaxSrc];
-    for (int i = 0; i < nsrc; ++i) m |= (unsigned long long)s_ptr[i];
-    s_meta[0] = (m & 31ull) == 0ull ? 2 : ((m & 15ull) == 0ull ? 1 : 0);   // widest vector every pointer allows
-  }
-  __syncthreads();
-  const int align_level = s_meta[0];
+  // widest vector every pointer allows (every thread works it out from the shared table: no second barrier)
+  unsigned long long m = (unsigned long long)s_ptr[kMaxSrc];
+  for (int i = 0; i < nsrc; ++i) m |= (unsigned long long)s_ptr[i];
+  const int align_level = (m & 31ull) == 0ull ? 2 : ((m & 15ull) == 0ull ? 1 : 0);
   const bool aligned = align_level != 0;
   char* dst = const_cast<char*>(s_ptr[kMaxSrc]);
   const bool do_scale = (st.flags & OPF_FINAL) && scale != 1.0f;
@@ -212,45 +274,10 @@ __device__ __forceinline__ void run_step(const DevStep& st, const DevSrc* __rest
         d += UC * stride;
       }
     }
-    constexpr int UW = 2;
-    for (; j0 < nw; j0 += TT * UW) {
-      Acc a[UW][2][VE];
-      for (int s = 0; s < nsrc; s += G) {
-        uint4 x[G][UW][2];
-#pragma unroll
-        for (int gi = 0; gi < G; ++gi) {
-          if (s + gi < nsrc) {
-            const char* p0 = s_ptr[s + gi];
-#pragma unroll
-            for (int u = 0; u < UW; ++u) {
-              const long long j = j0 + (long long)u * TT;
-              if (j < nw) ld32_cg(p0 + j * 32, x[gi][u][0], x[gi][u][1]);
-              else x[gi][u][0] = x[gi][u][1] = zero;
-            }
-          }
-        }
-#pragma unroll
-        for (int gi = 0; gi < G; ++gi) {
-          if (s + gi < nsrc) {
-            if (gi == 0 && s == 0) {
-#pragma unroll
-              for (int u = 0; u < UW; ++u) { vec_to_acc<T>(x[0][u][0], a[u][0]); vec_to_acc<T>(x[0][u][1], a[u][1]); }
-            } else {
-#pragma unroll
-              for (int u = 0; u < UW; ++u) { vec_combine<T>(op, x[gi][u][0], a[u][0]); vec_combine<T>(op, x[gi][u][1], a[u][1]); }
-            }
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < UW; ++u) {
-        const long long j = j0 + (long long)u * TT;
-        if (j < nw) {
-          if (do_scale) { acc_scale<T>(a[u][0], scale); acc_scale<T>(a[u][1], scale); }
-          st32(dst + j * 32, acc_to_vec<T>(a[u][0]), acc_to_vec<T>(a[u][1]));
-        }
-      }
-    }
+    // a tile with at most one vector per thread is bound by the depth of its chain of round trips: four sources at
+    // a time; longer tiles by bytes in flight: two sources, two vectors deep (the same 128 bytes per thread)
+    if (nw <= TT) reduce_loop32<T, 4, 1>(s_ptr, dst, nsrc, j0, nw, TT, op, do_scale, scale);
+    else reduce_loop32<T, kSrcGroup, 2>(s_ptr, dst, nsrc, j0, nw, TT, op, do_scale, scale);
     i0 = nw * 2 + g;
   }
   constexpr int U = 2;
@@ -309,9 +336,8 @@ __device__ __forceinline__ void run_step(const DevStep& st, const DevSrc* __rest
 // them one after the other: testing/custom_implementations/work_dir/all_reduce/all_reduce_radix_batch.cpp:343-364),
 // and at any moment the P readers of one round are spread over P different owners instead of all
 // reading from the owner that comes first in the schedule.
-constexpr int kMaxBig = 64;                       // large steps per round handled by the tile scheduler
 constexpr long long kTileGrain = 16 << 10;        // tiles are multiples of this (keeps 32-byte alignment for every type)
-constexpr long long kTileMin = 64 << 10, kTileMax = 512 << 10;
+constexpr long long kTileMin = 16 << 10, kTileMax = 512 << 10;   // 16 KiB = one 32-byte vector per thread of a CTA
 
 template <typename T>
 __global__ void __launch_bounds__(kInterpThreads, 1)
@@ -327,14 +353,13 @@ interp_kernel(World w, const char* __restrict__ blob, IoTable io, int op, float 
   const DevWait* waits = reinterpret_cast<const DevWait*>(blob + h->off_waits);
   const int* sigs = reinterpret_cast<const int*>(blob + h->off_sigs);
   const int* exits = reinterpret_cast<const int*>(blob + h->off_exit);
+  const int* order = reinterpret_cast<const int*>(blob + h->off_order);
   const int P = h->P, nrounds = h->nrounds;
 
   __shared__ unsigned long long s_base;
   __shared__ int s_ok;
   __shared__ const char* s_ptr[kMaxSrc + 1];
   __shared__ int s_meta[4];
-  __shared__ int s_big[kMaxBig];
-  __shared__ long long s_tile;
   if (tid == 0) {
     s_base = ld_volatile_u64(&c->epoch);
     s_ok = ld_volatile_u32(&c->abort) ? 0 : 1;
@@ -363,51 +388,25 @@ interp_kernel(World w, const char* __restrict__ blob, IoTable io, int op, float 
     if (tr && cta == 0 && tid == 0 && t < w.trace_rounds) tr[2 * t] = globaltimer_ns();   // waits of round t satisfied
     const int nst = R.step_end - R.step_begin;
     if (nst > 0) {
-      if (tid == 0) {
-        int nb = 0;
-        long long maxc = 0, tot = 0;
-        for (int s = R.step_begin; s < R.step_end; ++s) {
-          const long long cnt = steps[s].count;
-          if (cnt * (long long)sizeof(T) < kSmallStepBytes) continue;
-          if (nb < kMaxBig) s_big[nb] = s;
-          ++nb;
-          maxc = cnt > maxc ? cnt : maxc;
-          tot += cnt;
-        }
-        // about four tiles per CTA and round: enough for balance, few enough to keep the set-up cost per tile small
-        long long tb = tot * (long long)sizeof(T) / ((long long)nct * 4);
-        tb = tb < kTileMin ? kTileMin : (tb > kTileMax ? kTileMax : tb);
-        tb = tb / kTileGrain * kTileGrain;
-        const long long te = tb / (long long)sizeof(T);
-        s_tile = te;
-        s_meta[1] = nb;
-        s_meta[2] = (int)((maxc + te - 1) / te);
-      }
-      __syncthreads();
-      const int nb = s_meta[1], nsmall = nst - nb;
-      const long long te = s_tile;
-      const long long nitems = (long long)nsmall + (long long)s_meta[2] * nb;
+      // about four tiles per CTA and round: enough for balance, few enough to keep the set-up cost per tile small
+      const int nb = R.nbig, nsmall = nst - nb;
+      long long tb = R.big_tot * (long long)sizeof(T) / ((long long)nct * 4);
+      tb = tb < kTileMin ? kTileMin : (tb > kTileMax ? kTileMax : tb);
+      tb = tb / kTileGrain * kTileGrain;
+      const long long te = tb / (long long)sizeof(T);
+      const long long rows = nb ? (R.big_max + te - 1) / te : 0;
+      const long long nitems = (long long)nsmall + rows * nb;
       // work items of this round: the small steps (one CTA each), then the tiles of the large steps
       for (long long v = cta; v < nitems; v += nct) {
-        int sidx = -1;
+        int sidx;
         long long e0 = 0;
         if (v < nsmall) {
-          long long seen = 0;
-          for (int s = R.step_begin; s < R.step_end; ++s)
-            if (steps[s].count * (long long)sizeof(T) < kSmallStepBytes && seen++ == v) { sidx = s; break; }
+          sidx = order[R.ord_begin + nb + (int)v];
         } else {
           const long long u = v - nsmall;
-          const int bi = (int)((u % nb + rank) % nb);
+          sidx = order[R.ord_begin + (int)((u % nb + rank) % nb)];
           e0 = (u / nb) * te;
-          if (nb <= kMaxBig) {
-            sidx = s_big[bi];
-          } else {   // more large steps than the table holds: find the bi-th one by walking the round
-            int seen = 0;
-            for (int s = R.step_begin; s < R.step_end; ++s)
-              if (steps[s].count * (long long)sizeof(T) >= kSmallStepBytes && seen++ == bi) { sidx = s; break; }
-          }
         }
-        if (sidx < 0) continue;
         const DevStep st = steps[sidx];
         if (e0 >= st.count) continue;
         long long cnt = st.count - e0;
@@ -594,7 +593,7 @@ int chb_run_program(chb_comm* c, const chb_program* p, int dtype, int op, const 
     long long bytes = (long long)std::max(g.in_elems, g.out_elems) * (long long)esz;
     // NVLink wants about 2 MB in flight per GPU (rate x loaded latency) and a thread keeps 128 bytes in flight:
     // bandwidth-bound sizes take (nearly) every SM, one CTA each
-    nctas = bytes <= (64 << 10) ? 1 : (bytes <= (1 << 20) ? 16 : (bytes <= (4 << 20) ? 64 : 128));
+    nctas = bytes <= (64 << 10) ? 1 : (bytes <= (1 << 20) ? 32 : (bytes <= (4 << 20) ? 64 : 128));
     // a single-rank world only copies locally: HBM-bound, wants every SM
     if (c->P == 1 && bytes > (16 << 20)) nctas = per_rank_budget;
   }

@@ -15,7 +15,7 @@
 
 namespace chb {
 
-constexpr int kFp8Threads = 512;
+constexpr int kFp8Threads = 1024;   // 32 warps per SM at <= 64 registers: the kernel is bound by instruction issue, not by bytes
 constexpr int kGroup = 128;  // elements per scale
 constexpr int kPeerBatch = 4; // peers whose wire data is loaded together in the pull phase
 
@@ -107,7 +107,7 @@ fp8_rs_kernel(World w, Fp8Io io, long long n, float out_scale) {
     __syncthreads();
     ok = ok && s_entry_ok != 0;
   }
-  constexpr int U = 4;   // groups in flight per half-warp
+  constexpr int U = 2;   // groups in flight per half-warp (two 16-lane halves per warp, 32 warps per SM)
   // ---- quantise the blocks owed to the peers (the loads of the next iteration are issued before the
   // arithmetic of this one: the phase is bound by bytes in flight, not by instructions)
   if (ok) {
@@ -266,7 +266,7 @@ int chb_rs_fp8_wire(chb_comm* c, int dtype, const void* const* in, void* const* 
   if (n == 0) return CHB_SUCCESS;
   const int max_pair_ctas = (kSigSlots - kSigNvlsBase) / kMaxRanks;
   int budget = c->max_ctas / c->nlocal;
-  if (nctas <= 0) nctas = (int)(((long long)c->P * n / kGroup + 127) / 128);
+  if (nctas <= 0) nctas = (int)(((long long)c->P * n / kGroup + 127) / 128);   // about four half-warp iterations per CTA
   if (nctas > 120) nctas = 120;
   if (nctas > max_pair_ctas) nctas = max_pair_ctas;
   if (nctas > budget) nctas = budget;

@@ -337,7 +337,7 @@ __device__ __forceinline__ void run_step(const DevStep& st, const DevSrc* __rest
 // and at any moment the P readers of one round are spread over P different owners instead of all
 // reading from the owner that comes first in the schedule.
 constexpr long long kTileGrain = 16 << 10;        // tiles are multiples of this (keeps 32-byte alignment for every type)
-constexpr long long kTileMin = 16 << 10, kTileMax = 512 << 10;   // 16 KiB = one 32-byte vector per thread of a CTA
+constexpr long long kTileMin = 16 << 10, kTileMax = 1 << 20;   // 16 KiB = one 32-byte vector per thread of a CTA
 
 template <typename T>
 __global__ void __launch_bounds__(kInterpThreads, 1)
@@ -388,12 +388,21 @@ interp_kernel(World w, const char* __restrict__ blob, IoTable io, int op, float 
     if (tr && cta == 0 && tid == 0 && t < w.trace_rounds) tr[2 * t] = globaltimer_ns();   // waits of round t satisfied
     const int nst = R.step_end - R.step_begin;
     if (nst > 0) {
-      // about four tiles per CTA and round: enough for balance, few enough to keep the set-up cost per tile small
+      // Tile size: every CTA gets the same number m of tiles (one, unless that tile would exceed kTileMax), each as
+      // large as that allows: the shortest chain of dependent round trips per CTA and the most bytes in flight per
+      // thread, and no CTA left with one tile more than the others.  A large step is cut into q = nct * m / nb tiles.
       const int nb = R.nbig, nsmall = nst - nb;
-      long long tb = R.big_tot * (long long)sizeof(T) / ((long long)nct * 4);
-      tb = tb < kTileMin ? kTileMin : (tb > kTileMax ? kTileMax : tb);
-      tb = tb / kTileGrain * kTileGrain;
-      const long long te = tb / (long long)sizeof(T);
+      const long long grain_e = kTileGrain / (long long)sizeof(T), max_e = kTileMax / (long long)sizeof(T);
+      long long te = kTileMin / (long long)sizeof(T);
+      if (nb > 0) {
+        long long m = (R.big_max * nb + (long long)nct * max_e - 1) / ((long long)nct * max_e);
+        if (m < 1) m = 1;
+        long long q = (long long)nct * m / nb;
+        if (q < 1) q = 1;
+        long long t = (R.big_max + q - 1) / q;
+        t = (t + grain_e - 1) / grain_e * grain_e;
+        if (t > te) te = t;
+      }
       const long long rows = nb ? (R.big_max + te - 1) / te : 0;
       const long long nitems = (long long)nsmall + rows * nb;
       // work items of this round: the small steps (one CTA each), then the tiles of the large steps

@@ -411,7 +411,7 @@ int chb_run_program_ll(chb_comm* c, const chb_program* p, int dtype, int op, con
   if (nctas <= 0) {
     // about four lines per thread in the busiest level
     nctas = (int)((hd.max_level_lines + kLPThreads * 4 - 1) / (kLPThreads * 4));
-    if (nctas > 32) nctas = 32;
+    if (nctas > 64) nctas = 64;
   }
   if (nctas > 64) nctas = 64;
   if (nctas > budget) nctas = budget;

@@ -358,6 +358,26 @@ long long chb_program_ll_lines(const chb_program* p, int esz) {
   return worst;
 }
 
+// What the flagged-line form of a program looks like, for tests and tuning: info = levels, messages pushed in a
+// level's push phase, messages forwarded line by line from the previous level's steps, rank-local barriers (summed
+// over ranks), lines in the fullest inbox, lines of the busiest (rank, level).
+int chb_program_ll_info(const chb_program* p, int esz, long long* info, int n) {
+  if (!p || !info || esz < 1) return CHB_ERR_ARG;
+  LPHeader h{};
+  std::vector<char> blob = make_ll_blob(p->prog, esz, &h);
+  const LPLevel* lv = reinterpret_cast<const LPLevel*>(blob.data() + h.off_levels);
+  long long barriers = 0;
+  for (long long i = 0; i < (long long)h.P * h.nlevels; ++i) barriers += lv[i].barrier_before;
+  const long long nfwd = (h.off_fwds < (long long)blob.size()) ? ((long long)blob.size() - h.off_fwds) / (long long)sizeof(LPFwd) : 0;
+  long long fwd_exact = 0;
+  const LPStep* st = reinterpret_cast<const LPStep*>(blob.data() + h.off_steps);
+  for (int i = 0; i < h.nsteps; ++i) fwd_exact += st[i].nfwd;
+  (void)nfwd;
+  const long long v[6] = {h.nlevels, h.nsends, fwd_exact, barriers, h.inbox_lines, h.max_level_lines};
+  for (int i = 0; i < n && i < 6; ++i) info[i] = v[i];
+  return CHB_SUCCESS;
+}
+
 // Run a compiled program with flagged lines (see the head of this file).  The program must have been
 // lowered with in_symmetric and out_symmetric set (no staging copies are wanted: nobody reads a peer's
 // buffers here, so the caller's buffers may live anywhere), for a collective in which every rank's

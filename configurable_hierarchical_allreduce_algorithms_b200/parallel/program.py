@@ -169,6 +169,21 @@ class Program:
             raise RuntimeError(f"simulate({self.name}) failed: {err.value.decode()}")
         return [o[:self.out_elems] for o in outs]
 
+    def ll_info(self, elem_bytes: int = 4) -> dict:
+        """Shape of the flagged-line (push) form of this program: rounds, messages pushed per round's push phase,
+        messages forwarded line by line from the previous round's steps, rank-local barriers (all ranks), lines in
+        the fullest inbox and in the busiest (rank, round)."""
+        L = N.lib()
+        if not hasattr(L, "chb_program_ll_info"):
+            raise N.NativeLibraryMissing("libchb.so was built without its CUDA half")
+        L.chb_program_ll_info.restype = C.c_int
+        L.chb_program_ll_info.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_longlong), C.c_int]
+        v = (C.c_longlong * 6)()
+        rc = L.chb_program_ll_info(self._h, elem_bytes, v, 6)
+        if rc:
+            raise RuntimeError(f"ll_info failed with code {rc}")
+        return dict(zip(("levels", "pushed", "forwarded", "barriers", "inbox_lines", "busiest_level_lines"), [int(x) for x in v]))
+
     def run_threads(self, inputs: list[np.ndarray], op: str = "sum", iters: int = 1,
                     late_rank: int | None = None, delay_ms: int = 20):
         """Run all P ranks as concurrent host threads; returns (outputs, mean seconds per repetition).

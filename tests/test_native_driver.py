@@ -66,3 +66,13 @@ def test_forked_ranks_one_per_gpu(exe, tmp_path, coll):
     names = set(df.algorithm_name)
     assert any("radix_batch" in x for x in names)
     assert names & {"MPICH_allreduce", "reduce_scatter_standard", "allgather_standard"}, names     # the NCCL row
+    # the launcher's heaps come from the native virtual-memory allocator with a multicast alias where the devices have
+    # one: the in-switch kernels then run from this binary too (skipped, with a message, where there is no alias)
+    out2 = tmp_path / "nvls.csv"
+    r = subprocess.run([exe, "2", "--overwrite", f"ngpus={n}", f"b={n}", "base=4096", f"coll={coll}", "dtype=fp32", "reps=3",
+                        "symmetric=1", "algos=nvls,radix_batch", f"out={out2}"], capture_output=True, text=True, timeout=400)
+    assert r.returncode == 0, r.stdout + r.stderr
+    df2 = pd.read_csv(out2)
+    assert (df2.is_correct == 1).all()
+    if "skipped" not in r.stderr:
+        assert any("nvls" in x for x in set(df2.algorithm_name)), set(df2.algorithm_name)

@@ -440,52 +440,51 @@ def main():
         for sz in [int(s) for s in args.sweep.split(",") if s]:
             if sz > S:
                 continue
-            if True:
-                esz = 4 if dtype == torch.float32 else 2
-                ne = max(1, sz // esz)
-                ne_rs = max(1, ne // max(N, 1))
-                xf, yf = x.view(dtype), y.view(dtype)     # slices below may be longer than ne for tiny sizes
-                xv, yv = xf[:ne], yf[:ne]
-                row = {"bytes": ne * esz, "dtype": dname}
-                rf = scratch_ref.view(dtype)
-                cases = {
-                    "allreduce": (lambda: chb.all_reduce(comm, xv, out=yv),
-                                  (lambda: dist.all_reduce(yv)) if world > 1 else None, 2 * (N - 1) / N, ne * esz,
-                                  (lambda: (rf[:ne].copy_(xv), dist.all_reduce(rf[:ne]) if world > 1 else None, (yv, rf[:ne]))[-1])),
-                    "reduce_scatter": (lambda: chb.reduce_scatter(comm, xf[:ne_rs * N], out=yf[:ne_rs]),
-                                       (lambda: dist.reduce_scatter_tensor(yf[:ne_rs], xf[:ne_rs * N])) if world > 1 else None,
-                                       (N - 1) / N, ne_rs * N * esz,
-                                       (lambda: (dist.reduce_scatter_tensor(rf[:ne_rs], xf[:ne_rs * N]) if world > 1
-                                                 else rf[:ne_rs].copy_(xf[:ne_rs]), (yf[:ne_rs], rf[:ne_rs]))[-1])),
-                    "allgather": (lambda: chb.all_gather(comm, xf[:ne_rs], out=yf[:ne_rs * N]),
-                                  (lambda: dist.all_gather_into_tensor(yf[:ne_rs * N], xf[:ne_rs])) if world > 1 else None,
-                                  (N - 1) / N, ne_rs * N * esz,
-                                  (lambda: (dist.all_gather_into_tensor(rf[:ne_rs * N], xf[:ne_rs]) if world > 1
-                                            else rf[:ne_rs].copy_(xf[:ne_rs]), (yf[:ne_rs * N], rf[:ne_rs * N]))[-1])),
-                }
-                for name, (ours, theirs, factor, total_bytes, checker) in cases.items():
-                    # about 20 ms of back-to-back calls first (the same count on every rank): after the small
-                    # sizes of the sweep the links and clocks need more than three calls to be back at speed
-                    n_warm = min(100, max(3, int(20e-3 / (20e-6 + total_bytes / 2e11))))
+            esz = 4 if dtype == torch.float32 else 2
+            ne = max(1, sz // esz)
+            ne_rs = max(1, ne // max(N, 1))
+            xf, yf = x.view(dtype), y.view(dtype)     # slices below may be longer than ne for tiny sizes
+            xv, yv = xf[:ne], yf[:ne]
+            row = {"bytes": ne * esz, "dtype": dname}
+            rf = scratch_ref.view(dtype)
+            cases = {
+                "allreduce": (lambda: chb.all_reduce(comm, xv, out=yv),
+                              (lambda: dist.all_reduce(yv)) if world > 1 else None, 2 * (N - 1) / N, ne * esz,
+                              (lambda: (rf[:ne].copy_(xv), dist.all_reduce(rf[:ne]) if world > 1 else None, (yv, rf[:ne]))[-1])),
+                "reduce_scatter": (lambda: chb.reduce_scatter(comm, xf[:ne_rs * N], out=yf[:ne_rs]),
+                                   (lambda: dist.reduce_scatter_tensor(yf[:ne_rs], xf[:ne_rs * N])) if world > 1 else None,
+                                   (N - 1) / N, ne_rs * N * esz,
+                                   (lambda: (dist.reduce_scatter_tensor(rf[:ne_rs], xf[:ne_rs * N]) if world > 1
+                                             else rf[:ne_rs].copy_(xf[:ne_rs]), (yf[:ne_rs], rf[:ne_rs]))[-1])),
+                "allgather": (lambda: chb.all_gather(comm, xf[:ne_rs], out=yf[:ne_rs * N]),
+                              (lambda: dist.all_gather_into_tensor(yf[:ne_rs * N], xf[:ne_rs])) if world > 1 else None,
+                              (N - 1) / N, ne_rs * N * esz,
+                              (lambda: (dist.all_gather_into_tensor(rf[:ne_rs * N], xf[:ne_rs]) if world > 1
+                                        else rf[:ne_rs].copy_(xf[:ne_rs]), (yf[:ne_rs * N], rf[:ne_rs * N]))[-1])),
+            }
+            for name, (ours, theirs, factor, total_bytes, checker) in cases.items():
+                # about 20 ms of back-to-back calls first (the same count on every rank): after the small
+                # sizes of the sweep the links and clocks need more than three calls to be back at speed
+                n_warm = min(100, max(3, int(20e-3 / (20e-6 + total_bytes / 2e11))))
+                for _ in range(n_warm):
+                    ours()
+                t = [max_over_ranks(v) for v in per_call_ms(ours, args.sweep_iters, flush, barrier)]
+                p50 = statistics.median(t)
+                row[name] = {"p50_us": p50 * 1e3, "busbw_GBps": total_bytes / (p50 * 1e-3) / 1e9 * factor}
+                if total_bytes <= scratch_ref.numel() * 4:
+                    ours()
+                    got, want = checker()
+                    torch.cuda.synchronize()
+                    row[name]["is_correct"] = all_ranks_ok(close_enough(got, want, dtype))
+                if theirs is not None and not args.no_nccl:
                     for _ in range(n_warm):
-                        ours()
-                    t = [max_over_ranks(v) for v in per_call_ms(ours, args.sweep_iters, flush, barrier)]
-                    p50 = statistics.median(t)
-                    row[name] = {"p50_us": p50 * 1e3, "busbw_GBps": total_bytes / (p50 * 1e-3) / 1e9 * factor}
-                    if total_bytes <= scratch_ref.numel() * 4:
-                        ours()
-                        got, want = checker()
-                        torch.cuda.synchronize()
-                        row[name]["is_correct"] = all_ranks_ok(close_enough(got, want, dtype))
-                    if theirs is not None and not args.no_nccl:
-                        for _ in range(n_warm):
-                            theirs()
-                        t = [max_over_ranks(v) for v in per_call_ms(theirs, args.sweep_iters, flush, barrier)]
-                        p50n = statistics.median(t)
-                        row[name]["nccl_p50_us"] = p50n * 1e3
-                        row[name]["nccl_busbw_GBps"] = total_bytes / (p50n * 1e-3) / 1e9 * factor
-                        row[name]["vs_nccl"] = p50n / p50
-                sweep.append(row)
+                        theirs()
+                    t = [max_over_ranks(v) for v in per_call_ms(theirs, args.sweep_iters, flush, barrier)]
+                    p50n = statistics.median(t)
+                    row[name]["nccl_p50_us"] = p50n * 1e3
+                    row[name]["nccl_busbw_GBps"] = total_bytes / (p50n * 1e-3) / 1e9 * factor
+                    row[name]["vs_nccl"] = p50n / p50
+            sweep.append(row)
         comm.check()
 
     if args.sweep:

@@ -368,12 +368,10 @@ int chb_program_ll_info(const chb_program* p, int esz, long long* info, int n) {
   const LPLevel* lv = reinterpret_cast<const LPLevel*>(blob.data() + h.off_levels);
   long long barriers = 0;
   for (long long i = 0; i < (long long)h.P * h.nlevels; ++i) barriers += lv[i].barrier_before;
-  const long long nfwd = (h.off_fwds < (long long)blob.size()) ? ((long long)blob.size() - h.off_fwds) / (long long)sizeof(LPFwd) : 0;
-  long long fwd_exact = 0;
+  long long forwarded = 0;
   const LPStep* st = reinterpret_cast<const LPStep*>(blob.data() + h.off_steps);
-  for (int i = 0; i < h.nsteps; ++i) fwd_exact += st[i].nfwd;
-  (void)nfwd;
-  const long long v[6] = {h.nlevels, h.nsends, fwd_exact, barriers, h.inbox_lines, h.max_level_lines};
+  for (int i = 0; i < h.nsteps; ++i) forwarded += st[i].nfwd;
+  const long long v[6] = {h.nlevels, h.nsends, forwarded, barriers, h.inbox_lines, h.max_level_lines};
   for (int i = 0; i < n && i < 6; ++i) info[i] = v[i];
   return CHB_SUCCESS;
 }

@@ -70,3 +70,20 @@ def test_flagged_line_wait_times_out(cuda):
     c.run_ll(0, x, y, 64)
     assert c.status()["rc"] == N.ERR_TIMEOUT
     c.close()
+
+
+def test_flagged_line_program_wait_times_out(cuda):
+    """The push form of a step program: the line a missing peer owes never arrives, the poll gives up within its
+    limit, the rank records which peer it waited for, and later levels and launches do no more work."""
+    c = _half_world(timeout_us=200_000)
+    x = torch.ones(256, device="cuda")
+    y = torch.zeros(256, device="cuda")
+    prog = c.program("allreduce", "radix_batch", 256, 2, 1, in_symmetric=True, out_symmetric=True)
+    c.run_program(prog, x, y, mode="ll")
+    st = c.status()
+    assert st["rc"] == N.ERR_TIMEOUT and st["code"] == 5 and st["peer"] == 1
+    c.run_program(prog, x, y, mode="ll")
+    assert c.status()["rc"] == N.ERR_TIMEOUT
+    z = torch.ones(1024, device="cuda")
+    assert float(z.sum()) == 1024.0
+    c.close()

@@ -90,14 +90,18 @@ def build(verbose: bool = False, force: bool = False) -> Path:
                     logs.append(f"== {futs[f].name}\n{out}")
     need_link = bool(todo) or not LIB.exists() or any(o.stat().st_mtime > LIB.stat().st_mtime for o in objs)
     if need_link:
+        # linked next to its final place and renamed into it: a process that loads the library (or a copy of the
+        # tree taken) while a build is running sees the old file or the new one, never a half-written one
+        tmp = LIB.with_name(LIB.name + ".tmp")
         if cu:
-            cmd = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB),
+            cmd = [NVCC, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(tmp),
                    *map(str, objs), "-lpthread"]
         else:
-            cmd = [CXX, "-shared", "-o", str(LIB), *map(str, objs), "-lpthread"]
+            cmd = [CXX, "-shared", "-o", str(tmp), *map(str, objs), "-lpthread"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, LIB)
     if cu:
         _build_tools(hdr_t, force)
     if verbose and logs:
@@ -112,11 +116,13 @@ def _build_tools(hdr_t: float, force: bool) -> None:
         exe = BIN / src.stem
         if not force and exe.exists() and exe.stat().st_mtime >= max(src.stat().st_mtime, hdr_t, LIB.stat().st_mtime):
             continue
+        tmp = exe.with_name(exe.name + ".tmp")
         cmd = [NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-I", str(CSRC),
-               str(src), "-o", str(exe), "-L", str(HERE), "-lchb", "-ldl", "-Xlinker", "-rpath=$ORIGIN/.."]
+               str(src), "-o", str(tmp), "-L", str(HERE), "-lchb", "-ldl", "-Xlinker", "-rpath=$ORIGIN/.."]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"tool build failed: {' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, exe)
 
 
 if __name__ == "__main__":

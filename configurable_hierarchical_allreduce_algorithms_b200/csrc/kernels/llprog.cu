@@ -134,11 +134,27 @@ static std::vector<char> make_ll_blob(const Program& p, int esz, LPHeader* hout)
       }
       next.swap(keep);
     }
+  // Every sender starts with the receiver after itself and goes round from there (pushes of a level and
+  // forwards of a step alike): at any moment the P senders aim at P different receivers, instead of all
+  // filling receiver 0's inbox first, then receiver 1's, ... with one ingress link busy and the others idle.
+  auto after = [P](int sender, int dst) { return (dst - sender - 1 + P) % P; };
   std::vector<LPFwd> fwds;
-  for (size_t si = 0; si < steps.size(); ++si) {
-    steps[si].fwd_begin = (int)fwds.size();
-    steps[si].nfwd = (int)fwd_of[si].size();
-    for (const LPFwd& f : fwd_of[si]) fwds.push_back(f);
+  {
+    size_t si = 0;
+    for (int r = 0; r < P; ++r)
+      for (int t = 0; t < T; ++t) {
+        const LPLevel& lv = levels[(size_t)r * T + t];
+        for (si = (size_t)lv.step_begin; si < (size_t)lv.step_end; ++si) {
+          std::stable_sort(fwd_of[si].begin(), fwd_of[si].end(),
+                           [&](const LPFwd& a, const LPFwd& b) { return after(r, a.dst_rank) < after(r, b.dst_rank); });
+          steps[si].fwd_begin = (int)fwds.size();
+          steps[si].nfwd = (int)fwd_of[si].size();
+          for (const LPFwd& f : fwd_of[si]) fwds.push_back(f);
+        }
+        std::vector<LPSend>& sd = sends_of[(size_t)r * T + t];
+        std::stable_sort(sd.begin(), sd.end(),
+                         [&](const LPSend& a, const LPSend& b) { return after(r, a.dst_rank) < after(r, b.dst_rank); });
+      }
   }
   // barriers: before level t only if it reads local memory written since the last barrier, or overwrites local
   // memory read or written since then (the caller's input is never written; inbox lines carry their own flags)
@@ -262,6 +278,11 @@ llprog_kernel(World w, const char* __restrict__ blob, LPIo io, int op, float sca
     // a level that touches local memory of the levels before it starts only when those are complete on this rank;
     // all threads take part in the barrier, also those that have given up, and an aborted rank leaves here together
     if (L.barrier_before && !rank_barrier(c, nct, gen, w.timeout_ns, rank, t)) break;
+    // per-level stamps of the first thread (the counterpart of the interpreter's per-round trace): when it starts
+    // the level and when its own share of the level is done
+    unsigned long long* tr = w.trace[rank];
+    const bool stamp = tr && gtid == 0 && t < w.trace_rounds;
+    if (stamp) tr[2 * t] = globaltimer_ns();
     // ---- 1. push what peers' steps of this level read from me (and no step of mine has forwarded already)
     {
       int cur = -1;
@@ -321,6 +342,7 @@ llprog_kernel(World w, const char* __restrict__ blob, LPIo io, int op, float sca
         if (lf >= 0 && lf < F.nlines) st_line(w.ll[F.dst_rank] + (half + F.inbox_line + lf) * 16, v.x, v.y, flag);
       }
     }
+    if (stamp) tr[2 * t + 1] = globaltimer_ns();
   }
   rank_exit(c, nct, [&](Ctrl* cc) { cc->ll_seq = seq + 1ull; });
 }

@@ -263,12 +263,20 @@ def test_round_trace(comms):
     comm.enable_trace(32)
     ins = make_inputs(P, P * 4096, torch.float32)
     prog = comm.program("allreduce", "radix_batch", P * 4096, 2, 4)
-    chb.all_reduce(comm, ins, algo="radix_batch", k=2, b=4)
+    chb.all_reduce(comm, ins, algo="radix_batch:pull", k=2, b=4)
     for r in (0, 5):
         tr = comm.read_trace(prog.nrounds, r)
         assert len(tr) == prog.nrounds
         assert all(e >= s for s, e in tr), tr
         assert all(tr[i + 1][0] >= tr[i][1] - 1e-3 for i in range(len(tr) - 1)), tr   # rounds are ordered
+        assert tr[-1][1] > 0                                                          # and were really stamped
+    # the push form stamps its levels too (first thread of the rank: start of the level, end of its own share)
+    prog_ll = comm.program("allreduce", "radix_batch", P * 4096, 2, 4, in_symmetric=True, out_symmetric=True)
+    chb.all_reduce(comm, ins, algo="radix_batch:ll", k=2, b=4)
+    for r in (0, 5):
+        tr = comm.read_trace(prog_ll.nrounds, r)
+        assert all(e >= s for s, e in tr) and tr[-1][1] > 0, tr
+        assert all(tr[i + 1][0] >= tr[i][0] for i in range(len(tr) - 1)), tr
     comm.enable_trace(0)
     chb.all_reduce(comm, ins, algo="radix_batch", k=2, b=4)
     comm.check()

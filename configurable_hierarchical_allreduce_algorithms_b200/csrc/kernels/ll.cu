@@ -69,38 +69,28 @@ ll_kernel(World w, LLIo io, long long nbytes, int op, float scale, long long lin
     const uint2 mine = load_payload(in + (MODE == LL_RS ? (long long)rank * nbytes : 0ll), l * 8, nbytes);
     Acc a[8 / sizeof(T)];
     bool have = false, failed = false;
-    for (int p = 0; p < P; ++p) {
-      uint2 v;
-      if (p == rank) {
-        v = mine;
-      } else {
-        const char* line = w.ll[rank] + ((half + p) * lines_per_src + l) * 16;
-        unsigned d0, f0, d1, f1;
-        ld_line(line, d0, f0, d1, f1);
-        if (f0 != flag || f1 != flag) {
-          const unsigned long long t0 = globaltimer_ns();
-          unsigned spins = 0;
-          for (;;) {
-            ld_line(line, d0, f0, d1, f1);
-            if (f0 == flag && f1 == flag) break;
-            if ((++spins & 31u) == 0u) {
-              if (ld_volatile_u32(&c->abort)) { failed = true; break; }
-              if (globaltimer_ns() - t0 > w.timeout_ns) {
-                record_timeout(c, ST_TIMEOUT_LL, rank, (int)l, p, flag, f0);
-                failed = true;
-                break;
-              }
-            }
-          }
-        }
-        if (failed) break;
-        v = make_uint2(d0, d1);
+    for (int p0 = 0; p0 < P && !failed; p0 += kLineGroup) {
+      const char* line[kLineGroup];
+      int peer[kLineGroup];
+      uint2 v[kLineGroup];
+#pragma unroll
+      for (int i = 0; i < kLineGroup; ++i) {
+        const int p = p0 + i;
+        peer[i] = p;
+        v[i] = mine;
+        line[i] = (p < P && p != rank) ? w.ll[rank] + ((half + p) * lines_per_src + l) * 16 : nullptr;
       }
-      if (MODE == LL_AG) {
-        store_payload(out + (long long)p * nbytes, l * 8, nbytes, v);
-      } else {
-        if (!have) { payload_to_acc<T>(v, a); have = true; }
-        else payload_combine<T>(op, v, a);
+      if (!poll_lines(line, peer, flag, v, c, w.timeout_ns, rank, l)) { failed = true; break; }
+#pragma unroll
+      for (int i = 0; i < kLineGroup; ++i) {
+        const int p = p0 + i;
+        if (p >= P) continue;
+        if (MODE == LL_AG) {
+          store_payload(out + (long long)p * nbytes, l * 8, nbytes, v[i]);
+        } else {
+          if (!have) { payload_to_acc<T>(v[i], a); have = true; }
+          else payload_combine<T>(op, v[i], a);
+        }
       }
     }
     if (failed) break;
@@ -160,12 +150,26 @@ ll2_kernel(World w, LLIo io, long long total_bytes, long long slice_bytes, int o
   bool failed = false;
   for (long long l = l0; l * 8 < mine_n && !dead && !failed; l += TT) {
     Acc a[8 / sizeof(T)];
-    for (int p = 0; p < P && !failed; ++p) {
-      uint2 v;
-      if (p == rank) v = load_payload(in + (long long)rank * slice_bytes, l * 8, mine_n);
-      else if (!poll_line(w.ll[rank] + ((half + p) * lines_per_src + l) * 16, flag, v, c, w.timeout_ns, rank, l, p)) { failed = true; break; }
-      if (p == 0) payload_to_acc<T>(v, a);
-      else payload_combine<T>(op, v, a);
+    const uint2 mine = load_payload(in + (long long)rank * slice_bytes, l * 8, mine_n);
+    for (int p0 = 0; p0 < P && !failed; p0 += kLineGroup) {
+      const char* line[kLineGroup];
+      int peer[kLineGroup];
+      uint2 v[kLineGroup];
+#pragma unroll
+      for (int i = 0; i < kLineGroup; ++i) {
+        const int p = p0 + i;
+        peer[i] = p;
+        v[i] = mine;
+        line[i] = (p < P && p != rank) ? w.ll[rank] + ((half + p) * lines_per_src + l) * 16 : nullptr;
+      }
+      if (!poll_lines(line, peer, flag, v, c, w.timeout_ns, rank, l)) { failed = true; break; }
+#pragma unroll
+      for (int i = 0; i < kLineGroup; ++i) {
+        const int p = p0 + i;
+        if (p >= P) continue;
+        if (p == 0) payload_to_acc<T>(v[i], a);
+        else payload_combine<T>(op, v[i], a);
+      }
     }
     if (failed) break;
     const uint2 r = acc_to_payload<T>(a, scale, do_scale);
@@ -177,14 +181,21 @@ ll2_kernel(World w, LLIo io, long long total_bytes, long long slice_bytes, int o
   }
   // phase C: collect the other reduced slices
   for (long long l = l0; l < max_lines && !dead && !failed; l += TT)
-    for (int i = 1; i < P; ++i) {
-      const int p = (rank + i) % P;
-      const long long n = slice_len(p);
-      if (l * 8 < n) {
-        uint2 v;
-        if (!poll_line(w.ll[rank] + ((half + p) * lines_per_src + upper + l) * 16, flag, v, c, w.timeout_ns, rank, l, p)) { failed = true; break; }
-        store_payload(out + (long long)p * slice_bytes, l * 8, n, v);
+    for (int i0 = 1; i0 < P && !failed; i0 += kLineGroup) {
+      const char* line[kLineGroup];
+      int peer[kLineGroup];
+      uint2 v[kLineGroup];
+#pragma unroll
+      for (int i = 0; i < kLineGroup; ++i) {
+        const int p = (rank + i0 + i) % P;
+        peer[i] = p;
+        v[i] = make_uint2(0u, 0u);
+        line[i] = (i0 + i < P && l * 8 < slice_len(p)) ? w.ll[rank] + ((half + p) * lines_per_src + upper + l) * 16 : nullptr;
       }
+      if (!poll_lines(line, peer, flag, v, c, w.timeout_ns, rank, l)) { failed = true; break; }
+#pragma unroll
+      for (int i = 0; i < kLineGroup; ++i)
+        if (line[i] != nullptr) store_payload(out + (long long)peer[i] * slice_bytes, l * 8, slice_len(peer[i]), v[i]);
     }
   rank_exit(c, nct, [&](Ctrl* cc) { cc->ll_seq = seq + 1ull; });
 }

@@ -83,4 +83,27 @@ __device__ __forceinline__ bool poll_line(const char* line, unsigned flag, uint2
   return true;
 }
 
+// Several inbox lines at once: every first read is issued before any flag is looked at, so a group of lines
+// that have already arrived costs one memory latency instead of one per line; a line that has not arrived is
+// then polled on its own (bounded).  line[i] == nullptr skips slot i and leaves v[i] alone.
+constexpr int kLineGroup = 4;
+__device__ __forceinline__ bool poll_lines(const char* const (&line)[kLineGroup], const int (&peer)[kLineGroup],
+                                           unsigned flag, uint2 (&v)[kLineGroup], Ctrl* c,
+                                           unsigned long long timeout_ns, int rank, long long l) {
+  unsigned d0[kLineGroup], f0[kLineGroup], d1[kLineGroup], f1[kLineGroup];
+#pragma unroll
+  for (int i = 0; i < kLineGroup; ++i) {
+    d0[i] = d1[i] = 0u;
+    f0[i] = f1[i] = flag;
+    if (line[i] != nullptr) ld_line(line[i], d0[i], f0[i], d1[i], f1[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < kLineGroup; ++i) {
+    if (line[i] == nullptr) continue;
+    if (f0[i] == flag && f1[i] == flag) v[i] = make_uint2(d0[i], d1[i]);
+    else if (!poll_line(line[i], flag, v[i], c, timeout_ns, rank, l, peer[i])) return false;
+  }
+  return true;
+}
+
 }  // namespace chb

@@ -318,17 +318,38 @@ llprog_kernel(World w, const char* __restrict__ blob, LPIo io, int op, float sca
       uint2 v = make_uint2(0u, 0u);
       bool have = false;
       if (acc) { payload_to_acc<T>(load_payload(dst, l * 8, nbytes), a); have = true; }
-      for (int j = 0; j < st.nsrc; ++j) {
-        const LPSrc sc = srcs[st.src_begin + j];
-        if (sc.inbox_line < 0) {
-          const char* base = (sc.buf == 0 ? my_in : (sc.buf == 1 ? my_out : my_work)) + sc.off * (long long)sizeof(T);
-          v = load_payload(base, l * 8, nbytes);
-        } else if (!poll_line(inbox + (sc.inbox_line + l) * 16, flag, v, c, w.timeout_ns, rank, l, sc.peer)) {
-          dead = true;
-          break;
+      // sources four at a time: their table entries are loaded together, their lines are read together (one
+      // memory latency for the group instead of one per source), then combined left to right; a line that has
+      // not arrived yet is polled on its own
+      for (int j0 = 0; j0 < st.nsrc && !dead; j0 += kLineGroup) {
+        const char* line[kLineGroup];
+        int peer[kLineGroup];
+        uint2 x[kLineGroup];
+#pragma unroll
+        for (int jj = 0; jj < kLineGroup; ++jj) {
+          line[jj] = nullptr;
+          peer[jj] = -1;
+          x[jj] = make_uint2(0u, 0u);
+          if (j0 + jj < st.nsrc) {
+            const LPSrc sc = srcs[st.src_begin + j0 + jj];
+            peer[jj] = sc.peer;
+            if (sc.inbox_line >= 0) {
+              line[jj] = inbox + (sc.inbox_line + l) * 16;
+            } else {
+              const char* base = (sc.buf == 0 ? my_in : (sc.buf == 1 ? my_out : my_work)) + sc.off * (long long)sizeof(T);
+              x[jj] = load_payload(base, l * 8, nbytes);
+            }
+          }
         }
-        if (!have) { payload_to_acc<T>(v, a); have = true; }
-        else payload_combine<T>(op, v, a);
+        if (!poll_lines(line, peer, flag, x, c, w.timeout_ns, rank, l)) { dead = true; break; }
+#pragma unroll
+        for (int jj = 0; jj < kLineGroup; ++jj) {
+          if (j0 + jj < st.nsrc) {
+            v = x[jj];
+            if (!have) { payload_to_acc<T>(v, a); have = true; }
+            else payload_combine<T>(op, v, a);
+          }
+        }
       }
       if (dead) break;
       // a plain copy keeps the payload's bits; everything else goes through the accumulator type

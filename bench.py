@@ -175,6 +175,58 @@ def headline_config(N: int, S: int) -> dict:
             "l2": "inputs larger than L2 for the headline; explicit 256 MiB L2 flush before every timed call in the sweep"}
 
 
+def emulated_rows(W: int, K: int) -> list:
+    """Allreduce of eight emulated ranks on the current GPU: every rank's kernel runs in one cooperative launch.
+    Per row: the schedule, the bytes per rank, microseconds per call (CUDA events, L2 flushed before every timed
+    call) and the comparison with an fp64 sum of the inputs."""
+    import torch
+
+    import configurable_hierarchical_allreduce_algorithms_b200 as chb
+    from configurable_hierarchical_allreduce_algorithms_b200.parallel.comm import Communicator
+
+    P = 8
+    comm = Communicator.emulated(P, ll_bytes=1 << 20, scratch_bytes=72 << 20, user_bytes=1 << 20)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    rows = []
+    try:
+        for nbytes in (32 << 10, 1 << 20, 16 << 20):
+            n = nbytes // 4
+            g = torch.Generator(device="cuda").manual_seed(77)
+            ins = [torch.rand(n, generator=g, device="cuda") * 2 - 1 for _ in range(P)]
+            exp = torch.stack([t.double() for t in ins]).sum(0)
+            cands = [("radix_batch:pull", 2, 1), ("radix_batch:pull", 4, 2), ("radix_batch:pull", 8, 8)]
+            if nbytes <= (1 << 20):
+                cands += [("radix_batch:ll", 2, 1), ("radix_batch:ll", 8, 8), ("ll" if nbytes <= (64 << 10) else "ll2", 2, 1)]
+            for algo, k, b in cands:
+                row = {"algo": algo, "k": k, "b": b, "bytes_per_rank": nbytes, "dtype": "fp32"}
+                rows.append(row)
+                try:
+                    outs = chb.all_reduce(comm, ins, algo=algo, k=k, b=b)
+                    torch.cuda.synchronize()
+                    comm.check()
+                except Exception as e:  # noqa: BLE001 - e.g. messages larger than the inbox: say so and go on
+                    row["skipped"] = repr(e)[:120]
+                    comm.clear_error()
+                    continue
+                err = max(float((o.double() - exp).abs().max()) for o in outs)
+                for _ in range(W):
+                    chb.all_reduce(comm, ins, algo=algo, k=k, b=b)
+                ts = []
+                for _ in range(K):
+                    flush.fill_(1)
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    chb.all_reduce(comm, ins, algo=algo, k=k, b=b)
+                    e1.record()
+                    torch.cuda.synchronize()
+                    ts.append(e0.elapsed_time(e1) * 1e3)
+                comm.check()
+                row.update({"us_p50": statistics.median(ts), "is_correct": err <= 1e-4 * P, "max_abs_err": err})
+    finally:
+        comm.close()
+    return rows
+
+
 def reference_arm(args):
     from baseline import reference_bench
 
@@ -209,6 +261,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-emulated", action="store_true", help="skip the emulated 8-rank table of the 1-GPU run")
     ap.add_argument("--bytes", type=int, default=1 << 30, help="allreduce vector bytes per GPU (headline)")
     ap.add_argument("--sweep", default=",".join(str(8 * 4 ** i) for i in range(14)) + ",1073741824",
                     help="comma separated message sizes in bytes for the latency / bandwidth table ('' = none); "
@@ -591,6 +644,17 @@ def main():
         sweep.sort(key=lambda r: (r["bytes"], r["dtype"] != "fp32"))
     scratch_ref = None
 
+    # ---- one GPU has no peers, so the headline above is a copy.  To show the collective kernels themselves on this
+    # GPU too, eight ranks are emulated on it (one cooperative launch runs all ranks; "peer" reads and pushes go
+    # through this GPU's memory instead of NVLink): the hierarchical program in both execution modes and the
+    # flagged-line kernels, checked against an fp64 sum.  These rows say nothing about NVLink.
+    emulated = []
+    if world == 1 and args.sweep and not args.no_emulated:
+        try:
+            emulated = emulated_rows(max(3, W), max(5, min(K, 20)))
+        except Exception as e:  # noqa: BLE001 - an optional table must not cost the headline
+            emulated = [{"error": repr(e)[:200]}]
+
     if rank == 0:
         peaks = {}
         try:
@@ -619,6 +683,8 @@ def main():
             "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "nccl": nccl,
             "grid": grid, "sweep": sweep, "graph_replay_latency": graph_lat,
         }
+        if emulated:
+            out["emulated_8_ranks_on_one_gpu"] = emulated
         print(json.dumps(out), flush=True)
     comm.close()
     if world > 1:

@@ -76,3 +76,32 @@ def test_forked_ranks_one_per_gpu(exe, tmp_path, coll):
     assert (df2.is_correct == 1).all()
     if "skipped" not in r.stderr:
         assert any("nvls" in x for x in set(df2.algorithm_name)), set(df2.algorithm_name)
+
+
+LINKBW = EXE.with_name("chb_linkbw")
+
+
+def test_linkbw_arguments(exe):
+    r = subprocess.run([str(LINKBW), "0"], capture_output=True, text=True)
+    assert r.returncode == 2 and "usage" in r.stderr
+    r = subprocess.run([str(LINKBW), "8", "1"], capture_output=True, text=True)
+    assert r.returncode == 2
+
+
+@pytest.mark.gpu
+def test_linkbw_runs(exe, cuda):
+    """Two GPUs: one CSV row per (width, mode, directions, CTAs) with positive rates, and pulling from the peer is not
+    faster than copying locally.  One GPU: it says what it needs and leaves."""
+    r = subprocess.run([str(LINKBW), "64", "2"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    if torch.cuda.device_count() < 2:
+        assert "needs two GPUs" in r.stdout
+        return
+    if "cannot access" in r.stdout:
+        return
+    import io
+    df = pd.read_csv(io.StringIO(r.stdout))
+    assert len(df) == 2 * 3 * 2 * 4 and (df.GBps_gpu0 > 0).all()
+    pull = df[(df["mode"] == "pull (read peer)") & (df.directions == "both")].GBps_gpu0.max()
+    local = df[(df["mode"] == "local copy") & (df.directions == "both")].GBps_gpu0.max()
+    assert pull < local

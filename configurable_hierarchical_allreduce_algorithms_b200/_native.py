@@ -51,6 +51,12 @@ def _declare(L: C.CDLL) -> None:
     L.chb_program_run_threads.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(vp), i32, C.POINTER(C.c_double)]
     L.chb_program_run_threads_late.restype = i32
     L.chb_program_run_threads_late.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(vp), i32, i32]
+    L.chb_program_ll_lines.restype = C.c_longlong
+    L.chb_program_ll_lines.argtypes = [vp, i32]
+    L.chb_program_ll_info.restype = i32
+    L.chb_program_ll_info.argtypes = [vp, i32, C.POINTER(C.c_longlong), i32]
+    L.chb_program_simulate_ll.restype = i32
+    L.chb_program_simulate_ll.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(vp), u64, i32, i32, cp, i32]
     L.chb_program_export.restype = i32
     L.chb_program_export.argtypes = [vp, vp, vp, vp, vp, vp]
     L.chb_list_algorithms.restype = i32

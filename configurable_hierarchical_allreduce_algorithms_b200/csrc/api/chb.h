@@ -62,6 +62,19 @@ int chb_program_verify(const chb_program_t* p, char* err, int errlen);
 /* run all ranks on host buffers; in[r] / out[r] are rank r's buffers */
 int chb_program_simulate(const chb_program_t* p, int dtype, int op, void* const* in,
                          void* const* out, uint64_t seed, char* err, int errlen);
+/* The push (flagged-line) form of a program, see sched/ll_plan.h.
+ * chb_program_ll_lines: lines the fullest inbox needs for elements of esz bytes (-1: bad argument).
+ * chb_program_ll_info: info = rounds, messages pushed in a round's push phase, messages forwarded line by line
+ *   from the previous round's steps, rank-local barriers (summed over ranks), lines in the fullest inbox, lines
+ *   of the busiest (rank, round).
+ * chb_program_simulate_ll: run that form on host buffers, line by line, nthreads virtual threads per rank
+ *   advanced in a random order (seed); a message that nobody sends ends as CHB_ERR_TIMEOUT with the waiting
+ *   rank and peer in err.  fault: 0, or a defect injected into the plan to test the simulator itself
+ *   (1 = its barriers are ignored, 2 = the last forward of every step is left out). */
+long long chb_program_ll_lines(const chb_program_t* p, int esz);
+int chb_program_ll_info(const chb_program_t* p, int esz, long long* info, int n);
+int chb_program_simulate_ll(const chb_program_t* p, int dtype, int op, void* const* in, void* const* out,
+                            uint64_t seed, int nthreads, int fault, char* err, int errlen);
 /* run all ranks as host threads (real concurrency); mean wall seconds per repetition in *seconds */
 int chb_program_run_threads(const chb_program_t* p, int dtype, int op, void* const* in, void* const* out,
                             int iters, double* seconds);

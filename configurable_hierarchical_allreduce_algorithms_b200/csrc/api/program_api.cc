@@ -4,6 +4,7 @@
 #include <exception>
 #include <string>
 
+#include "../sched/ll_plan.h"
 #include "../sched/algos.h"
 #include "../sched/program.h"
 #include "chb.h"
@@ -110,6 +111,35 @@ int chb_program_simulate(const chb_program_t* p, int dtype, int op, void* const*
   if (!p) return CHB_ERR_ARG;
   std::string e;
   int rc = chb::simulate(p->prog, dtype, op, in, out, seed, &e);
+  if (rc) { set_err(err, errlen, e); return rc == -1 ? CHB_ERR_TIMEOUT : CHB_ERR_ARG; }
+  return CHB_SUCCESS;
+}
+
+long long chb_program_ll_lines(const chb_program_t* p, int esz) {
+  if (!p || esz < 1) return -1;
+  return chb::ll_inbox_lines(p->prog, esz);
+}
+
+int chb_program_ll_info(const chb_program_t* p, int esz, long long* info, int n) {
+  if (!p || !info || esz < 1) return CHB_ERR_ARG;
+  chb::LPHeader h{};
+  std::vector<char> blob = chb::make_ll_blob(p->prog, esz, &h);
+  const chb::LPLevel* lv = reinterpret_cast<const chb::LPLevel*>(blob.data() + h.off_levels);
+  long long barriers = 0;
+  for (long long i = 0; i < (long long)h.P * h.nlevels; ++i) barriers += lv[i].barrier_before;
+  long long forwarded = 0;
+  const chb::LPStep* st = reinterpret_cast<const chb::LPStep*>(blob.data() + h.off_steps);
+  for (int i = 0; i < h.nsteps; ++i) forwarded += st[i].nfwd;
+  const long long v[6] = {h.nlevels, h.nsends, forwarded, barriers, h.inbox_lines, h.max_level_lines};
+  for (int i = 0; i < n && i < 6; ++i) info[i] = v[i];
+  return CHB_SUCCESS;
+}
+
+int chb_program_simulate_ll(const chb_program_t* p, int dtype, int op, void* const* in, void* const* out,
+                            uint64_t seed, int nthreads, int fault, char* err, int errlen) {
+  if (!p || !in || !out || fault < 0 || fault > 2) return CHB_ERR_ARG;
+  std::string e;
+  int rc = chb::simulate_ll(p->prog, dtype, op, in, out, seed, nthreads, fault, &e);
   if (rc) { set_err(err, errlen, e); return rc == -1 ? CHB_ERR_TIMEOUT : CHB_ERR_ARG; }
   return CHB_SUCCESS;
 }

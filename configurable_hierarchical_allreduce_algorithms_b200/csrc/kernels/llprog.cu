@@ -43,6 +43,7 @@
 
 #include "../api/chb.h"
 #include "../api/program_handle.h"
+#include "../sched/ll_plan.h"
 #include "../symm/comm.h"
 #include "common.cuh"
 #include "ll_lines.cuh"
@@ -51,183 +52,10 @@ namespace chb {
 
 constexpr int kLPThreads = 512;
 
-struct LPLevel { int step_begin, step_end, send_begin, send_end; long long step_lines, send_lines; int barrier_before, pad; };
-struct LPStep { long long dst_off, count, line_prefix; int dst_buf, nsrc, src_begin; unsigned flags; int fwd_begin, nfwd; };
-// lines [line_begin, line_begin + nlines) of a step's result go to inbox_line.. of dst_rank as they are produced
-struct LPFwd { long long line_begin, nlines, inbox_line; int dst_rank, pad; };
-struct LPSrc { long long off, inbox_line; int peer, buf; };          // inbox_line < 0: local source
-struct LPSend { long long src_off, count, inbox_line, line_prefix; int dst_rank, src_buf; };
-struct LPHeader {
-  int P, nlevels, nsteps, nsrcs, nsends, esz;
-  long long off_levels, off_steps, off_srcs, off_sends, off_fwds;
-  long long max_level_lines;     // busiest (rank, level): lines pushed + lines executed
-  long long inbox_lines;         // lines needed in the fullest inbox
-};
-
 struct LPIo {
   const char* in[kMaxRanks];
   char* out[kMaxRanks];
 };
-
-static long long lines_of(long long count, int esz) { return (count * esz + 7) / 8; }
-
-// Flatten a lowered program into the level tables above for elements of `esz` bytes.
-static std::vector<char> make_ll_blob(const Program& p, int esz, LPHeader* hout) {
-  const int P = p.P, T = p.nrounds;
-  std::vector<LPLevel> levels((size_t)P * T);
-  std::vector<LPStep> steps;
-  std::vector<LPSrc> srcs;
-  std::vector<std::vector<LPSend>> sends_of((size_t)P * T);
-  std::vector<long long> inbox(P, 0);
-  LPHeader h{};
-  // steps in (rank, level) order; every remote source gets its inbox slot and its owner a send
-  for (int r = 0; r < P; ++r)
-    for (int t = 0; t < T; ++t) {
-      LPLevel& lv = levels[(size_t)r * T + t];
-      lv.step_begin = (int)steps.size();
-      long long pre = 0;
-      for (int oi : p.rr[r][t].ops) {
-        const Op& o = p.ops[oi];
-        LPStep s{};
-        s.dst_off = o.dst_off;
-        s.count = o.count;
-        s.dst_buf = o.dst_buf;
-        s.flags = o.flags | (o.acc ? 0x100u : 0u);
-        s.src_begin = (int)srcs.size();
-        s.nsrc = (int)o.srcs.size();
-        s.line_prefix = pre;
-        const long long nl = lines_of(o.count, esz);
-        pre += nl;
-        for (const Src& x : o.srcs) {
-          LPSrc d{x.off, -1, x.peer, x.buf};
-          if (x.peer != r) {
-            d.inbox_line = inbox[r];
-            inbox[r] += nl;
-            sends_of[(size_t)x.peer * T + t].push_back(LPSend{x.off, o.count, d.inbox_line, 0, r, x.buf});
-          }
-          srcs.push_back(d);
-        }
-        steps.push_back(s);
-      }
-      lv.step_end = (int)steps.size();
-      lv.step_lines = pre;
-    }
-  // forwarding: a send of level t + 1 whose source lies inside the destination of ONE step of level t (same
-  // buffer, offset difference a whole number of lines) is issued by that step's threads instead
-  std::vector<std::vector<LPFwd>> fwd_of(steps.size());
-  for (int r = 0; r < P; ++r)
-    for (int t = 0; t + 1 < T; ++t) {
-      const LPLevel& lv = levels[(size_t)r * T + t];
-      std::vector<LPSend>& next = sends_of[(size_t)r * T + t + 1];
-      std::vector<LPSend> keep;
-      for (const LPSend& sd : next) {
-        bool done = false;
-        for (int si = lv.step_begin; si < lv.step_end && !done; ++si) {
-          const LPStep& st = steps[(size_t)si];
-          if (st.dst_buf != sd.src_buf || sd.src_off < st.dst_off || sd.src_off + sd.count > st.dst_off + st.count) continue;
-          const long long delta = (sd.src_off - st.dst_off) * esz;
-          if (delta % 8) continue;
-          fwd_of[(size_t)si].push_back(LPFwd{delta / 8, lines_of(sd.count, esz), sd.inbox_line, sd.dst_rank, 0});
-          done = true;
-        }
-        if (!done) keep.push_back(sd);
-      }
-      next.swap(keep);
-    }
-  // Every sender starts with the receiver after itself and goes round from there (pushes of a level and
-  // forwards of a step alike): at any moment the P senders aim at P different receivers, instead of all
-  // filling receiver 0's inbox first, then receiver 1's, ... with one ingress link busy and the others idle.
-  auto after = [P](int sender, int dst) { return (dst - sender - 1 + P) % P; };
-  std::vector<LPFwd> fwds;
-  {
-    size_t si = 0;
-    for (int r = 0; r < P; ++r)
-      for (int t = 0; t < T; ++t) {
-        const LPLevel& lv = levels[(size_t)r * T + t];
-        for (si = (size_t)lv.step_begin; si < (size_t)lv.step_end; ++si) {
-          std::stable_sort(fwd_of[si].begin(), fwd_of[si].end(),
-                           [&](const LPFwd& a, const LPFwd& b) { return after(r, a.dst_rank) < after(r, b.dst_rank); });
-          steps[si].fwd_begin = (int)fwds.size();
-          steps[si].nfwd = (int)fwd_of[si].size();
-          for (const LPFwd& f : fwd_of[si]) fwds.push_back(f);
-        }
-        std::vector<LPSend>& sd = sends_of[(size_t)r * T + t];
-        std::stable_sort(sd.begin(), sd.end(),
-                         [&](const LPSend& a, const LPSend& b) { return after(r, a.dst_rank) < after(r, b.dst_rank); });
-      }
-  }
-  // barriers: before level t only if it reads local memory written since the last barrier, or overwrites local
-  // memory read or written since then (the caller's input is never written; inbox lines carry their own flags)
-  struct Reg { int buf; long long lo, hi; };
-  auto hits = [](const std::vector<Reg>& a, const Reg& x) {
-    for (const Reg& y : a)
-      if (y.buf == x.buf && x.lo < y.hi && y.lo < x.hi) return true;
-    return false;
-  };
-  for (int r = 0; r < P; ++r) {
-    std::vector<Reg> wr, rd;
-    for (int t = 0; t < T; ++t) {
-      LPLevel& lv = levels[(size_t)r * T + t];
-      std::vector<Reg> reads, writes;
-      for (int si = lv.step_begin; si < lv.step_end; ++si) {
-        const LPStep& st = steps[(size_t)si];
-        writes.push_back(Reg{st.dst_buf, st.dst_off, st.dst_off + st.count});
-        if (st.flags & 0x100u) reads.push_back(Reg{st.dst_buf, st.dst_off, st.dst_off + st.count});
-        for (int j = 0; j < st.nsrc; ++j) {
-          const LPSrc& x = srcs[(size_t)st.src_begin + j];
-          if (x.inbox_line < 0) reads.push_back(Reg{x.buf, x.off, x.off + st.count});
-        }
-      }
-      for (const LPSend& sd : sends_of[(size_t)r * T + t]) reads.push_back(Reg{sd.src_buf, sd.src_off, sd.src_off + sd.count});
-      bool need = false;
-      for (const Reg& x : reads) need = need || hits(wr, x);
-      for (const Reg& x : writes) need = need || hits(wr, x) || hits(rd, x);
-      lv.barrier_before = (t > 0 && need) ? 1 : 0;
-      if (lv.barrier_before) { wr.clear(); rd.clear(); }
-      wr.insert(wr.end(), writes.begin(), writes.end());
-      rd.insert(rd.end(), reads.begin(), reads.end());
-    }
-  }
-  std::vector<LPSend> sends;
-  for (int r = 0; r < P; ++r)
-    for (int t = 0; t < T; ++t) {
-      LPLevel& lv = levels[(size_t)r * T + t];
-      lv.send_begin = (int)sends.size();
-      long long pre = 0;
-      for (LPSend s : sends_of[(size_t)r * T + t]) {
-        s.line_prefix = pre;
-        pre += lines_of(s.count, esz);
-        sends.push_back(s);
-      }
-      lv.send_end = (int)sends.size();
-      lv.send_lines = pre;
-      h.max_level_lines = std::max(h.max_level_lines, lv.send_lines + lv.step_lines);
-    }
-  h.P = P;
-  h.nlevels = T;
-  h.nsteps = (int)steps.size();
-  h.nsrcs = (int)srcs.size();
-  h.nsends = (int)sends.size();
-  h.esz = esz;
-  for (int r = 0; r < P; ++r) h.inbox_lines = std::max(h.inbox_lines, inbox[r]);
-  auto al = [](size_t x) { return (x + 15) / 16 * 16; };
-  size_t off = al(sizeof(LPHeader));
-  h.off_levels = (long long)off; off = al(off + levels.size() * sizeof(LPLevel));
-  h.off_steps = (long long)off;  off = al(off + steps.size() * sizeof(LPStep));
-  h.off_srcs = (long long)off;   off = al(off + srcs.size() * sizeof(LPSrc));
-  h.off_sends = (long long)off;  off = al(off + sends.size() * sizeof(LPSend));
-  h.off_fwds = (long long)off;   off = al(off + fwds.size() * sizeof(LPFwd));
-  std::vector<char> blob(off, 0);
-  std::memcpy(blob.data(), &h, sizeof(h));
-  auto put = [&](long long o, const void* src, size_t n) { if (n) std::memcpy(blob.data() + o, src, n); };
-  put(h.off_levels, levels.data(), levels.size() * sizeof(LPLevel));
-  put(h.off_steps, steps.data(), steps.size() * sizeof(LPStep));
-  put(h.off_srcs, srcs.data(), srcs.size() * sizeof(LPSrc));
-  put(h.off_sends, sends.data(), sends.size() * sizeof(LPSend));
-  put(h.off_fwds, fwds.data(), fwds.size() * sizeof(LPFwd));
-  *hout = h;
-  return blob;
-}
 
 // Index of the item in [begin, end) whose line range holds global line gl (prefixes ascend from 0).
 template <typename Item>
@@ -357,10 +185,21 @@ llprog_kernel(World w, const char* __restrict__ blob, LPIo io, int op, float sca
         v = acc_to_payload<T>(a, scale, do_scale && (st.flags & OPF_FINAL));
       store_payload(dst, l * 8, nbytes, v);
       // the next level's readers of this line get it now, from registers
-      for (int f = 0; f < st.nfwd; ++f) {
-        const LPFwd F = fwds[st.fwd_begin + f];
-        const long long lf = l - F.line_begin;
-        if (lf >= 0 && lf < F.nlines) st_line(w.ll[F.dst_rank] + (half + F.inbox_line + lf) * 16, v.x, v.y, flag);
+      // (table entries four at a time, so that their loads overlap instead of queueing behind the stores)
+      for (int f0 = 0; f0 < st.nfwd; f0 += kLineGroup) {
+        char* to[kLineGroup];
+#pragma unroll
+        for (int i = 0; i < kLineGroup; ++i) {
+          to[i] = nullptr;
+          if (f0 + i < st.nfwd) {
+            const LPFwd F = fwds[st.fwd_begin + f0 + i];
+            const long long lf = l - F.line_begin;
+            if (lf >= 0 && lf < F.nlines) to[i] = w.ll[F.dst_rank] + (half + F.inbox_line + lf) * 16;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < kLineGroup; ++i)
+          if (to[i] != nullptr) st_line(to[i], v.x, v.y, flag);
       }
     }
     if (stamp) tr[2 * t + 1] = globaltimer_ns();
@@ -387,37 +226,6 @@ static LPFn pick_lp(int dtype) {
 using namespace chb;
 
 extern "C" {
-
-// Lines the fullest inbox needs when program p runs with flagged lines on elements of esz bytes,
-// or -1 if the program is not eligible (see chb_run_program_ll).
-long long chb_program_ll_lines(const chb_program* p, int esz) {
-  if (!p || esz < 1) return -1;
-  long long worst = 0;
-  std::vector<long long> inbox(p->prog.P, 0);
-  for (const Op& o : p->prog.ops)
-    for (const Src& x : o.srcs)
-      if (x.peer != o.rank) inbox[o.rank] += lines_of(o.count, esz);
-  for (long long v : inbox) worst = std::max(worst, v);
-  return worst;
-}
-
-// What the flagged-line form of a program looks like, for tests and tuning: info = levels, messages pushed in a
-// level's push phase, messages forwarded line by line from the previous level's steps, rank-local barriers (summed
-// over ranks), lines in the fullest inbox, lines of the busiest (rank, level).
-int chb_program_ll_info(const chb_program* p, int esz, long long* info, int n) {
-  if (!p || !info || esz < 1) return CHB_ERR_ARG;
-  LPHeader h{};
-  std::vector<char> blob = make_ll_blob(p->prog, esz, &h);
-  const LPLevel* lv = reinterpret_cast<const LPLevel*>(blob.data() + h.off_levels);
-  long long barriers = 0;
-  for (long long i = 0; i < (long long)h.P * h.nlevels; ++i) barriers += lv[i].barrier_before;
-  long long forwarded = 0;
-  const LPStep* st = reinterpret_cast<const LPStep*>(blob.data() + h.off_steps);
-  for (int i = 0; i < h.nsteps; ++i) forwarded += st[i].nfwd;
-  const long long v[6] = {h.nlevels, h.nsends, forwarded, barriers, h.inbox_lines, h.max_level_lines};
-  for (int i = 0; i < n && i < 6; ++i) info[i] = v[i];
-  return CHB_SUCCESS;
-}
 
 // Run a compiled program with flagged lines (see the head of this file).  The program must have been
 // lowered with in_symmetric and out_symmetric set (no staging copies are wanted: nobody reads a peer's

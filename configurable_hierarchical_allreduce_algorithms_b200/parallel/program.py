@@ -169,15 +169,34 @@ class Program:
             raise RuntimeError(f"simulate({self.name}) failed: {err.value.decode()}")
         return [o[:self.out_elems] for o in outs]
 
+    def simulate_ll(self, inputs: list[np.ndarray], op: str = "sum", seed: int = 0, threads: int = 5,
+                    fault: int = 0) -> list[np.ndarray]:
+        """Run the push (flagged-line) form of this program on host arrays, line by line, the way the GPU executor
+        does: ``threads`` virtual threads per rank, advanced in a random order drawn from ``seed``; only the plan's
+        own messages, forwards and barriers order them.  The program must have been lowered with
+        ``in_symmetric=True, out_symmetric=True`` (the push form has no staging copies).  ``fault`` injects a defect
+        into the plan to test the simulator itself: 1 ignores the plan's barriers, 2 drops one forward per step."""
+        assert len(inputs) == self.P
+        dt = inputs[0].dtype
+        code = _DT_FROM_NP[np.dtype(dt)]
+        ins = [np.ascontiguousarray(x, dtype=dt) for x in inputs]
+        for x in ins:
+            assert x.size == self.in_elems, (x.size, self.in_elems)
+        poison = 239 if np.dtype(dt).kind == "u" else -17
+        outs = [np.full(self.out_elems, poison, dtype=dt) for _ in range(self.P)]
+        ip = (C.c_void_p * self.P)(*[x.ctypes.data for x in ins])
+        opp = (C.c_void_p * self.P)(*[x.ctypes.data for x in outs])
+        err = C.create_string_buffer(512)
+        rc = N.lib().chb_program_simulate_ll(self._h, code, _OPS[op], ip, opp, seed, threads, fault, err, len(err))
+        if rc:
+            raise RuntimeError(f"simulate_ll({self.name}) failed: {err.value.decode()}")
+        return outs
+
     def ll_info(self, elem_bytes: int = 4) -> dict:
         """Shape of the flagged-line (push) form of this program: rounds, messages pushed per round's push phase,
         messages forwarded line by line from the previous round's steps, rank-local barriers (all ranks), lines in
         the fullest inbox and in the busiest (rank, round)."""
         L = N.lib()
-        if not hasattr(L, "chb_program_ll_info"):
-            raise N.NativeLibraryMissing("libchb.so was built without its CUDA half")
-        L.chb_program_ll_info.restype = C.c_int
-        L.chb_program_ll_info.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_longlong), C.c_int]
         v = (C.c_longlong * 6)()
         rc = L.chb_program_ll_info(self._h, elem_bytes, v, 6)
         if rc:

@@ -49,3 +49,118 @@ def test_element_size_scales_the_lines():
     prog = _prog("allreduce", "recursive_doubling", P, n, 2, 1)
     assert prog.ll_info(8)["inbox_lines"] == 2 * prog.ll_info(4)["inbox_lines"]
     assert prog.ll_info(2)["inbox_lines"] * 4 == prog.ll_info(8)["inbox_lines"]
+
+
+# ---- the push form executed on the host, line by line (csrc/sched/ll_plan.cc: simulate_ll) ----
+import numpy as np  # noqa: E402
+
+from configurable_hierarchical_allreduce_algorithms_b200.parallel.program import ProgramError, list_algorithms  # noqa: E402
+
+
+def _pattern(P, n, dt, seed=5):
+    return [((seed * 31 + r * 1009 + np.arange(n) * 7) % 97).astype(dt) for r in range(P)]
+
+
+def _expected(coll, ins, P, n):
+    if coll == "allgather":
+        return [np.concatenate(ins)] * P
+    tot = ins[0].copy()
+    for x in ins[1:]:
+        tot = tot + x
+    return [tot] * P if coll == "allreduce" else [tot[r * n:(r + 1) * n] for r in range(P)]
+
+
+def _check(coll, algo, P, n, k, b, dt=np.int32, threads=5, seeds=(0, 1, 2)):
+    count = n * P if coll == "allreduce" else n
+    prog = _prog(coll, algo, P, count, k, b)
+    ins = _pattern(P, prog.in_elems, dt)
+    exp = _expected(coll, ins, P, n)
+    for seed in seeds:
+        outs = prog.simulate_ll(ins, seed=seed, threads=threads)
+        for r in range(P):
+            np.testing.assert_array_equal(outs[r], exp[r], err_msg=f"{coll}/{algo} P={P} n={n} k={k} b={b} rank {r} seed {seed}")
+    return prog
+
+
+@pytest.mark.parametrize("coll", ["allreduce", "reduce_scatter", "allgather"])
+@pytest.mark.parametrize("P", [2, 3, 4, 6, 8, 12])
+def test_radix_batch_push_form_on_the_host(coll, P):
+    """Every (k, b) shape: inbox slots, pushes, line-level forwards and the barriers that were kept give the sum / the
+    concatenation under random interleavings of the ranks' threads.  Odd counts leave partial last lines."""
+    for b in [d for d in range(1, P + 1) if P % d == 0]:
+        for k in (2, 3, 4, 8):
+            for n in (1, 5, 16):
+                _check(coll, "radix_batch", P, n, k, b)
+
+
+@pytest.mark.parametrize("coll", ["allreduce", "reduce_scatter", "allgather"])
+def test_every_algorithm_push_form_on_the_host(coll):
+    ran = 0
+    for algo in list_algorithms(coll):
+        for P in (2, 4, 5, 8):
+            for k, b in ((2, 1), (4, 2)):
+                if P % b:
+                    continue
+                try:
+                    _check(coll, algo, P, 7, k, b, seeds=(0, 3))
+                    ran += 1
+                except ProgramError:
+                    pass     # shape not defined for this algorithm (e.g. a power-of-two baseline at P = 5)
+    assert ran > 10
+
+
+@pytest.mark.parametrize("dt", [np.uint8, np.int64, np.float64, np.float32])
+def test_push_form_element_sizes(dt):
+    """1-, 4- and 8-byte elements: 8, 2 and 1 elements per line, forwards at offsets that are whole lines only."""
+    for P, k, b in ((4, 2, 2), (8, 2, 1), (8, 8, 8), (6, 3, 2)):
+        _check("allreduce", "radix_batch", P, 3, k, b, dt=dt)
+        _check("allreduce", "radix_batch", P, 8, k, b, dt=dt)
+
+
+def test_push_form_matches_the_pull_form_bit_for_bit_on_floats():
+    """Both forms add in the program's order, so floats that do not add exactly agree to the last bit."""
+    P, n = 8, 33
+    rng = np.random.default_rng(3)
+    ins = [rng.standard_normal(n * P).astype(np.float32) for _ in range(P)]
+    for k, b in ((2, 1), (2, 4), (4, 2), (8, 8)):
+        prog = _prog("allreduce", "radix_batch", P, n * P, k, b)
+        pull = prog.simulate(ins, seed=1)
+        push = prog.simulate_ll(ins, seed=2, threads=7)
+        for r in range(P):
+            assert pull[r].tobytes() == push[r].tobytes()
+
+
+def test_one_thread_per_rank_and_many():
+    for threads in (1, 2, 64):
+        _check("allreduce", "radix_batch", 8, 16, 2, 2, threads=threads, seeds=(0,))
+
+
+def test_staged_program_is_refused():
+    prog = Program("allreduce", "radix_batch", 4, 64, 2, 1)      # lowered with staging copies
+    with pytest.raises(RuntimeError, match="staging"):
+        prog.simulate_ll(_pattern(4, 64, np.int32))
+
+
+def test_the_simulator_notices_a_plan_without_its_barriers():
+    """The in-place form reads a staged copy of its input, so it keeps barriers; with the barriers ignored, threads
+    that own different lines in consecutive rounds read the copy before it is complete."""
+    P, n = 4, 64
+    prog = _prog("allreduce", "radix_batch", P, n * P, 2, 1, in_place=True)
+    assert prog.ll_info(4)["barriers"] > 0
+    ins = _pattern(P, prog.in_elems, np.int32)
+    exp = _expected("allreduce", ins, P, n)
+    wrong = 0
+    for threads in (7, 64):
+        for seed in range(6):
+            outs = prog.simulate_ll(ins, seed=seed, threads=threads)
+            assert all((outs[r] == exp[r]).all() for r in range(P))
+            outs = prog.simulate_ll(ins, seed=seed, threads=threads, fault=1)
+            wrong += any((outs[r] != exp[r]).any() for r in range(P))
+    assert wrong > 0
+
+
+def test_the_simulator_notices_a_message_that_nobody_sends():
+    P, n = 8, 16
+    prog = _prog("allreduce", "radix_batch", P, n * P, 2, 1)
+    with pytest.raises(RuntimeError, match=r"deadlock: rank \d+ level \d+ waits for line \d+ from rank \d+"):
+        prog.simulate_ll(_pattern(P, prog.in_elems, np.int32), fault=2)

@@ -56,6 +56,8 @@ def candidates(coll: str, P: int, nbytes: int, comm, total: int | None = None) -
         flat = b == 1
         if total <= (4 << 20):                       # owners push flagged lines: one traversal per round
             out.append(("radix_batch:ll", k, b, 0))
+            if flat and total >= (1 << 20):          # the default stops at 64 CTAs
+                out.append(("radix_batch:ll", k, b, 128))
         if total <= (64 << 10):                      # readers pull: the persistent interpreter
             out.append(("radix_batch:pull", k, b, 1))
         elif total <= (4 << 20):

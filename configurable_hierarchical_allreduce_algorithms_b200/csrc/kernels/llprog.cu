@@ -51,6 +51,7 @@
 namespace chb {
 
 constexpr int kLPThreads = 512;
+constexpr int kLPMaxCtas = 128;   // an explicit request may go this far; the default stops at 64
 
 struct LPIo {
   const char* in[kMaxRanks];
@@ -282,7 +283,7 @@ int chb_run_program_ll(chb_comm* c, const chb_program* p, int dtype, int op, con
     nctas = (int)((hd.max_level_lines + kLPThreads * 4 - 1) / (kLPThreads * 4));
     if (nctas > 64) nctas = 64;
   }
-  if (nctas > 64) nctas = 64;
+  if (nctas > kLPMaxCtas) nctas = kLPMaxCtas;
   if (nctas > budget) nctas = budget;
   if (nctas < 1) nctas = 1;
   dim3 grid((unsigned)nctas, (unsigned)c->nlocal, 1), block(kLPThreads, 1, 1);

@@ -51,6 +51,7 @@
 namespace chb {
 
 constexpr int kLPThreads = 512;
+constexpr long long kLPSmemTables = 40 << 10;   // bytes of table entries a CTA keeps in shared memory
 constexpr int kLPMaxCtas = 128;   // an explicit request may go this far; the default stops at 64
 
 struct LPIo {
@@ -72,12 +73,18 @@ __device__ __forceinline__ int find_item(const Item* items, int begin, int end, 
 
 template <typename T>
 __global__ void __launch_bounds__(kLPThreads, 1)
-llprog_kernel(World w, const char* __restrict__ blob, LPIo io, int op, float scale, long long lines_per_src) {
+llprog_kernel(World w, const char* __restrict__ blob, LPIo io, int op, float scale, long long lines_per_src,
+              int tables_in_smem) {
   using Acc = typename Elem<T>::Acc;
   constexpr int PE = (int)(8 / sizeof(T));     // elements per line
+  extern __shared__ __align__(16) unsigned char lp_tables[];
   const int rank = w.rank0 + (int)blockIdx.y;
   const unsigned nct = gridDim.x;
   Ctrl* c = w.ctrl[rank];
+  // the launch number and the abort word are asked for first, so that they travel while the tables are fetched
+  unsigned long long seq_first = 0ull;
+  int abort_first = 0;
+  if (threadIdx.x == 0) { seq_first = ld_volatile_u64(&c->ll_seq); abort_first = ld_volatile_u32(&c->abort); }
   const LPHeader* h = reinterpret_cast<const LPHeader*>(blob);
   const int nlevels = h->nlevels;
   const LPLevel* levels = reinterpret_cast<const LPLevel*>(blob + h->off_levels) + (size_t)rank * nlevels;
@@ -85,9 +92,41 @@ llprog_kernel(World w, const char* __restrict__ blob, LPIo io, int op, float sca
   const LPSrc* srcs = reinterpret_cast<const LPSrc*>(blob + h->off_srcs);
   const LPSend* sends = reinterpret_cast<const LPSend*>(blob + h->off_sends);
   const LPFwd* fwds = reinterpret_cast<const LPFwd*>(blob + h->off_fwds);
+  if (tables_in_smem) {
+    // This rank's own table entries move into shared memory: every lookup below (which send or step owns a line,
+    // its sources, its forwards) is then a shared-memory access instead of a chain of dependent global loads,
+    // which is most of the time of a small message.  One 8-byte word per thread and table first, all loads issued
+    // before any store, so the five tables arrive together; loops take what is left of a long table.
+    const LPRank R = reinterpret_cast<const LPRank*>(blob + kLPRanksOffset)[rank];
+    const unsigned long long* g[5] = {
+        reinterpret_cast<const unsigned long long*>(levels), reinterpret_cast<const unsigned long long*>(steps + R.step0),
+        reinterpret_cast<const unsigned long long*>(srcs + R.src0), reinterpret_cast<const unsigned long long*>(sends + R.send0),
+        reinterpret_cast<const unsigned long long*>(fwds + R.fwd0)};
+    const int words[5] = {nlevels * (int)(sizeof(LPLevel) / 8), R.nstep * (int)(sizeof(LPStep) / 8), R.nsrc * (int)(sizeof(LPSrc) / 8),
+                          R.nsend * (int)(sizeof(LPSend) / 8), R.nfwd * (int)(sizeof(LPFwd) / 8)};
+    unsigned long long* s[5];
+    s[0] = reinterpret_cast<unsigned long long*>(lp_tables);
+#pragma unroll
+    for (int k = 1; k < 5; ++k) s[k] = s[k - 1] + words[k - 1];
+    unsigned long long first[5];
+#pragma unroll
+    for (int k = 0; k < 5; ++k) first[k] = (int)threadIdx.x < words[k] ? g[k][threadIdx.x] : 0ull;
+#pragma unroll
+    for (int k = 0; k < 5; ++k)
+      if ((int)threadIdx.x < words[k]) s[k][threadIdx.x] = first[k];
+#pragma unroll
+    for (int k = 0; k < 5; ++k)
+      for (int i = (int)threadIdx.x + (int)blockDim.x; i < words[k]; i += (int)blockDim.x) s[k][i] = g[k][i];
+    // the tables keep their global indices: each pointer is moved back by the index of the rank's first entry
+    levels = reinterpret_cast<const LPLevel*>(s[0]);
+    steps = reinterpret_cast<const LPStep*>(s[1]) - R.step0;
+    srcs = reinterpret_cast<const LPSrc*>(s[2]) - R.src0;
+    sends = reinterpret_cast<const LPSend*>(s[3]) - R.send0;
+    fwds = reinterpret_cast<const LPFwd*>(s[4]) - R.fwd0;
+  }
   __shared__ unsigned long long s_seq;
   __shared__ int s_abort;
-  if (threadIdx.x == 0) { s_seq = ld_volatile_u64(&c->ll_seq); s_abort = ld_volatile_u32(&c->abort); }
+  if (threadIdx.x == 0) { s_seq = seq_first; s_abort = abort_first; }
   __syncthreads();
   const unsigned long long seq = s_seq;
   bool dead = s_abort != 0;                 // this thread does no more work (an expired wait, or an aborted rank)
@@ -208,7 +247,7 @@ llprog_kernel(World w, const char* __restrict__ blob, LPIo io, int op, float sca
   rank_exit(c, nct, [&](Ctrl* cc) { cc->ll_seq = seq + 1ull; });
 }
 
-typedef void (*LPFn)(World, const char*, LPIo, int, float, long long);
+typedef void (*LPFn)(World, const char*, LPIo, int, float, long long, int);
 static LPFn pick_lp(int dtype) {
   switch (dtype) {
     case DT_F32: return llprog_kernel<float>;
@@ -256,7 +295,8 @@ int chb_run_program_ll(chb_comm* c, const chb_program* p, int dtype, int op, con
   auto it = c->ll_blobs.find(key);
   if (it != c->ll_blobs.end()) {
     blob = it->second.first;
-    hd.max_level_lines = it->second.second;
+    hd.max_level_lines = it->second.second.first;
+    hd.rank_table_bytes = it->second.second.second;
   } else {
     std::vector<char> host = make_ll_blob(g, esz, &hd);
     if (hd.inbox_lines > (long long)c->P * (long long)c->ll_lines_per_src) {
@@ -269,7 +309,7 @@ int chb_run_program_ll(chb_comm* c, const chb_program* p, int dtype, int op, con
       c->last_error = "cudaMemcpy(program lines) failed";
       return CHB_ERR_CUDA;
     }
-    c->ll_blobs[key] = {blob, hd.max_level_lines};
+    c->ll_blobs[key] = {blob, {hd.max_level_lines, hd.rank_table_bytes}};
   }
   LPIo io{};
   for (int l = 0; l < c->nlocal; ++l) {
@@ -290,10 +330,13 @@ int chb_run_program_ll(chb_comm* c, const chb_program* p, int dtype, int op, con
   World w = c->world;
   const char* bp = (const char*)blob;
   long long lps = (long long)c->ll_lines_per_src;
-  void* args[] = {&w, &bp, &io, &op, &scale, &lps};
+  // a rank's own table entries go to shared memory when they fit what every kernel may have without opting in
+  int in_smem = hd.rank_table_bytes > 0 && hd.rank_table_bytes <= kLPSmemTables ? 1 : 0;
+  const size_t smem = in_smem ? (size_t)hd.rank_table_bytes : 0;
+  void* args[] = {&w, &bp, &io, &op, &scale, &lps, &in_smem};
   cudaError_t e;
-  if (c->nlocal > 1 || nctas > 1) e = cudaLaunchCooperativeKernel((const void*)fn, grid, block, args, 0, stream);
-  else e = cudaLaunchKernel((const void*)fn, grid, block, args, 0, stream);
+  if (c->nlocal > 1 || nctas > 1) e = cudaLaunchCooperativeKernel((const void*)fn, grid, block, args, smem, stream);
+  else e = cudaLaunchKernel((const void*)fn, grid, block, args, smem, stream);
   if (e != cudaSuccess) { c->last_error = std::string("flagged-line program launch failed: ") + cudaGetErrorString(e); return CHB_ERR_CUDA; }
   return CHB_SUCCESS;
 }

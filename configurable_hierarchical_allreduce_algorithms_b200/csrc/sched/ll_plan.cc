@@ -152,8 +152,29 @@ std::vector<char> make_ll_blob(const Program& p, int esz, LPHeader* hout) {
   h.nsends = (int)sends.size();
   h.esz = esz;
   for (int r = 0; r < P; ++r) h.inbox_lines = std::max(h.inbox_lines, inbox[r]);
+  // every rank's own entries, for executors that keep them close (shared memory on the GPU)
+  std::vector<LPRank> ranks((size_t)P);
+  for (int r = 0; r < P && T > 0; ++r) {
+    LPRank& R = ranks[(size_t)r];
+    const LPLevel& first = levels[(size_t)r * T];
+    const LPLevel& last = levels[(size_t)r * T + T - 1];
+    R.step0 = first.step_begin;
+    R.nstep = last.step_end - first.step_begin;
+    R.send0 = first.send_begin;
+    R.nsend = last.send_end - first.send_begin;
+    R.src0 = R.nstep ? steps[(size_t)R.step0].src_begin : 0;
+    R.fwd0 = R.nstep ? steps[(size_t)R.step0].fwd_begin : 0;
+    for (int i = 0; i < R.nstep; ++i) {
+      R.nsrc += steps[(size_t)(R.step0 + i)].nsrc;
+      R.nfwd += steps[(size_t)(R.step0 + i)].nfwd;
+    }
+    const long long bytes = (long long)T * sizeof(LPLevel) + (long long)R.nstep * sizeof(LPStep) + (long long)R.nsrc * sizeof(LPSrc) +
+                            (long long)R.nsend * sizeof(LPSend) + (long long)R.nfwd * sizeof(LPFwd);
+    h.rank_table_bytes = std::max(h.rank_table_bytes, bytes);
+  }
   auto al = [](size_t x) { return (x + 15) / 16 * 16; };
-  size_t off = al(sizeof(LPHeader));
+  size_t off = (size_t)kLPRanksOffset;
+  h.off_ranks = (long long)off;  off = al(off + ranks.size() * sizeof(LPRank));
   h.off_levels = (long long)off; off = al(off + levels.size() * sizeof(LPLevel));
   h.off_steps = (long long)off;  off = al(off + steps.size() * sizeof(LPStep));
   h.off_srcs = (long long)off;   off = al(off + srcs.size() * sizeof(LPSrc));
@@ -162,6 +183,7 @@ std::vector<char> make_ll_blob(const Program& p, int esz, LPHeader* hout) {
   std::vector<char> blob(off, 0);
   std::memcpy(blob.data(), &h, sizeof(h));
   auto put = [&](long long o, const void* src, size_t n) { if (n) std::memcpy(blob.data() + o, src, n); };
+  put(h.off_ranks, ranks.data(), ranks.size() * sizeof(LPRank));
   put(h.off_levels, levels.data(), levels.size() * sizeof(LPLevel));
   put(h.off_steps, steps.data(), steps.size() * sizeof(LPStep));
   put(h.off_srcs, srcs.data(), srcs.size() * sizeof(LPSrc));

@@ -23,17 +23,23 @@ struct LPStep { long long dst_off, count, line_prefix; int dst_buf, nsrc, src_be
 struct LPFwd { long long line_begin, nlines, inbox_line; int dst_rank, pad; };
 struct LPSrc { long long off, inbox_line; int peer, buf; };          // inbox_line < 0: local source
 struct LPSend { long long src_off, count, inbox_line, line_prefix; int dst_rank, src_buf; };
+// the entries of one rank are contiguous in every table: [first, first + n)
+struct LPRank { int step0, nstep, src0, nsrc, send0, nsend, fwd0, nfwd; };
 struct LPHeader {
   int P, nlevels, nsteps, nsrcs, nsends, esz;
-  long long off_levels, off_steps, off_srcs, off_sends, off_fwds;
+  long long off_ranks, off_levels, off_steps, off_srcs, off_sends, off_fwds;
   long long max_level_lines;     // busiest (rank, level): lines pushed + lines executed
   long long inbox_lines;         // lines needed in the fullest inbox
+  long long rank_table_bytes;    // bytes of the largest rank's own entries (levels, steps, sources, sends, forwards)
 };
+// LPRank[P] follows the header at this fixed offset, so that a rank can fetch its ranges and the header together
+constexpr long long kLPRanksOffset = 128;
+static_assert(sizeof(LPHeader) <= kLPRanksOffset, "the rank table starts right after the header");
 
 inline long long ll_lines_of(long long count, int esz) { return (count * esz + 7) / 8; }
 
-// Flatten a lowered program into the tables above for elements of esz bytes.  Layout of the result: LPHeader, then
-// at the header's offsets LPLevel[P * nlevels] (rank-major), LPStep[], LPSrc[], LPSend[], LPFwd[].
+// Flatten a lowered program into the tables above for elements of esz bytes.  Layout of the result: LPHeader, LPRank[P]
+// at kLPRanksOffset, then at the header's offsets LPLevel[P * nlevels] (rank-major), LPStep[], LPSrc[], LPSend[], LPFwd[].
 std::vector<char> make_ll_blob(const Program& p, int esz, LPHeader* hout);
 
 // Lines the fullest inbox needs (without building the tables).

@@ -40,7 +40,7 @@ struct chb_comm {
   std::map<uint64_t, void*> blobs;
   // flagged-line form of compiled programs: key = program id * 16 + element size; value = device tables
   // and the line count of the busiest level (sizes the grid)
-  std::map<uint64_t, std::pair<void*, long long>> ll_blobs;
+  std::map<uint64_t, std::pair<void*, std::pair<long long, long long>>> ll_blobs;   // blob, (busiest level lines, largest rank table bytes)
   std::string last_error;
   // set only by the native constructors (chb_comm_create_ipc / chb_comm_create_emulated), which own the heap
   void* owned_heap = nullptr;

@@ -39,6 +39,12 @@ struct DevHeader {
   long long off_rounds, off_steps, off_srcs, off_waits, off_sigs, off_exit, off_order;
   long long limit[3];   // elements of the caller input, caller output and scratch (for range checks)
 };
+// The entries of one rank are contiguous in every table: [first, first + n).  DevRank[P] follows the header at a
+// fixed offset, so that a rank fetches its ranges together with the header.
+struct DevRank { int step0, nstep, src0, nsrc, wait0, nwait, sig0, nsig, ord0, nord, exit0, nexit; };
+constexpr long long kDevRanksOffset = 128;
+static_assert(sizeof(DevHeader) <= kDevRanksOffset, "the rank table starts right after the header");
+constexpr long long kInterpSmemTables = 40 << 10;   // bytes of table entries a CTA keeps in shared memory
 
 struct IoTable {
   const char* in[kMaxRanks];
@@ -63,7 +69,7 @@ static bool ranges_ok(const Program& p, std::string* why) {
   return true;
 }
 
-static std::vector<char> make_blob(const Program& p) {
+static std::vector<char> make_blob(const Program& p, long long* rank_table_bytes) {
   DevHeader h{};
   h.P = p.P;
   h.nrounds = p.nrounds;
@@ -124,8 +130,29 @@ static std::vector<char> make_blob(const Program& p) {
   h.nsrcs = (int)srcs.size();
   h.nwaits = (int)waits.size();
   h.nsigs = (int)sigs.size();
+  std::vector<DevRank> ranks((size_t)p.P);
+  long long worst = 0;
+  for (int r = 0; r < p.P && p.nrounds > 0; ++r) {
+    DevRank& R = ranks[(size_t)r];
+    const DevRound& first = rounds[(size_t)r * p.nrounds];
+    const DevRound& last = rounds[(size_t)r * p.nrounds + p.nrounds - 1];
+    R.step0 = first.step_begin;  R.nstep = last.step_end - first.step_begin;
+    R.wait0 = first.wait_begin;  R.nwait = last.wait_end - first.wait_begin;
+    R.sig0 = first.sig_begin;    R.nsig = last.sig_end - first.sig_begin;
+    R.ord0 = first.ord_begin;    R.nord = R.nstep;
+    R.src0 = R.nstep ? steps[(size_t)R.step0].src_begin : 0;
+    for (int i = 0; i < R.nstep; ++i) R.nsrc += steps[(size_t)(R.step0 + i)].nsrc;
+    R.exit0 = exits[2 * (size_t)r];
+    R.nexit = exits[2 * (size_t)r + 1] - exits[2 * (size_t)r];
+    const long long bytes = (long long)p.nrounds * sizeof(DevRound) + (long long)R.nstep * sizeof(DevStep) +
+                            (long long)R.nsrc * sizeof(DevSrc) + (long long)(R.nwait + R.nexit) * sizeof(DevWait) +
+                            (long long)(R.nsig + R.nord) * sizeof(int);
+    worst = std::max(worst, bytes);
+  }
+  if (rank_table_bytes) *rank_table_bytes = worst;
   auto al = [](size_t x) { return (x + 15) / 16 * 16; };
-  size_t off = al(sizeof(DevHeader));
+  size_t off = (size_t)kDevRanksOffset;
+  off = al(off + ranks.size() * sizeof(DevRank));
   h.off_rounds = (long long)off; off = al(off + rounds.size() * sizeof(DevRound));
   h.off_steps = (long long)off;  off = al(off + steps.size() * sizeof(DevStep));
   h.off_srcs = (long long)off;   off = al(off + srcs.size() * sizeof(DevSrc));
@@ -136,6 +163,7 @@ static std::vector<char> make_blob(const Program& p) {
   std::vector<char> blob(off, 0);
   std::memcpy(blob.data(), &h, sizeof(h));
   auto put = [&](long long o, const void* src, size_t n) { if (n) std::memcpy(blob.data() + o, src, n); };
+  put(kDevRanksOffset, ranks.data(), ranks.size() * sizeof(DevRank));
   put(h.off_rounds, rounds.data(), rounds.size() * sizeof(DevRound));
   put(h.off_steps, steps.data(), steps.size() * sizeof(DevStep));
   put(h.off_srcs, srcs.data(), srcs.size() * sizeof(DevSrc));
@@ -339,13 +367,76 @@ __device__ __forceinline__ void run_step(const DevStep& st, const DevSrc* __rest
 constexpr long long kTileGrain = 16 << 10;        // tiles are multiples of this (keeps 32-byte alignment for every type)
 constexpr long long kTileMin = 16 << 10, kTileMax = 1 << 20;   // 16 KiB = one 32-byte vector per thread of a CTA
 
+// This rank's own table entries move into shared memory: a round then finds its waits, steps, sources and signals
+// there instead of through a chain of dependent global loads (about ten of them per launch of a two-round program).
+// One word per thread and table first, all loads issued before any store, so that the tables arrive together;
+// loops take what is left of a long table.  The tables keep their global indices: each returned pointer is moved
+// back by the index of the rank's first entry.  Round waits and exit waits sit in two places of one global table
+// and become two tables here.  (Not inlined: the interpreter's own register allocation stays as it is.)  The
+// caller synchronises the CTA before the first use.
+struct RankTables {
+  const DevRound* rounds;
+  const DevStep* steps;
+  const DevSrc* srcs;
+  const DevWait* waits;
+  const DevWait* exit_waits;
+  const int* sigs;
+  const int* order;
+  int n_exit;
+};
+__device__ __noinline__ RankTables tables_to_smem(const char* __restrict__ blob, const DevHeader* h, int rank, unsigned char* smem) {
+  const int tid = threadIdx.x;
+  const int nrounds = h->nrounds;
+  const DevRank R = reinterpret_cast<const DevRank*>(blob + kDevRanksOffset)[rank];
+  constexpr int NT = 7;
+  const unsigned* g[NT] = {
+      reinterpret_cast<const unsigned*>(reinterpret_cast<const DevRound*>(blob + h->off_rounds) + (size_t)rank * nrounds),
+      reinterpret_cast<const unsigned*>(reinterpret_cast<const DevStep*>(blob + h->off_steps) + R.step0),
+      reinterpret_cast<const unsigned*>(reinterpret_cast<const DevSrc*>(blob + h->off_srcs) + R.src0),
+      reinterpret_cast<const unsigned*>(reinterpret_cast<const DevWait*>(blob + h->off_waits) + R.wait0),
+      reinterpret_cast<const unsigned*>(reinterpret_cast<const DevWait*>(blob + h->off_waits) + R.exit0),
+      reinterpret_cast<const unsigned*>(reinterpret_cast<const int*>(blob + h->off_sigs) + R.sig0),
+      reinterpret_cast<const unsigned*>(reinterpret_cast<const int*>(blob + h->off_order) + R.ord0)};
+  const int words[NT] = {nrounds * (int)(sizeof(DevRound) / 4), R.nstep * (int)(sizeof(DevStep) / 4),
+                         R.nsrc * (int)(sizeof(DevSrc) / 4), R.nwait * (int)(sizeof(DevWait) / 4),
+                         R.nexit * (int)(sizeof(DevWait) / 4), R.nsig, R.nord};
+  unsigned* s[NT];
+  s[0] = reinterpret_cast<unsigned*>(smem);
+#pragma unroll
+  for (int k = 1; k < NT; ++k) s[k] = s[k - 1] + ((words[k - 1] + 1) & ~1);     // 8-byte aligned starts
+  unsigned first[NT];
+#pragma unroll
+  for (int k = 0; k < NT; ++k) first[k] = tid < words[k] ? g[k][tid] : 0u;
+#pragma unroll
+  for (int k = 0; k < NT; ++k)
+    if (tid < words[k]) s[k][tid] = first[k];
+#pragma unroll
+  for (int k = 0; k < NT; ++k)
+    for (int i = tid + (int)blockDim.x; i < words[k]; i += (int)blockDim.x) s[k][i] = g[k][i];
+  RankTables t;
+  t.rounds = reinterpret_cast<const DevRound*>(s[0]);
+  t.steps = reinterpret_cast<const DevStep*>(s[1]) - R.step0;
+  t.srcs = reinterpret_cast<const DevSrc*>(s[2]) - R.src0;
+  t.waits = reinterpret_cast<const DevWait*>(s[3]) - R.wait0;
+  t.exit_waits = reinterpret_cast<const DevWait*>(s[4]);
+  t.sigs = reinterpret_cast<const int*>(s[5]) - R.sig0;
+  t.order = reinterpret_cast<const int*>(s[6]) - R.ord0;
+  t.n_exit = R.nexit;
+  return t;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kInterpThreads, 1)
-interp_kernel(World w, const char* __restrict__ blob, IoTable io, int op, float scale) {
+interp_kernel(World w, const char* __restrict__ blob, IoTable io, int op, float scale, int tables_in_smem) {
+  extern __shared__ __align__(16) unsigned char interp_tables[];
   const int rank = w.rank0 + (int)blockIdx.y;
   const unsigned nct = gridDim.x, cta = blockIdx.x;
   const int tid = threadIdx.x;
   Ctrl* c = w.ctrl[rank];
+  // the epoch and the abort word are asked for first, so that they travel while the tables are fetched
+  unsigned long long epoch_first = 0ull;
+  unsigned abort_first = 0u;
+  if (tid == 0) { epoch_first = ld_volatile_u64(&c->epoch); abort_first = ld_volatile_u32(&c->abort); }
   const DevHeader* h = reinterpret_cast<const DevHeader*>(blob);
   const DevRound* rounds = reinterpret_cast<const DevRound*>(blob + h->off_rounds) + (size_t)rank * h->nrounds;
   const DevStep* steps = reinterpret_cast<const DevStep*>(blob + h->off_steps);
@@ -355,14 +446,27 @@ interp_kernel(World w, const char* __restrict__ blob, IoTable io, int op, float 
   const int* exits = reinterpret_cast<const int*>(blob + h->off_exit);
   const int* order = reinterpret_cast<const int*>(blob + h->off_order);
   const int P = h->P, nrounds = h->nrounds;
+  const DevWait* exit_waits = nullptr;   // this rank's exit waits; looked up in the global table when left null
+  int n_exit = -1;
+  if (tables_in_smem) {
+    const RankTables tb = tables_to_smem(blob, h, rank, interp_tables);
+    rounds = tb.rounds;
+    steps = tb.steps;
+    srcs = tb.srcs;
+    waits = tb.waits;
+    sigs = tb.sigs;
+    order = tb.order;
+    exit_waits = tb.exit_waits;
+    n_exit = tb.n_exit;
+  }
 
   __shared__ unsigned long long s_base;
   __shared__ int s_ok;
   __shared__ const char* s_ptr[kMaxSrc + 1];
   __shared__ int s_meta[4];
   if (tid == 0) {
-    s_base = ld_volatile_u64(&c->epoch);
-    s_ok = ld_volatile_u32(&c->abort) ? 0 : 1;
+    s_base = epoch_first;
+    s_ok = abort_first ? 0 : 1;
   }
   __syncthreads();
   const unsigned long long base = s_base;
@@ -437,8 +541,12 @@ interp_kernel(World w, const char* __restrict__ blob, IoTable io, int op, float 
   }
   // peers that read this rank's caller buffers directly must be done with them
   if (ok) {
-    for (int i = exits[2 * rank] + tid; i < exits[2 * rank + 1]; i += blockDim.x) {
-      const DevWait wt = waits[i];
+    if (n_exit < 0) {
+      exit_waits = waits + exits[2 * rank];
+      n_exit = exits[2 * rank + 1] - exits[2 * rank];
+    }
+    for (int i = tid; i < n_exit; i += blockDim.x) {
+      const DevWait wt = exit_waits[i];
       wait_flag_ge(&w.sig[rank][wt.peer], base + (unsigned long long)wt.need + 1ull, c, w.timeout_ns,
                    ST_TIMEOUT_EXIT, rank, nrounds, wt.peer);
     }
@@ -477,7 +585,7 @@ local_copy_kernel(Ctrl* c, const char* __restrict__ src, char* __restrict__ dst,
   rank_exit(c, gridDim.x, [&](Ctrl* cc) { cc->epoch = cc->epoch + (unsigned long long)nrounds; });
 }
 
-typedef void (*InterpFn)(World, const char*, IoTable, int, float);
+typedef void (*InterpFn)(World, const char*, IoTable, int, float, int);
 
 static InterpFn pick_kernel(int dtype) {
   switch (dtype) {
@@ -504,7 +612,8 @@ static int get_blob(chb_comm* c, const chb_program* p, void** out) {
   if (it != c->blobs.end()) { *out = it->second; return CHB_SUCCESS; }
   if (p->prog.stats.max_nsrc > kMaxSrc) { c->last_error = "program has a step with too many sources"; return CHB_ERR_UNSUPPORTED; }
   if (!ranges_ok(p->prog, &c->last_error)) return CHB_ERR_ARG;
-  std::vector<char> blob = make_blob(p->prog);
+  long long table_bytes = 0;
+  std::vector<char> blob = make_blob(p->prog, &table_bytes);
   void* d = nullptr;
   if (cudaMalloc(&d, blob.size()) != cudaSuccess) { c->last_error = "cudaMalloc(program blob) failed"; return CHB_ERR_NO_MEM; }
   if (cudaMemcpy(d, blob.data(), blob.size(), cudaMemcpyHostToDevice) != cudaSuccess) {
@@ -513,6 +622,7 @@ static int get_blob(chb_comm* c, const chb_program* p, void** out) {
     return CHB_ERR_CUDA;
   }
   c->blobs[p->uid] = d;
+  c->blob_table_bytes[p->uid] = table_bytes;
   *out = d;
   return CHB_SUCCESS;
 }
@@ -527,7 +637,7 @@ void chb_program_release(chb_comm* c, const chb_program* p) {
   if (!c) return;
   if (!p) return;
   auto it = c->blobs.find(p->uid);
-  if (it != c->blobs.end()) { cudaFree(it->second); c->blobs.erase(it); }
+  if (it != c->blobs.end()) { cudaFree(it->second); c->blobs.erase(it); c->blob_table_bytes.erase(p->uid); }
   for (auto jt = c->ll_blobs.lower_bound(p->uid * 16u); jt != c->ll_blobs.end() && jt->first < (p->uid + 1) * 16u;) {
     cudaFree(jt->second.first);
     jt = c->ll_blobs.erase(jt);
@@ -610,10 +720,14 @@ int chb_run_program(chb_comm* c, const chb_program* p, int dtype, int op, const 
   dim3 grid((unsigned)nctas, (unsigned)c->nlocal, 1), block(kInterpThreads, 1, 1);
   World w = c->world;
   const char* blobp = (const char*)blob;
-  void* args[] = {&w, &blobp, &io, &op, &scale};
+  // a rank's own table entries go to shared memory when they fit what every kernel may have without opting in
+  const long long table_bytes = c->blob_table_bytes[p->uid];
+  int in_smem = table_bytes > 0 && table_bytes + 64 <= kInterpSmemTables && tables_in_smem_wanted() ? 1 : 0;
+  const size_t smem = in_smem ? (size_t)table_bytes + 64 : 0;      // + the padding between the tables
+  void* args[] = {&w, &blobp, &io, &op, &scale, &in_smem};
   cudaError_t e;
-  if (c->nlocal > 1 || nctas > 1) e = cudaLaunchCooperativeKernel((const void*)fn, grid, block, args, 0, stream);
-  else e = cudaLaunchKernel((const void*)fn, grid, block, args, 0, stream);
+  if (c->nlocal > 1 || nctas > 1) e = cudaLaunchCooperativeKernel((const void*)fn, grid, block, args, smem, stream);
+  else e = cudaLaunchKernel((const void*)fn, grid, block, args, smem, stream);
   if (e != cudaSuccess) {
     c->last_error = std::string("interp launch failed: ") + cudaGetErrorString(e);
     return CHB_ERR_CUDA;

@@ -151,28 +151,89 @@ llprog_kernel(World w, const char* __restrict__ blob, LPIo io, int op, float sca
     unsigned long long* tr = w.trace[rank];
     const bool stamp = tr && gtid == 0 && t < w.trace_rounds;
     if (stamp) tr[2 * t] = globaltimer_ns();
-    // ---- 1. push what peers' steps of this level read from me (and no step of mine has forwarded already)
+    // ---- 1. push what peers' steps of this level read from me (and no step of mine has forwarded already):
+    // four lines of a thread at a time, all payload loads issued before the first store
     {
       int cur = -1;
       LPSend S{};
       long long end = 0;
-      for (long long gl = gtid; gl < L.send_lines && !dead; gl += TT) {
-        if (cur < 0 || gl >= end) {
-          cur = find_item(sends, L.send_begin, L.send_end, gl);
-          S = sends[cur];
-          end = S.line_prefix + (S.count * (long long)sizeof(T) + 7) / 8;
+      for (long long gl0 = gtid; gl0 < L.send_lines && !dead; gl0 += kLineGroup * TT) {
+        const char* from[kLineGroup];
+        char* to[kLineGroup];
+        long long at[kLineGroup], len[kLineGroup];
+#pragma unroll
+        for (int u = 0; u < kLineGroup; ++u) {
+          const long long gl = gl0 + u * TT;
+          from[u] = nullptr;
+          to[u] = nullptr;
+          at[u] = len[u] = 0;
+          if (gl < L.send_lines) {
+            if (cur < 0 || gl >= end) {
+              cur = find_item(sends, L.send_begin, L.send_end, gl);
+              S = sends[cur];
+              end = S.line_prefix + (S.count * (long long)sizeof(T) + 7) / 8;
+            }
+            const long long l = gl - S.line_prefix;
+            from[u] = (S.src_buf == 0 ? my_in : (S.src_buf == 1 ? my_out : my_work)) + S.src_off * (long long)sizeof(T);
+            at[u] = l * 8;
+            len[u] = S.count * (long long)sizeof(T);
+            to[u] = w.ll[S.dst_rank] + (half + S.inbox_line + l) * 16;
+          }
         }
-        const long long l = gl - S.line_prefix;
-        const char* base = (S.src_buf == 0 ? my_in : (S.src_buf == 1 ? my_out : my_work)) + S.src_off * (long long)sizeof(T);
-        const uint2 v = load_payload(base, l * 8, S.count * (long long)sizeof(T));
-        st_line(w.ll[S.dst_rank] + (half + S.inbox_line + l) * 16, v.x, v.y, flag);
+        uint2 v[kLineGroup];
+#pragma unroll
+        for (int u = 0; u < kLineGroup; ++u) v[u] = from[u] ? load_payload(from[u], at[u], len[u]) : make_uint2(0u, 0u);
+#pragma unroll
+        for (int u = 0; u < kLineGroup; ++u)
+          if (to[u]) st_line(to[u], v[u].x, v[u].y, flag);
       }
     }
     // ---- 2. my steps of this level
     int cur = -1;
     LPStep st{};
     long long end = 0;
-    for (long long gl = gtid; gl < L.step_lines && !dead; gl += TT) {
+    // a level of plain copies (an allgather round): four lines of a thread at a time, their inbox lines read together
+    for (long long gl0 = gtid; L.all_copy && gl0 < L.step_lines && !dead; gl0 += kLineGroup * TT) {
+      const char* line[kLineGroup];
+      int peer[kLineGroup], item[kLineGroup];
+      long long at[kLineGroup];
+      uint2 x[kLineGroup];
+#pragma unroll
+      for (int u = 0; u < kLineGroup; ++u) {
+        const long long gl = gl0 + u * TT;
+        line[u] = nullptr;
+        peer[u] = -1;
+        item[u] = 0;
+        at[u] = 0;
+        x[u] = make_uint2(0u, 0u);
+        if (gl < L.step_lines) {
+          if (cur < 0 || gl >= end) {
+            cur = find_item(steps, L.step_begin, L.step_end, gl);
+            st = steps[cur];
+            end = st.line_prefix + (st.count * (long long)sizeof(T) + 7) / 8;
+          }
+          const LPSrc sc = srcs[st.src_begin];
+          item[u] = cur;
+          at[u] = gl - st.line_prefix;
+          peer[u] = sc.peer;
+          line[u] = inbox + (sc.inbox_line + at[u]) * 16;
+        }
+      }
+      if (!poll_lines(line, peer, flag, x, c, w.timeout_ns, rank, gl0)) { dead = true; break; }
+#pragma unroll
+      for (int u = 0; u < kLineGroup; ++u) {
+        if (line[u] == nullptr) continue;
+        const LPStep s2 = steps[item[u]];
+        char* dst = (s2.dst_buf == 1 ? my_out : my_work) + s2.dst_off * (long long)sizeof(T);
+        store_payload(dst, at[u] * 8, s2.count * (long long)sizeof(T), x[u]);
+        for (int f = 0; f < s2.nfwd; ++f) {
+          const LPFwd F = fwds[s2.fwd_begin + f];
+          const long long lf = at[u] - F.line_begin;
+          if (lf >= 0 && lf < F.nlines) st_line(w.ll[F.dst_rank] + (half + F.inbox_line + lf) * 16, x[u].x, x[u].y, flag);
+        }
+      }
+    }
+    for (long long gl = gtid; !L.all_copy && gl < L.step_lines && !dead; gl += TT) {
       if (cur < 0 || gl >= end) {
         cur = find_item(steps, L.step_begin, L.step_end, gl);
         st = steps[cur];
@@ -331,7 +392,7 @@ int chb_run_program_ll(chb_comm* c, const chb_program* p, int dtype, int op, con
   const char* bp = (const char*)blob;
   long long lps = (long long)c->ll_lines_per_src;
   // a rank's own table entries go to shared memory when they fit what every kernel may have without opting in
-  int in_smem = hd.rank_table_bytes > 0 && hd.rank_table_bytes <= kLPSmemTables ? 1 : 0;
+  int in_smem = hd.rank_table_bytes > 0 && hd.rank_table_bytes <= kLPSmemTables && tables_in_smem_wanted() ? 1 : 0;
   const size_t smem = in_smem ? (size_t)hd.rank_table_bytes : 0;
   void* args[] = {&w, &bp, &io, &op, &scale, &lps, &in_smem};
   cudaError_t e;

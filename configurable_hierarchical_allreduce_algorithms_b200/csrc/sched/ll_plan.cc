@@ -140,6 +140,11 @@ std::vector<char> make_ll_blob(const Program& p, int esz, LPHeader* hout) {
       for (const Reg& x : reads) need = need || hits(wr, x);
       for (const Reg& x : writes) need = need || hits(wr, x) || hits(rd, x);
       lv.barrier_before = (t > 0 && need) ? 1 : 0;
+      lv.all_copy = lv.step_end > lv.step_begin ? 1 : 0;
+      for (int si = lv.step_begin; si < lv.step_end; ++si) {
+        const LPStep& st = steps[(size_t)si];
+        if (st.nsrc != 1 || (st.flags & (0x100u | OPF_FINAL)) || srcs[(size_t)st.src_begin].inbox_line < 0) lv.all_copy = 0;
+      }
       if (lv.barrier_before) { wr.clear(); rd.clear(); }
       wr.insert(wr.end(), writes.begin(), writes.end());
       rd.insert(rd.end(), reads.begin(), reads.end());

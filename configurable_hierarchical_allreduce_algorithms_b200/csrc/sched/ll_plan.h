@@ -17,7 +17,9 @@
 
 namespace chb {
 
-struct LPLevel { int step_begin, step_end, send_begin, send_end; long long step_lines, send_lines; int barrier_before, pad; };
+// all_copy: every step of the level stores one remote source unchanged (an allgather round): the executor then
+// takes several lines of a thread at once
+struct LPLevel { int step_begin, step_end, send_begin, send_end; long long step_lines, send_lines; int barrier_before, all_copy; };
 struct LPStep { long long dst_off, count, line_prefix; int dst_buf, nsrc, src_begin; unsigned flags; int fwd_begin, nfwd; };
 // lines [line_begin, line_begin + nlines) of a step's result go to inbox_line.. of dst_rank as they are produced
 struct LPFwd { long long line_begin, nlines, inbox_line; int dst_rank, pad; };

@@ -12,6 +12,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdlib>
 #include <map>
 #include <string>
 #include <vector>
@@ -38,6 +39,7 @@ struct chb_comm {
   int sm_count = 0;
   // device copies of compiled programs, keyed by the program's unique id
   std::map<uint64_t, void*> blobs;
+  std::map<uint64_t, long long> blob_table_bytes;   // per program: bytes of the largest rank's own table entries
   // flagged-line form of compiled programs: key = program id * 16 + element size; value = device tables
   // and the line count of the busiest level (sizes the grid)
   std::map<uint64_t, std::pair<void*, std::pair<long long, long long>>> ll_blobs;   // blob, (busiest level lines, largest rank table bytes)
@@ -60,3 +62,13 @@ struct chb_comm {
     return heap[peer] + (c - b);
   }
 };
+
+// CHB_TABLES_IN_SMEM=0 keeps the program kernels' schedule tables in global memory (for A/B timing and debugging)
+inline bool tables_in_smem_wanted() {
+  static const bool on = [] {
+    const char* e = std::getenv("CHB_TABLES_IN_SMEM");
+    return !(e && e[0] == '0');
+  }();
+  return on;
+}
+

@@ -569,3 +569,35 @@ def test_tile_scheduler_large_steps(comms, k, b):
     outs = chb.all_reduce(comm, [x.contiguous() for x in ins], algo="radix_batch:pull", k=k, b=b, nctas=4)
     check(outs[P - 1], ref_reduce(ins, "sum"), torch.float32, P)
     comm.check()
+
+
+def test_schedule_tables_in_global_memory(cuda):
+    """Both program kernels keep their rank's schedule tables in shared memory when they fit; the other path (tables
+    read from global memory, what a very long schedule gets) is chosen per process, so it runs in a child."""
+    import os
+    import subprocess
+    import sys
+    code = r"""
+import torch
+import configurable_hierarchical_allreduce_algorithms_b200 as chb
+from configurable_hierarchical_allreduce_algorithms_b200.parallel.comm import Communicator
+P, n = 8, 8 * 1031
+comm = Communicator.emulated(P, scratch_bytes=8 << 20, user_bytes=1 << 20)
+g = torch.Generator(device="cuda").manual_seed(5)
+ins = [torch.randint(-50, 50, (n,), generator=g, device="cuda", dtype=torch.int32) for _ in range(P)]
+exp = torch.stack(ins).sum(0)
+for algo, k, b in (("radix_batch:pull", 2, 1), ("radix_batch:pull", 2, 4), ("radix_batch:ll", 2, 1), ("radix_batch:ll", 4, 2),
+                   ("ring:pull", 2, 1), ("recursive_doubling:ll", 2, 1)):
+    outs = chb.all_reduce(comm, ins, algo=algo, k=k, b=b)
+    torch.cuda.synchronize()
+    comm.check()
+    assert all(torch.equal(o, exp) for o in outs), algo
+outs = chb.all_gather(comm, [x[:1031].contiguous() for x in ins], algo="radix_batch:ll", k=2, b=2)
+assert all(torch.equal(o, torch.cat([x[:1031] for x in ins])) for o in outs)
+comm.close()
+print("tables in global memory: ok")
+"""
+    env = dict(os.environ, CHB_TABLES_IN_SMEM="0")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, env=env,
+                       cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0 and "tables in global memory: ok" in r.stdout, r.stdout + r.stderr

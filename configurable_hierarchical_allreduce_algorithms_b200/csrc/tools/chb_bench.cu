@@ -38,6 +38,10 @@
 
 namespace {
 
+// payload bytes one source may have in flight in a rank's flagged-line inbox (per launch parity): a 4 MiB
+// allreduce still fits as a push program on 2 to 8 GPUs; the inbox takes 16 * P * this many bytes of each heap
+constexpr size_t kInboxBytes = 4u << 20;
+
 struct Opts {
   int n_iter = 0;
   bool overwrite = false;
@@ -397,11 +401,11 @@ int main(int argc, char** argv) {
       if (!vmm_env || std::strcmp(vmm_env, "0") != 0) {
         const char* nvls_env = std::getenv("CHB_NVLS");
         int code = 0;
-        c = chb_comm_create_vmm(boot, 1 << 20, 4 * total + (32u << 20), o.symmetric ? 2 * total + 4096 : 4096,
+        c = chb_comm_create_vmm(boot, kInboxBytes, 4 * total + (32u << 20), o.symmetric ? 2 * total + 4096 : 4096,
                                 (nvls_env && !std::strcmp(nvls_env, "0")) ? 0 : 1, &code, err, sizeof err);
         if (!c && code != CHB_ERR_UNSUPPORTED) { std::fprintf(stderr, "rank %d: communicator: %s\n", r, err); chb_bootstrap_destroy(boot); _exit(1); }
       }
-      if (!c) c = chb_comm_create_ipc(boot, 1 << 20, 4 * total + (32u << 20), o.symmetric ? 2 * total + 4096 : 4096, err, sizeof err);
+      if (!c) c = chb_comm_create_ipc(boot, kInboxBytes, 4 * total + (32u << 20), o.symmetric ? 2 * total + 4096 : 4096, err, sizeof err);
       if (!c) { std::fprintf(stderr, "rank %d: communicator: %s\n", r, err); chb_bootstrap_destroy(boot); _exit(1); }
       int rc = run(o, c, boot, P, r, 1, P);
       if (rc == 1) chb_bootstrap_abort(boot);      // the others stop waiting for this rank

@@ -132,7 +132,7 @@ class Communicator:
         return self
 
     @classmethod
-    def from_process_group(cls, group=None, backend: str | None = None, ll_bytes: int = 1 << 20,
+    def from_process_group(cls, group=None, backend: str | None = None, ll_bytes: int = 4 << 20,
                            scratch_bytes: int = 256 << 20, user_bytes: int = 64 << 20,
                            timeout_us: int = 10_000_000):
         """One rank per process.  ``backend``: "symm_mem" (VMM + NVLS multicast via
@@ -186,7 +186,7 @@ class Communicator:
         return self
 
     @classmethod
-    def from_shared_memory(cls, name: str, rank: int, world: int, ll_bytes: int = 1 << 20,
+    def from_shared_memory(cls, name: str, rank: int, world: int, ll_bytes: int = 4 << 20,
                            scratch_bytes: int = 256 << 20, user_bytes: int = 64 << 20,
                            timeout_us: int = 10_000_000, rendezvous_timeout_ms: int = 60_000,
                            heap: str = "auto", multicast: bool = True):

@@ -167,8 +167,10 @@ int chb_collective(chb_comm* c, int coll, const char* algo, int k, int b, int au
     }
   }
   algo = name.c_str();
-  const bool ll_kind = coll == CHB_ALLREDUCE || coll == CHB_REDUCE_SCATTER || coll == CHB_ALLGATHER;
-  if (mode == 1 && !ll_kind) { c->last_error = "flagged-line execution covers allreduce, reduce-scatter and allgather"; return CHB_ERR_UNSUPPORTED; }
+  // (the launch-parity argument of the inbox needs every rank's result to depend on every rank's input: a gather
+  // or a stand-alone phase does not qualify)
+  const bool ll_kind = coll == CHB_ALLREDUCE || coll == CHB_REDUCE_SCATTER || coll == CHB_ALLGATHER || coll == CHB_ALLTOALL;
+  if (mode == 1 && !ll_kind) { c->last_error = "flagged-line execution covers allreduce, reduce-scatter, allgather and all-to-all"; return CHB_ERR_UNSUPPORTED; }
   // In place means in == out, except for the allgather, whose in-place form is
   // "my block already sits at its slot of the output" (in == out + rank * block):
   // that needs no staging, the self copy is a no-op.

@@ -35,7 +35,7 @@
 // Flags are launch sequence numbers shared with the one-shot kernels (ll.cu);
 // the two inbox halves alternate by launch parity.  That is sound for
 // collectives in which every rank's result depends on every rank's input
-// (allreduce, reduce-scatter, allgather): a rank can finish launch n only after
+// (allreduce, reduce-scatter, allgather, all-to-all): a rank can finish launch n only after
 // every peer has entered launch n, so nobody is ever two launches ahead.
 #include <algorithm>
 #include <cstring>

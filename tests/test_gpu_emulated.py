@@ -140,11 +140,13 @@ def test_all_to_all_and_gather(comms):
     comm = comms(P)
     n = 100
     ins = make_inputs(P, n * P, torch.float32)
+    # every schedule in both execution modes, and as the library chooses (flagged lines at this size)
     for algo, k, b in (("tuna", 2, 1), ("tuna", 3, 2), ("linear", 2, 1)):
-        outs = chb.all_to_all(comm, ins, algo=algo, k=k, b=b)
-        for r in range(P):
-            exp = torch.cat([ins[s][r * n:(r + 1) * n] for s in range(P)])
-            assert torch.equal(outs[r], exp)
+        for mode in ("", ":pull", ":ll"):
+            outs = chb.all_to_all(comm, ins, algo=algo + mode, k=k, b=b)
+            for r in range(P):
+                exp = torch.cat([ins[s][r * n:(r + 1) * n] for s in range(P)])
+                assert torch.equal(outs[r], exp), (algo, mode, r)
     blocks = [x[:n].contiguous() for x in ins]
     outs = chb.gather(comm, blocks, root=5, k=3)
     assert torch.equal(outs[5], torch.cat(blocks))

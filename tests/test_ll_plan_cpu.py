@@ -64,6 +64,8 @@ def _pattern(P, n, dt, seed=5):
 def _expected(coll, ins, P, n):
     if coll == "allgather":
         return [np.concatenate(ins)] * P
+    if coll == "alltoall":
+        return [np.concatenate([ins[s][r * n:(r + 1) * n] for s in range(P)]) for r in range(P)]
     tot = ins[0].copy()
     for x in ins[1:]:
         tot = tot + x
@@ -93,7 +95,7 @@ def test_radix_batch_push_form_on_the_host(coll, P):
                 _check(coll, "radix_batch", P, n, k, b)
 
 
-@pytest.mark.parametrize("coll", ["allreduce", "reduce_scatter", "allgather"])
+@pytest.mark.parametrize("coll", ["allreduce", "reduce_scatter", "allgather", "alltoall"])
 def test_every_algorithm_push_form_on_the_host(coll):
     ran = 0
     for algo in list_algorithms(coll):
@@ -106,7 +108,7 @@ def test_every_algorithm_push_form_on_the_host(coll):
                     ran += 1
                 except ProgramError:
                     pass     # shape not defined for this algorithm (e.g. a power-of-two baseline at P = 5)
-    assert ran > 10
+    assert ran > (10 if coll != "alltoall" else 3)
 
 
 @pytest.mark.parametrize("dt", [np.uint8, np.int64, np.float64, np.float32])

@@ -55,3 +55,45 @@ def test_random_shapes(case):
         outs, _ = p.run_threads(ins, op=op)
         for r in range(P):
             np.testing.assert_array_equal(outs[r], exp[r], err_msg=f"{case} rank {r} (threads)")
+
+
+@st.composite
+def push_cases(draw):
+    coll = draw(st.sampled_from(COLLS + ["alltoall"]))
+    algo = draw(st.sampled_from(list_algorithms(coll)))
+    P = draw(st.integers(2, 16))
+    b = draw(st.sampled_from([d for d in range(1, P + 1) if P % d == 0]))
+    k = draw(st.integers(2, 9))
+    n = draw(st.integers(1, 9))
+    dt = draw(st.sampled_from([np.uint8, np.int32, np.int64]))
+    threads = draw(st.sampled_from([1, 2, 3, 7, 32]))
+    seed = draw(st.integers(0, 2 ** 31))
+    in_place = draw(st.booleans()) and coll in ("allreduce",)
+    return coll, algo, P, k, b, n, dt, threads, seed, in_place
+
+
+@settings(max_examples=300, deadline=None, suppress_health_check=list(HealthCheck))
+@given(push_cases())
+def test_random_shapes_push_form(case):
+    """The flagged-line (push) form of the same programs, executed line by line on the host under random thread
+    interleavings: inbox slots, forwards, partial last lines (1-, 4- and 8-byte elements) and the barriers that
+    the plan kept must give the definition of the collective."""
+    coll, algo, P, k, b, n, dt, threads, seed, in_place = case
+    count = n * P if coll == "allreduce" else n
+    aux = b if algo == "inter_reduce_exchange_bcast" else 0
+    try:
+        p = Program(coll, algo, P, count, k=k, b=b, aux=aux, in_symmetric=True, out_symmetric=True, in_place=in_place)
+    except ProgramError:
+        return
+    rng = np.random.default_rng(seed)
+    ins = [rng.integers(0, 30, p.in_elems).astype(dt) for _ in range(P)]
+    outs = p.simulate_ll(ins, seed=seed, threads=threads)
+    if coll == "allgather":
+        exp = [np.concatenate(ins)] * P
+    elif coll == "alltoall":
+        exp = [np.concatenate([ins[s][r * n:(r + 1) * n] for s in range(P)]) for r in range(P)]
+    else:
+        red = np.stack(ins).sum(axis=0, dtype=dt)
+        exp = [red] * P if coll == "allreduce" else [red[r * n:(r + 1) * n] for r in range(P)]
+    for r in range(P):
+        np.testing.assert_array_equal(outs[r], exp[r], err_msg=f"{case} rank {r}")

@@ -66,6 +66,7 @@ def test_two_level_on_gpus():
     P = torch.cuda.device_count() if torch.cuda.is_available() else 0
     if P < 2:
         pytest.skip("needs at least two GPUs")
+    P = min(P, int(os.environ.get("CHB_TEST_MAX_GPUS", "4")))
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()

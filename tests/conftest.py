@@ -27,3 +27,15 @@ def cuda():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+def gpus_for_test(at_most: int = 4) -> int:
+    """Ranks (one per GPU) a multi-GPU test world uses: the visible GPUs, at most ``at_most``, and at most
+    CHB_TEST_MAX_GPUS (default 2: every multi-GPU test spawns its own world of processes, and the suite on two
+    ranks is the quick everyday check; export 4 or 8 to widen it).  0 without CUDA."""
+    import os
+
+    import torch
+
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    return min(n, at_most, int(os.environ.get("CHB_TEST_MAX_GPUS", "2")))

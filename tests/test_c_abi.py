@@ -66,7 +66,8 @@ def test_native_ranks_example_compiles(tmp_path):
 @pytest.mark.multigpu
 def test_native_ranks_example_runs(tmp_path):
     import torch
-    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    from conftest import gpus_for_test
+    n = gpus_for_test(4)
     if n < 2:
         pytest.skip("needs at least two GPUs")
     exe = _build_ranks_example(tmp_path)

@@ -192,10 +192,9 @@ def _launch(P, backend):
 
 
 def _ngpus():
-    """GPUs a test world uses: all of them up to CHB_TEST_MAX_GPUS (default 4, like the other multi-GPU tests: one
-    rank per GPU is spawned per test, and eight-rank worlds make the suite several times longer for no new path)."""
-    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
-    return min(n, int(os.environ.get("CHB_TEST_MAX_GPUS", "4")))
+    """GPUs a test world uses: see conftest.gpus_for_test (CHB_TEST_MAX_GPUS widens it up to all eight)."""
+    from conftest import gpus_for_test
+    return gpus_for_test(8)
 
 
 @pytest.mark.timeout(900)

@@ -27,7 +27,8 @@ def _free_port():
 @pytest.mark.parametrize("coll,algos", [("allgather", "radix_batch,bulk,ll,nvls"), ("allreduce", "radix_batch,ll,ll2,nvls,ring"),
                                         ("reduce_scatter", "radix_batch,ll,nvls,pairwise")])
 def test_driver_on_symmetric_buffers(tmp_path, coll, algos):
-    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    from conftest import gpus_for_test
+    n = gpus_for_test(4)
     if n < 2:
         pytest.skip("needs at least two GPUs")
     n = 2 if n < 4 else 4
@@ -49,7 +50,8 @@ def test_driver_on_symmetric_buffers(tmp_path, coll, algos):
 @pytest.mark.timeout(600)
 def test_driver_two_levels_on_gpus(tmp_path):
     """Boxes of L GPUs (L = 1 with two GPUs, 2 with four): kernels inside a box, NCCL or a ring program along the lanes."""
-    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    from conftest import gpus_for_test
+    n = gpus_for_test(4)
     if n < 2:
         pytest.skip("needs at least two GPUs")
     n = 2 if n < 4 else 4

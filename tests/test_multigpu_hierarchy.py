@@ -63,10 +63,10 @@ def _worker(rank, P, port, q):
 
 @pytest.mark.timeout(600)
 def test_two_level_on_gpus():
-    P = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    from conftest import gpus_for_test
+    P = gpus_for_test(8)
     if P < 2:
         pytest.skip("needs at least two GPUs")
-    P = min(P, int(os.environ.get("CHB_TEST_MAX_GPUS", "4")))
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
@@ -124,10 +124,10 @@ def _native_worker(rank, P, name, q):
 @pytest.mark.timeout(600)
 def test_communicator_over_the_native_bootstrap():
     """One rank per GPU, rendezvous through POSIX shared memory: no process group is ever created."""
-    P = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    from conftest import gpus_for_test
+    P = gpus_for_test(4)
     if P < 2:
         pytest.skip("needs at least two GPUs")
-    P = min(P, 4)
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     name = f"/chb_test_{os.getpid()}"

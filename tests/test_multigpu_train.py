@@ -37,7 +37,8 @@ def _worker(rank, P, port, mode, q):
 @pytest.mark.timeout(900)
 @pytest.mark.parametrize("mode", ["dp", "zero"])
 def test_training_step_matches_nccl(mode):
-    P = min(torch.cuda.device_count() if torch.cuda.is_available() else 0, 4)
+    from conftest import gpus_for_test
+    P = gpus_for_test(4)
     if P < 2:
         pytest.skip("needs at least two GPUs")
     ctx = mp.get_context("spawn")

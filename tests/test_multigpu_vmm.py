@@ -76,10 +76,10 @@ def _worker(rank, P, name, q):
 
 @pytest.mark.timeout(600)
 def test_native_virtual_memory_heaps_and_multicast():
-    P = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    from conftest import gpus_for_test
+    P = gpus_for_test(4)
     if P < 2:
         pytest.skip("needs at least two GPUs")
-    P = min(P, 4)
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     name = f"/chb_vmm_{os.getpid()}"

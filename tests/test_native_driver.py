@@ -53,7 +53,8 @@ def test_emulated_world(exe, tmp_path, cuda, coll, dtype, op):
 @pytest.mark.multigpu
 @pytest.mark.parametrize("coll", ["allreduce", "reduce_scatter", "allgather"])
 def test_forked_ranks_one_per_gpu(exe, tmp_path, coll):
-    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    from conftest import gpus_for_test
+    n = gpus_for_test(4)
     if n < 2:
         pytest.skip("needs at least two GPUs")
     n = 2 if n < 4 else 4

@@ -44,7 +44,13 @@ enum { CHB_ALLREDUCE = 0, CHB_REDUCE_SCATTER = 1, CHB_ALLGATHER = 2, CHB_ALLTOAL
 
 void chb_set_stream(cudaStream_t s);
 
-/* generic: one pointer per local rank, any algorithm name, fused scale */
+/* generic: one pointer per local rank, any algorithm name, fused scale.
+ * algo: a schedule name ("radix_batch", "ring", "recursive_doubling", ...; chb_list_algorithms), optionally
+ * followed by ":ll" (owners push flagged lines: one NVLink traversal per round, rounds overlap line by line) or
+ * ":pull" (readers pull: the persistent interpreter with its tile scheduler); without a suffix allreduce,
+ * reduce-scatter, allgather and all-to-all run as push programs up to CHB_LL_PROGRAM_MAX bytes (environment,
+ * default 4 MiB) when their messages fit the inbox and as pull programs above.  The kernel-level names "ll",
+ * "ll2", "nvls", "nvls1" and "bulk" select the hand-written kernels. */
 int chb_collective(CHB_Comm c, int coll, const char* algo, int k, int b, int aux, int dtype, int op,
                    const void* const* in, void* const* out, int64_t count, float scale, int nctas,
                    cudaStream_t stream);

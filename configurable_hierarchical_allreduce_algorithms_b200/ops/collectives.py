@@ -51,6 +51,23 @@ def _ll_ok(comm, ins, outs, payload_bytes):
     return all((t.data_ptr() % 8) == 0 for t in ins + outs)
 
 
+# kernels and programs that take an allreduce of any length; every other schedule cuts the vector into P slices
+_ANY_COUNT = ("ll", "ll2", "nvls", "nvls1", "recursive_doubling", "ring", "k_reduce_scatter_allgather",
+              "recursive_multiplying", "recursive_exchange", "inter_reduce_exchange_bcast")
+
+
+def any_count(coll: str, algo: str, k: int, b: int, count: int, P: int, ll_ok: bool, payload_bytes: int = 0):
+    """The tuned table and the fallback rule are made from vectors whose length is a multiple of the number of
+    ranks.  An allreduce of any other length keeps the choice only if that kernel takes any length; otherwise it
+    runs on the one-shot line kernel while the message fits its inbox, as recursive doubling (whole-vector
+    exchanges, few rounds) up to 1 MiB and as the ring (bandwidth-optimal, ragged chunks) above."""
+    if coll != "allreduce" or P <= 1 or count % P == 0 or algo.split(":")[0] in _ANY_COUNT:
+        return algo, k, b
+    if ll_ok:
+        return "ll", 2, 1
+    return ("recursive_doubling", 2, 1) if payload_bytes <= (1 << 20) else ("ring", 2, 1)
+
+
 _COLL = {"allreduce": 0, "reduce_scatter": 1, "allgather": 2, "alltoall": 3, "gather": 4, "phase": 5}
 _ALGO_BYTES: dict = {}
 _NVTX = __import__("os").environ.get("CHB_NVTX", "0") == "1"   # NVTX range around every launch
@@ -77,6 +94,7 @@ def _run(comm: Communicator, coll: str, ins, outs, count: int, op, algo, k, b, a
         elif algo.startswith("nvls") and not (comm.has_multicast and sym and comm.nlocal == 1
                                               and payload_bytes % 16 == 0):
             algo, k, b = "radix_batch", 2, 1
+        algo, k, b = any_count(coll, algo, k, b, count, comm.P, _ll_ok(comm, ins, outs, payload_bytes), payload_bytes)
     if algo == "bulk" and not (coll == "allgather" and payload_bytes % 16 == 0 and comm.is_symmetric(ins[0])
                                and all(t.data_ptr() % 16 == 0 for t in ins + outs)):
         algo, k, b = "radix_batch", 2, 1      # the bulk-copy engine needs 16-byte granularity and a peer-visible input

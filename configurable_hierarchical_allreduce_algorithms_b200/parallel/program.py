@@ -154,13 +154,13 @@ class Program:
             assert x.size == self.in_elems, (x.size, self.in_elems)
         if alias:
             assert self.in_place, "aliased buffers need a program lowered with in_place=True"
-            bufs = [np.full(max(self.in_elems, self.out_elems), -17, dtype=dt) for _ in range(self.P)]
+            bufs = [np.full(max(self.in_elems, self.out_elems), 239 if np.dtype(dt).kind == "u" else -17, dtype=dt) for _ in range(self.P)]
             for b_, x in zip(bufs, ins):
                 b_[:x.size] = x
             ins, outs = bufs, bufs
         else:
             # outputs start poisoned so that positions the program never writes stand out
-            outs = [np.full(self.out_elems, -17, dtype=dt) for _ in range(self.P)]
+            outs = [np.full(self.out_elems, 239 if np.dtype(dt).kind == "u" else -17, dtype=dt) for _ in range(self.P)]
         ip = (C.c_void_p * self.P)(*[x.ctypes.data for x in ins])
         opp = (C.c_void_p * self.P)(*[x.ctypes.data for x in outs])
         err = C.create_string_buffer(512)

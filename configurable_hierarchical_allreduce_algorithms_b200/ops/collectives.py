@@ -94,7 +94,8 @@ def _run(comm: Communicator, coll: str, ins, outs, count: int, op, algo, k, b, a
         elif algo.startswith("nvls") and not (comm.has_multicast and sym and comm.nlocal == 1
                                               and payload_bytes % 16 == 0):
             algo, k, b = "radix_batch", 2, 1
-        algo, k, b = any_count(coll, algo, k, b, count, comm.P, _ll_ok(comm, ins, outs, payload_bytes), payload_bytes)
+        if coll == "allreduce" and count % comm.P:
+            algo, k, b = any_count(coll, algo, k, b, count, comm.P, _ll_ok(comm, ins, outs, payload_bytes), payload_bytes)
     if algo == "bulk" and not (coll == "allgather" and payload_bytes % 16 == 0 and comm.is_symmetric(ins[0])
                                and all(t.data_ptr() % 16 == 0 for t in ins + outs)):
         algo, k, b = "radix_batch", 2, 1      # the bulk-copy engine needs 16-byte granularity and a peer-visible input

@@ -56,7 +56,7 @@ def _declare(L: C.CDLL) -> None:
     L.chb_program_ll_info.restype = i32
     L.chb_program_ll_info.argtypes = [vp, i32, C.POINTER(C.c_longlong), i32]
     L.chb_program_simulate_ll.restype = i32
-    L.chb_program_simulate_ll.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(vp), u64, i32, i32, cp, i32]
+    L.chb_program_simulate_ll.argtypes = [vp, i32, i32, C.POINTER(vp), C.POINTER(vp), u64, i32, i32, i32, cp, i32]
     L.chb_program_export.restype = i32
     L.chb_program_export.argtypes = [vp, vp, vp, vp, vp, vp]
     L.chb_list_algorithms.restype = i32

@@ -70,11 +70,13 @@ int chb_program_simulate(const chb_program_t* p, int dtype, int op, void* const*
  * chb_program_simulate_ll: run that form on host buffers, line by line, nthreads virtual threads per rank
  *   advanced in a random order (seed); a message that nobody sends ends as CHB_ERR_TIMEOUT with the waiting
  *   rank and peer in err.  fault: 0, or a defect injected into the plan to test the simulator itself
- *   (1 = its barriers are ignored, 2 = the last forward of every step is left out). */
+ *   (1 = its barriers are ignored, 2 = the last forward of every step is left out).  launches: how often the
+ *   program runs back to back, each rank going on as soon as its own previous launch has returned (the inbox
+ *   halves alternate; a line overwritten before it was read ends the run with CHB_ERR_TIMEOUT). */
 long long chb_program_ll_lines(const chb_program_t* p, int esz);
 int chb_program_ll_info(const chb_program_t* p, int esz, long long* info, int n);
 int chb_program_simulate_ll(const chb_program_t* p, int dtype, int op, void* const* in, void* const* out,
-                            uint64_t seed, int nthreads, int fault, char* err, int errlen);
+                            uint64_t seed, int nthreads, int fault, int launches, char* err, int errlen);
 /* run all ranks as host threads (real concurrency); mean wall seconds per repetition in *seconds */
 int chb_program_run_threads(const chb_program_t* p, int dtype, int op, void* const* in, void* const* out,
                             int iters, double* seconds);

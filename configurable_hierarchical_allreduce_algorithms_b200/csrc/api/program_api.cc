@@ -136,10 +136,10 @@ int chb_program_ll_info(const chb_program_t* p, int esz, long long* info, int n)
 }
 
 int chb_program_simulate_ll(const chb_program_t* p, int dtype, int op, void* const* in, void* const* out,
-                            uint64_t seed, int nthreads, int fault, char* err, int errlen) {
+                            uint64_t seed, int nthreads, int fault, int launches, char* err, int errlen) {
   if (!p || !in || !out || fault < 0 || fault > 2) return CHB_ERR_ARG;
   std::string e;
-  int rc = chb::simulate_ll(p->prog, dtype, op, in, out, seed, nthreads, fault, &e);
+  int rc = chb::simulate_ll(p->prog, dtype, op, in, out, seed, nthreads, fault, launches, &e);
   if (rc) { set_err(err, errlen, e); return rc == -1 ? CHB_ERR_TIMEOUT : CHB_ERR_ARG; }
   return CHB_SUCCESS;
 }

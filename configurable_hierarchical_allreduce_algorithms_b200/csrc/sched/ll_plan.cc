@@ -247,7 +247,7 @@ void store_line(char* base, long long off, long long nbytes, const Line& v) {
 
 template <typename T>
 int simulate_ll_t(const Program& p, int rop, void* const* in, void* const* out, uint64_t seed, int TT,
-                  int fault, std::string* err) {
+                  int fault, int launches, std::string* err) {
   constexpr int PE = (int)(8 / sizeof(T));
   LPHeader h{};
   const std::vector<char> blob = make_ll_blob(p, (int)sizeof(T), &h);
@@ -258,13 +258,19 @@ int simulate_ll_t(const Program& p, int rop, void* const* in, void* const* out, 
   const LPSend* sends = reinterpret_cast<const LPSend*>(blob.data() + h.off_sends);
   const LPFwd* fwds = reinterpret_cast<const LPFwd*>(blob.data() + h.off_fwds);
   std::vector<std::vector<T>> work(P);
+  // Inbox: two halves that alternate by launch parity, like on the GPU.  tag = number of the launch that wrote the
+  // line, plus one (the flag a reader of that launch waits for); a line is overwritten without asking, so a sender
+  // that is two launches ahead of a reader destroys a line that was never read, which `unread` catches.
+  const size_t NLN = (size_t)h.inbox_lines;
   std::vector<std::vector<Line>> inbox(P);
-  std::vector<std::vector<unsigned char>> here(P);       // the flag of an inbox line
+  std::vector<std::vector<int>> tag(P);
+  std::vector<std::vector<unsigned char>> unread(P);
   for (int r = 0; r < P; ++r) {
     work[r].resize((size_t)p.work_elems);
     if (!work[r].empty()) std::memset(work[r].data(), 0xFF, work[r].size() * sizeof(T));
-    inbox[r].assign((size_t)h.inbox_lines, Line{});
-    here[r].assign((size_t)h.inbox_lines, 0);
+    inbox[r].assign(2 * NLN, Line{});
+    tag[r].assign(2 * NLN, 0);
+    unread[r].assign(2 * NLN, 0);
   }
   auto base = [&](int rank, int buf) -> char* {
     switch (buf) {
@@ -273,24 +279,40 @@ int simulate_ll_t(const Program& p, int rop, void* const* in, void* const* out, 
       default: return (char*)work[rank].data();
     }
   };
-  auto deliver = [&](int dst, long long line, const Line& v) -> bool {
-    if (dst < 0 || dst >= P || line < 0 || line >= h.inbox_lines || here[dst][(size_t)line]) return false;
-    inbox[dst][(size_t)line] = v;
-    here[dst][(size_t)line] = 1;
+  auto deliver = [&](int dst, long long line, const Line& v, int launch) -> bool {
+    if (dst < 0 || dst >= P || line < 0 || line >= h.inbox_lines) return false;
+    const size_t at = (size_t)(launch & 1) * NLN + (size_t)line;
+    if (unread[dst][at]) return false;            // written twice in one launch, or overwritten before it was read
+    inbox[dst][at] = v;
+    tag[dst][at] = launch + 1;
+    unread[dst][at] = 1;
     return true;
   };
   // one virtual thread: where it is in its rank's levels
-  struct Thr { int rank, v, level = 0, phase = 0; long long gl = 0; int passed = 0; bool arrived = false, done = false; };
+  struct Thr { int rank, v, level = 0, phase = 0, launch = 0; long long gl = 0; int passed = 0; bool arrived = false, done = false, at_end = false; };
   std::vector<Thr> th;
   for (int r = 0; r < P; ++r)
     for (int v = 0; v < TT; ++v) { Thr t; t.rank = r; t.v = v; t.gl = v; th.push_back(t); }
-  std::vector<long long> arrivals(P, 0);
+  std::vector<long long> arrivals(P, 0), finished(P, 0);
   std::string why;
   // advance thread t by one unit (a barrier, or one line); 1 progressed, 0 blocked, -1 error
   auto advance = [&](Thr& t) -> int {
     const int r = t.rank;
     while (true) {
-      if (t.level >= NL) { t.done = true; return 1; }
+      if (t.level >= NL) {
+        // end of a launch: the next kernel of this rank starts when every thread of this one has returned
+        if (!t.at_end) { t.at_end = true; ++finished[r]; }
+        if (t.launch + 1 >= launches) { t.done = true; return 1; }
+        if (finished[r] < (long long)TT * (t.launch + 1)) {
+          why = "rank " + std::to_string(r) + " waits for the end of its launch " + std::to_string(t.launch);
+          return 0;
+        }
+        t.at_end = false;
+        ++t.launch;
+        t.level = 0;
+        t.phase = 0;
+        return 1;
+      }
       const LPLevel& L = levels[(size_t)r * NL + t.level];
       if (t.phase == 0) {
         const bool barrier = L.barrier_before && fault != LL_FAULT_NO_BARRIERS;
@@ -312,7 +334,10 @@ int simulate_ll_t(const Program& p, int rop, void* const* in, void* const* out, 
         const LPSend& S = sends[find_item(sends, L.send_begin, L.send_end, t.gl)];
         const long long l = t.gl - S.line_prefix;
         const Line v = load_line(base(r, S.src_buf) + S.src_off * (long long)sizeof(T), l * 8, S.count * (long long)sizeof(T));
-        if (!deliver(S.dst_rank, S.inbox_line + l, v)) { why = "a pushed line has no free slot in the inbox of rank " + std::to_string(S.dst_rank); return -1; }
+        if (!deliver(S.dst_rank, S.inbox_line + l, v, t.launch)) {
+          why = "a line pushed by rank " + std::to_string(r) + " in launch " + std::to_string(t.launch) + " meets an unread line in the inbox of rank " + std::to_string(S.dst_rank);
+          return -1;
+        }
         t.gl += TT;
         return 1;
       }
@@ -322,7 +347,7 @@ int simulate_ll_t(const Program& p, int rop, void* const* in, void* const* out, 
       const long long nbytes = st.count * (long long)sizeof(T);
       for (int j = 0; j < st.nsrc; ++j) {
         const LPSrc& sc = srcs[(size_t)st.src_begin + j];
-        if (sc.inbox_line >= 0 && !here[r][(size_t)(sc.inbox_line + l)]) {
+        if (sc.inbox_line >= 0 && tag[r][(size_t)(t.launch & 1) * NLN + (size_t)(sc.inbox_line + l)] != t.launch + 1) {
           why = "rank " + std::to_string(r) + " level " + std::to_string(t.level) + " waits for line " + std::to_string(l) +
                 " from rank " + std::to_string(sc.peer);
           return 0;
@@ -342,8 +367,13 @@ int simulate_ll_t(const Program& p, int rop, void* const* in, void* const* out, 
       if (acc) take(load_line(dst, l * 8, nbytes));
       for (int j = 0; j < st.nsrc; ++j) {
         const LPSrc& sc = srcs[(size_t)st.src_begin + j];
-        v = sc.inbox_line >= 0 ? inbox[r][(size_t)(sc.inbox_line + l)]
-                               : load_line(base(r, sc.buf) + sc.off * (long long)sizeof(T), l * 8, nbytes);
+        if (sc.inbox_line >= 0) {
+          const size_t at = (size_t)(t.launch & 1) * NLN + (size_t)(sc.inbox_line + l);
+          v = inbox[r][at];
+          unread[r][at] = 0;
+        } else {
+          v = load_line(base(r, sc.buf) + sc.off * (long long)sizeof(T), l * 8, nbytes);
+        }
         take(v);
       }
       if (acc || st.nsrc > 1) std::memcpy(v.b, a, 8);
@@ -352,8 +382,8 @@ int simulate_ll_t(const Program& p, int rop, void* const* in, void* const* out, 
       for (int f = 0; f < nfwd; ++f) {
         const LPFwd& F = fwds[(size_t)st.fwd_begin + f];
         const long long lf = l - F.line_begin;
-        if (lf >= 0 && lf < F.nlines && !deliver(F.dst_rank, F.inbox_line + lf, v)) {
-          why = "a forwarded line has no free slot in the inbox of rank " + std::to_string(F.dst_rank);
+        if (lf >= 0 && lf < F.nlines && !deliver(F.dst_rank, F.inbox_line + lf, v, t.launch)) {
+          why = "a line forwarded by rank " + std::to_string(r) + " in launch " + std::to_string(t.launch) + " meets an unread line in the inbox of rank " + std::to_string(F.dst_rank);
           return -1;
         }
       }
@@ -390,18 +420,19 @@ int simulate_ll_t(const Program& p, int rop, void* const* in, void* const* out, 
 }  // namespace
 
 int simulate_ll(const Program& p, int dtype, int op, void* const* in, void* const* out, uint64_t seed,
-                int nthreads, int fault, std::string* err) {
+                int nthreads, int fault, int launches, std::string* err) {
+  if (launches < 1 || launches > 64) { if (err) *err = "simulate_ll: 1 to 64 launches"; return -2; }
   if (nthreads < 1 || nthreads > 4096) { if (err) *err = "simulate_ll: 1 to 4096 threads per rank"; return -2; }
   if ((p.reads_peer_in && !p.in_symmetric) || (p.reads_peer_out && !p.out_symmetric)) {
     if (err) *err = "simulate_ll: the push form wants a program lowered without staging copies";
     return -2;
   }
   switch (dtype) {
-    case DT_F32: return simulate_ll_t<float>(p, op, in, out, seed, nthreads, fault, err);
-    case DT_F64: return simulate_ll_t<double>(p, op, in, out, seed, nthreads, fault, err);
-    case DT_I32: return simulate_ll_t<int32_t>(p, op, in, out, seed, nthreads, fault, err);
-    case DT_I64: return simulate_ll_t<int64_t>(p, op, in, out, seed, nthreads, fault, err);
-    case DT_U8: return simulate_ll_t<uint8_t>(p, op, in, out, seed, nthreads, fault, err);
+    case DT_F32: return simulate_ll_t<float>(p, op, in, out, seed, nthreads, fault, launches, err);
+    case DT_F64: return simulate_ll_t<double>(p, op, in, out, seed, nthreads, fault, launches, err);
+    case DT_I32: return simulate_ll_t<int32_t>(p, op, in, out, seed, nthreads, fault, launches, err);
+    case DT_I64: return simulate_ll_t<int64_t>(p, op, in, out, seed, nthreads, fault, launches, err);
+    case DT_U8: return simulate_ll_t<uint8_t>(p, op, in, out, seed, nthreads, fault, launches, err);
   }
   if (err) *err = "simulate_ll: unsupported dtype on the host";
   return -2;

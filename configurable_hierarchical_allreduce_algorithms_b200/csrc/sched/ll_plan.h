@@ -56,7 +56,12 @@ long long ll_inbox_lines(const Program& p, int esz);
 // fault (for the tests of this simulator itself: does it notice a broken plan?): LL_FAULT_NO_BARRIERS ignores the
 // plan's barriers, LL_FAULT_DROP_A_FORWARD leaves out the last forward of every step.
 enum { LL_FAULT_NONE = 0, LL_FAULT_NO_BARRIERS = 1, LL_FAULT_DROP_A_FORWARD = 2 };
+// launches > 1 runs the program that many times back to back on the same buffers: every rank starts its next
+// launch as soon as its own previous one has returned (stream order), nothing else holds a rank back, and the
+// inbox halves alternate by launch parity as on the GPU.  A sender that gets two launches ahead of a reader then
+// overwrites a line that was never read, which ends the run with -1: that is the case the executor excludes by
+// accepting only collectives in which every rank's result depends on every rank's input.
 int simulate_ll(const Program& p, int dtype, int op, void* const* in, void* const* out, uint64_t seed,
-                int nthreads, int fault, std::string* err);
+                int nthreads, int fault, int launches, std::string* err);
 
 }  // namespace chb

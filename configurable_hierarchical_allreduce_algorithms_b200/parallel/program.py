@@ -170,12 +170,14 @@ class Program:
         return [o[:self.out_elems] for o in outs]
 
     def simulate_ll(self, inputs: list[np.ndarray], op: str = "sum", seed: int = 0, threads: int = 5,
-                    fault: int = 0) -> list[np.ndarray]:
+                    fault: int = 0, launches: int = 1) -> list[np.ndarray]:
         """Run the push (flagged-line) form of this program on host arrays, line by line, the way the GPU executor
         does: ``threads`` virtual threads per rank, advanced in a random order drawn from ``seed``; only the plan's
         own messages, forwards and barriers order them.  The program must have been lowered with
         ``in_symmetric=True, out_symmetric=True`` (the push form has no staging copies).  ``fault`` injects a defect
-        into the plan to test the simulator itself: 1 ignores the plan's barriers, 2 drops one forward per step."""
+        into the plan to test the simulator itself: 1 ignores the plan's barriers, 2 drops one forward per step.
+        ``launches`` runs the program that often back to back, every rank going on as soon as its own previous launch
+        has returned; a rank that gets two launches ahead of a reader of its lines is reported."""
         assert len(inputs) == self.P
         dt = inputs[0].dtype
         code = _DT_FROM_NP[np.dtype(dt)]
@@ -187,7 +189,7 @@ class Program:
         ip = (C.c_void_p * self.P)(*[x.ctypes.data for x in ins])
         opp = (C.c_void_p * self.P)(*[x.ctypes.data for x in outs])
         err = C.create_string_buffer(512)
-        rc = N.lib().chb_program_simulate_ll(self._h, code, _OPS[op], ip, opp, seed, threads, fault, err, len(err))
+        rc = N.lib().chb_program_simulate_ll(self._h, code, _OPS[op], ip, opp, seed, threads, fault, launches, err, len(err))
         if rc:
             raise RuntimeError(f"simulate_ll({self.name}) failed: {err.value.decode()}")
         return outs

@@ -166,3 +166,38 @@ def test_the_simulator_notices_a_message_that_nobody_sends():
     prog = _prog("allreduce", "radix_batch", P, n * P, 2, 1)
     with pytest.raises(RuntimeError, match=r"deadlock: rank \d+ level \d+ waits for line \d+ from rank \d+"):
         prog.simulate_ll(_pattern(P, prog.in_elems, np.int32), fault=2)
+
+
+@pytest.mark.parametrize("coll", ["allreduce", "reduce_scatter", "allgather", "alltoall"])
+def test_back_to_back_launches_share_two_inbox_halves(coll):
+    """Five launches in a row, every rank going on as soon as its own previous launch has returned and the inbox
+    halves alternating by launch parity: in these collectives nobody can get two launches ahead of a rank that
+    still has to read a line, so no line is ever overwritten unread."""
+    for algo in list_algorithms(coll):
+        for P, k, b in ((2, 2, 1), (4, 2, 2), (8, 2, 1), (8, 8, 8)):
+            try:
+                prog = _prog(coll, algo, P, 5 * P if coll == "allreduce" else 5, k, b)
+            except ProgramError:
+                continue
+            ins = _pattern(P, prog.in_elems, np.int32)
+            exp = _expected(coll, ins, P, 5)
+            for seed in (0, 1, 2):
+                outs = prog.simulate_ll(ins, seed=seed, threads=3, launches=5)
+                for r in range(P):
+                    np.testing.assert_array_equal(outs[r], exp[r])
+
+
+def test_a_gather_would_overwrite_unread_lines():
+    """Why the executor refuses collectives such as gather: a leaf only sends, so it runs launches ahead of its
+    parent, and its third launch writes into the half that still holds the unread line of its first."""
+    prog = _prog("gather", "k_nomial", 8, 6, 2, 1)
+    ins = _pattern(8, prog.in_elems, np.int32)
+    prog.simulate_ll(ins, seed=0, threads=2, launches=1)       # one launch alone is fine
+    hazards = 0
+    for seed in range(10):
+        try:
+            prog.simulate_ll(ins, seed=seed, threads=2, launches=6)
+        except RuntimeError as e:
+            assert "meets an unread line" in str(e)
+            hazards += 1
+    assert hazards > 0

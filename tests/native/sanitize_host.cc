@@ -14,6 +14,7 @@
 #include <vector>
 
 #include "sched/algos.h"
+#include "sched/ll_plan.h"
 #include "sched/program.h"
 #include "sched/types.h"
 
@@ -115,6 +116,14 @@ void run_case(const AlgoSpec& s, bool threads_only) {
         if (simulate(p, DT_I32, OP_SUM, ip.data(), op.data(), seed * 7919u + variant, &err) != 0) fail("simulate", s, err);
         else check("simulate");
       }
+    }
+    // the push form of the same program (plan tables + line-by-line execution, two launches on the two inbox
+    // halves) for the collectives the executor accepts
+    if (!threads_only && variant == 1 &&
+        (s.coll == "allreduce" || s.coll == "reduce_scatter" || s.coll == "allgather" || s.coll == "alltoall")) {
+      for (auto& v : out) std::fill(v.begin(), v.end(), -1);
+      if (simulate_ll(p, DT_I32, OP_SUM, ip.data(), op.data(), 17u, 3, LL_FAULT_NONE, 2, &err) != 0) fail("simulate_ll", s, err);
+      else check("simulate_ll");
     }
     for (auto& v : out) std::fill(v.begin(), v.end(), -1);
     double sec = 0;

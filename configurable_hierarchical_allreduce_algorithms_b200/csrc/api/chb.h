@@ -66,7 +66,8 @@ int chb_program_simulate(const chb_program_t* p, int dtype, int op, void* const*
  * chb_program_ll_lines: lines the fullest inbox needs for elements of esz bytes (-1: bad argument).
  * chb_program_ll_info: info = rounds, messages pushed in a round's push phase, messages forwarded line by line
  *   from the previous round's steps, rank-local barriers (summed over ranks), lines in the fullest inbox, lines
- *   of the busiest (rank, round).
+ *   of the busiest (rank, round), bytes of the largest rank's own table entries (what a CTA of the executor
+ *   keeps in shared memory when it fits).
  * chb_program_simulate_ll: run that form on host buffers, line by line, nthreads virtual threads per rank
  *   advanced in a random order (seed); a message that nobody sends ends as CHB_ERR_TIMEOUT with the waiting
  *   rank and peer in err.  fault: 0, or a defect injected into the plan to test the simulator itself

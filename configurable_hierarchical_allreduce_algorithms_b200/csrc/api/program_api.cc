@@ -130,8 +130,8 @@ int chb_program_ll_info(const chb_program_t* p, int esz, long long* info, int n)
   long long forwarded = 0;
   const chb::LPStep* st = reinterpret_cast<const chb::LPStep*>(blob.data() + h.off_steps);
   for (int i = 0; i < h.nsteps; ++i) forwarded += st[i].nfwd;
-  const long long v[6] = {h.nlevels, h.nsends, forwarded, barriers, h.inbox_lines, h.max_level_lines};
-  for (int i = 0; i < n && i < 6; ++i) info[i] = v[i];
+  const long long v[7] = {h.nlevels, h.nsends, forwarded, barriers, h.inbox_lines, h.max_level_lines, h.rank_table_bytes};
+  for (int i = 0; i < n && i < 7; ++i) info[i] = v[i];
   return CHB_SUCCESS;
 }
 

@@ -197,13 +197,15 @@ class Program:
     def ll_info(self, elem_bytes: int = 4) -> dict:
         """Shape of the flagged-line (push) form of this program: rounds, messages pushed per round's push phase,
         messages forwarded line by line from the previous round's steps, rank-local barriers (all ranks), lines in
-        the fullest inbox and in the busiest (rank, round)."""
+        the fullest inbox and in the busiest (rank, round), bytes of the largest rank's own table entries (kept in shared
+        memory by the executor up to 40 KiB)."""
         L = N.lib()
-        v = (C.c_longlong * 6)()
-        rc = L.chb_program_ll_info(self._h, elem_bytes, v, 6)
+        v = (C.c_longlong * 7)()
+        rc = L.chb_program_ll_info(self._h, elem_bytes, v, 7)
         if rc:
             raise RuntimeError(f"ll_info failed with code {rc}")
-        return dict(zip(("levels", "pushed", "forwarded", "barriers", "inbox_lines", "busiest_level_lines"), [int(x) for x in v]))
+        return dict(zip(("levels", "pushed", "forwarded", "barriers", "inbox_lines", "busiest_level_lines", "rank_table_bytes"),
+                        [int(x) for x in v]))
 
     def run_threads(self, inputs: list[np.ndarray], op: str = "sum", iters: int = 1,
                     late_rank: int | None = None, delay_ms: int = 20):

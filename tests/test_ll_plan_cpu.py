@@ -201,3 +201,11 @@ def test_a_gather_would_overwrite_unread_lines():
             assert "meets an unread line" in str(e)
             hazards += 1
     assert hazards > 0
+
+
+def test_a_ranks_own_table_entries_are_small():
+    """The executor keeps them in shared memory up to 40 KiB: every schedule of the sweeps is far below that."""
+    for coll, algo, P, k, b in (("allreduce", "radix_batch", 8, 2, 1), ("allreduce", "radix_batch", 8, 2, 4), ("allreduce", "ring", 16, 2, 1),
+                                ("allgather", "radix_batch", 16, 2, 4), ("alltoall", "tuna", 8, 2, 2)):
+        info = _prog(coll, algo, P, P * 64 if coll == "allreduce" else 64, k, b).ll_info(4)
+        assert 0 < info["rank_table_bytes"] < (8 << 10), (coll, algo, P, info)

@@ -40,16 +40,39 @@ def _md_table(path: str, header: list[str], rows: list[list]) -> str:
 
 
 VENDOR_NAMES = {"MPICH_allreduce", "allgather_standard", "reduce_scatter_standard"}
+# The tuner's CSV (bench/tune.py --csv) names its rows <collective>_<kernel or schedule>; the library rows there are
+# NCCL's default choice and NCCL pinned to ring / tree.  FILTER narrows such a file (all collectives, two dtypes)
+# to one collective and dtype before any statistic is taken.
+TUNER_VENDOR_SUFFIXES = ("_nccl", "_nccl_ring", "_nccl_tree")
+FILTER = {"coll": "", "dtype": ""}
+
+
+def is_vendor(name: str) -> bool:
+    return name in VENDOR_NAMES or name.endswith(TUNER_VENDOR_SUFFIXES)
+
+
+def is_vendor_default(name: str) -> bool:
+    """The library's own choice (what the speed-up is taken against), not one of its pinned variants."""
+    return name in VENDOR_NAMES or name.endswith("_nccl")
 
 
 def load(path: str) -> pd.DataFrame:
     df = pd.read_csv(path)
+    if FILTER["coll"]:
+        df = df[df["algorithm_name"].str.startswith(FILTER["coll"] + "_")]
+    if FILTER["dtype"] and "dtype" in df.columns:
+        df = df[df["dtype"] == FILTER["dtype"]]
+    df = df.reset_index(drop=True)
     bad = df[df["is_correct"] != 1]
     if len(bad):
         raise SystemExit(f"{len(bad)} rows of {path} have is_correct != 1; refusing to plot:\n{bad.head()}")
     if "b" not in df.columns:
         df["b"] = 0
-    df["label"] = np.where(df["k"] > 0, df["algorithm_name"] + " (k=" + df["k"].astype(str) + ")", df["algorithm_name"])
+    if "nctas" in df.columns:     # the tuner's file: a candidate is a shape (k, b) at a CTA count
+        df["label"] = np.where(df["k"] > 0, df["algorithm_name"] + " (k=" + df["k"].astype(str) + ", b=" + df["b"].astype(str) +
+                               ", ctas=" + df["nctas"].astype(str) + ")", df["algorithm_name"])
+    else:
+        df["label"] = np.where(df["k"] > 0, df["algorithm_name"] + " (k=" + df["k"].astype(str) + ")", df["algorithm_name"])
     return df
 
 
@@ -63,8 +86,8 @@ def winners_table(df: pd.DataFrame, stat: str = "median") -> pd.DataFrame:
     m = cell_stat(df, stat)
     rows = []
     for (p, n), g in m.groupby(["nprocs", "send_count"]):
-        mine = g[~g["algorithm_name"].isin(VENDOR_NAMES)]
-        vend = g[g["algorithm_name"].isin(VENDOR_NAMES)]
+        mine = g[~g["algorithm_name"].map(is_vendor)]
+        vend = g[g["algorithm_name"].map(is_vendor_default)]
         if not len(mine):
             continue
         best = mine.loc[mine["time"].idxmin()]
@@ -122,7 +145,7 @@ def per_algo(path: str, outdir: str = ".", stat: str = "median") -> list[str]:
         fig, ax = plt.subplots(figsize=(7, 4.5))
         for name, h in g.groupby("algorithm_name"):
             best = h.groupby("send_count")["time"].min()
-            ax.plot(best.index, best.values, marker="o", ms=3, label=name, ls="--" if name in VENDOR_NAMES else "-")
+            ax.plot(best.index, best.values, marker="o", ms=3, label=name, ls="--" if is_vendor(name) else "-")
         ax.set_xscale("log", base=2)
         ax.set_yscale("log")
         ax.set_xlabel("send_count / rank")
@@ -204,7 +227,10 @@ def main(argv=None):
     ap.add_argument("csv")
     ap.add_argument("--outdir", default=".")
     ap.add_argument("--stat", default="median", choices=["median", "mean", "min"])
+    ap.add_argument("--coll", default="", help="keep only rows of this collective (for the tuner's CSV, which holds all three)")
+    ap.add_argument("--dtype", default="", help="keep only rows of this dtype (column dtype, if the file has one)")
     a = ap.parse_args(argv)
+    FILTER.update(coll=a.coll, dtype=a.dtype)
     os.makedirs(a.outdir, exist_ok=True)
     print({"median_best": median_best, "per_algo": per_algo, "radix": radix, "winners": winners}[a.what](a.csv, a.outdir, a.stat))
 

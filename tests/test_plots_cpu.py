@@ -58,3 +58,21 @@ def test_reference_result_files_load_and_rank(tmp_path, rel):
     assert w.winner.str.contains("radix_batch|standard|MPICH|reduce_scatter|allgather|all_reduce").all()
     out = plots.median_best(str(path), str(tmp_path))
     assert Path(out).exists()
+
+
+def test_tuner_samples_through_the_winner_analysis(tmp_path):
+    """The tuner's CSV (all collectives in one file, NCCL rows named <collective>_nccl[_ring|_tree], a CTA count per
+    candidate) goes through the same analysis: one collective at a time, the speed-up against NCCL's default."""
+    from configurable_hierarchical_allreduce_algorithms_b200.bench import plots
+    src = Path(__file__).parent / "data" / "tune_samples_8xB200_fp32.csv"
+    try:
+        plots.main(["median_best", str(src), "--coll", "allreduce", "--outdir", str(tmp_path)])
+    finally:
+        plots.FILTER.update(coll="", dtype="")
+    outs = list(tmp_path.glob("median_best_*"))
+    assert len(outs) == 1
+    if outs[0].suffix == ".md":
+        text = outs[0].read_text()
+        rows = [l for l in text.splitlines() if l.startswith("| 8 |")]
+        assert len(rows) >= 8 and all("allreduce_" in r and "nccl" not in r.split("|")[3] for r in rows)
+        assert all(r.strip().endswith("x |") and "nan" not in r for r in rows)

@@ -168,7 +168,7 @@ def radix(path: str, outdir: str = ".", stat: str = "median") -> str:
         for n in ns:
             g = df[(df["send_count"] == n) & (df["k"] > 0)]
             order = getattr(g.groupby("k")["time"], stat)().sort_values()
-            v = df[(df["send_count"] == n) & df["algorithm_name"].isin(VENDOR_NAMES)]["time"]
+            v = df[(df["send_count"] == n) & df["algorithm_name"].map(is_vendor_default)]["time"]
             rows.append([int(n), int(order.index[0]) if len(order) else "", float(order.iloc[0]) if len(order) else "",
                          int(order.index[1]) if len(order) > 1 else "", int(order.index[-1]) if len(order) > 1 else "",
                          float(getattr(v, stat)()) if len(v) else ""])
@@ -185,7 +185,7 @@ def radix(path: str, outdir: str = ".", stat: str = "median") -> str:
             if len(order) > 1:
                 ax.scatter([order.index[1]], [order.iloc[1]], c="orange", zorder=3, label="second")
                 ax.scatter([order.index[-1]], [order.iloc[-1]], c="r", zorder=3, label="worst")
-        v = df[(df["send_count"] == n) & df["algorithm_name"].isin(VENDOR_NAMES)]["time"]
+        v = df[(df["send_count"] == n) & df["algorithm_name"].map(is_vendor_default)]["time"]
         if len(v):
             ax.axhline(getattr(v, stat)(), ls="--", c="k", lw=0.8)
         ax.set_title(f"send_count {n}", fontsize=8)

@@ -85,11 +85,13 @@ class _FakeLib:
         return 0
 
 
+@pytest.mark.parametrize("multicast", [True, False])
 @pytest.mark.parametrize("P", [2, 4, 8])
-def test_the_sizes_of_the_benchmark_sweep_reach_a_kernel_that_takes_them(P, monkeypatch):
+def test_the_sizes_of_the_benchmark_sweep_reach_a_kernel_that_takes_them(P, multicast, monkeypatch):
     """`bench.py` sweeps allreduce / reduce-scatter / allgather from 8 bytes up with `algo="auto"` on symmetric
     buffers.  With the committed table for P ranks, every call must name a kernel or a program that accepts the
-    length (the first sweep size is two fp32 elements, fewer than the ranks)."""
+    length (the first sweep size is two fp32 elements, fewer than the ranks), with and without a multicast alias (without
+    one the in-switch rows of the table give way to the fallback rule)."""
     from configurable_hierarchical_allreduce_algorithms_b200 import _native as N
     from configurable_hierarchical_allreduce_algorithms_b200.ops import collectives as ops
 
@@ -100,7 +102,7 @@ def test_the_sizes_of_the_benchmark_sweep_reach_a_kernel_that_takes_them(P, monk
     autotune.reload()
     errors = []
     comm = SimpleNamespace(P=P, nlocal=1, _h=None, _choices={}, launches=0, ll_max_bytes=4 << 20, ll2_max_bytes=(4 << 20) // 16 * 8 * P,
-                           has_multicast=True, device=0, is_symmetric=lambda t: True, _err=lambda rc: errors.append(rc))
+                           has_multicast=multicast, device=0, is_symmetric=lambda t: True, _err=lambda rc: errors.append(rc))
     for dtype in (torch.float32, torch.bfloat16):
         esz = 4 if dtype == torch.float32 else 2
         sz = 8
@@ -119,5 +121,5 @@ def test_the_sizes_of_the_benchmark_sweep_reach_a_kernel_that_takes_them(P, monk
     autotune.reload()
     assert not errors, (errors, [c for c in fake.calls][-6:])
     # the tuned hierarchical cell is still used where the length allows it (8 ranks: the 32-byte vector of the sweep)
-    if P == 8:
+    if P == 8 and multicast:
         assert any(name.startswith("radix_batch:ll") and coll == 0 and b == P for coll, name, k, b, count in fake.calls)

@@ -59,11 +59,11 @@ _ANY_COUNT = ("ll", "ll2", "nvls", "nvls1", "recursive_doubling", "ring", "k_red
 def any_count(coll: str, algo: str, k: int, b: int, count: int, P: int, ll_ok: bool, payload_bytes: int = 0):
     """The tuned table and the fallback rule are made from vectors whose length is a multiple of the number of
     ranks.  An allreduce of any other length keeps the choice only if that kernel takes any length; otherwise it
-    runs on the one-shot line kernel while the message fits its inbox, as recursive doubling (whole-vector
-    exchanges, few rounds) up to 1 MiB and as the ring (bandwidth-optimal, ragged chunks) above."""
+    runs on the one-shot line kernel up to 256 KiB (if the message fits its inbox), as recursive doubling
+    (whole-vector exchanges, few rounds) up to 1 MiB and as the ring (bandwidth-optimal, ragged chunks) above."""
     if coll != "allreduce" or P <= 1 or count % P == 0 or algo.split(":")[0] in _ANY_COUNT:
         return algo, k, b
-    if ll_ok:
+    if ll_ok and payload_bytes <= (256 << 10):      # one-shot: every rank sends the whole vector to every peer
         return "ll", 2, 1
     return ("recursive_doubling", 2, 1) if payload_bytes <= (1 << 20) else ("ring", 2, 1)
 
